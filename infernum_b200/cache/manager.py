@@ -1,0 +1,255 @@
+"""The cache manager: pages of keys and values with a block table per request,
+grouped by what layers need, and slots of fixed-size per-request state.
+
+* A *group* is a set of scheduled layer runs with the same paged-cache needs
+  (kv heads, head size, window).  Each group has its own page pool, its own
+  device pools (one K and one V tensor ``[pages, kv_heads, page_size, hd]``
+  per member) and its own block table per request; one page id covers all
+  members of its group.  The reference has a single implicit group: one table
+  indexes every layer (infernum-cuda/src/inner/cuda/paged_kv_cache.rs:45-112,
+  719-721).
+* Pages are taken per step for exactly the tokens of that step (``extend``),
+  counted as cached after the step ran (``commit``), and given back when the
+  request ends (``release``) or - in a group with a window - once every token
+  on them is out of reach of all later queries.  A returned page is handed out
+  again first.  (The reference allocates a whole prompt at admission and
+  frees only at the end: infernum-runtime/src/scheduler.rs:289-337.)
+* A request also holds one *slot* while it lives: the index of its row in
+  every state tensor ``[slots, *shape]`` that a mixer declared; the row is
+  zeroed when the slot is taken.
+
+All bookkeeping is host-side and runs without a GPU (``device=None``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..errors import CacheError, OutOfPagesError
+from ..parts.base import PagedCacheSpec, StateSpec
+from .pages import PagePool
+
+
+@dataclass
+class LayerCache:
+    """What a mixer gets for one scheduled run."""
+
+    group: int = -1  # index into StepContext.block_tables; -1: no paged cache
+    k_pool: Optional[torch.Tensor] = None
+    v_pool: Optional[torch.Tensor] = None
+    page_size: int = 0
+    num_pages: int = 0
+    state: Optional[torch.Tensor] = None  # [slots, *shape]
+    owner: bool = True  # False: this run reads another run's cache and must not write
+
+
+@dataclass
+class CacheGroup:
+    spec: PagedCacheSpec
+    positions: List[int]  # schedule positions that own a cache in this group
+    pool: PagePool
+
+
+@dataclass
+class RequestCache:
+    """Everything the manager holds for one live request."""
+
+    request_id: object
+    slot: int
+    num_tokens: int = 0  # tokens whose keys/values are in the cache
+    reserved_tokens: int = 0  # tokens that pages are held for (>= num_tokens)
+    tables: List[List[int]] = field(default_factory=list)  # per group; -1 = given back
+    released: bool = False
+
+
+class CacheManager:
+    def __init__(self, needs: Sequence, page_size: int, num_pages: int, max_requests: int,
+                 dtype: torch.dtype = torch.bfloat16, device=None):
+        """``needs``: one item per schedule position with attributes
+        ``paged`` (PagedCacheSpec or None), ``state`` (StateSpec or None) and
+        ``cache_of`` (an earlier position or None).  ``num_pages`` is the size
+        of every group's pool."""
+        if page_size <= 0:
+            raise CacheError("page_size must be positive")
+        if max_requests <= 0:
+            raise CacheError("max_requests must be positive")
+        self.page_size = int(page_size)
+        self.num_pages = int(num_pages)
+        self.max_requests = int(max_requests)
+        self.dtype = dtype
+        self.device = device
+        self.groups: List[CacheGroup] = []
+        self.layer_caches: List[LayerCache] = []
+        self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
+        self._requests: Dict[object, RequestCache] = {}
+        self._state_tensors: List[torch.Tensor] = []
+
+        group_of_spec: Dict[PagedCacheSpec, int] = {}
+        for need in needs:
+            lc = LayerCache()
+            if need.cache_of is not None:
+                src = self.layer_caches[need.cache_of]
+                lc = LayerCache(group=src.group, k_pool=src.k_pool, v_pool=src.v_pool,
+                                page_size=src.page_size, num_pages=src.num_pages, owner=False)
+            elif need.paged is not None:
+                g = group_of_spec.get(need.paged)
+                if g is None:
+                    g = len(self.groups)
+                    group_of_spec[need.paged] = g
+                    self.groups.append(CacheGroup(need.paged, [], PagePool(self.num_pages)))
+                self.groups[g].positions.append(need.position)
+                lc.group, lc.page_size, lc.num_pages = g, self.page_size, self.num_pages
+                if device is not None:
+                    shape = (self.num_pages, need.paged.kv_heads, self.page_size, need.paged.head_dim)
+                    lc.k_pool = torch.zeros(shape, dtype=dtype, device=device)
+                    lc.v_pool = torch.zeros(shape, dtype=dtype, device=device)
+            if need.state is not None and need.cache_of is None:
+                if device is not None:
+                    lc.state = torch.zeros((self.max_requests, *need.state.shape),
+                                           dtype=need.state.dtype, device=device)
+                    self._state_tensors.append(lc.state)
+            self.layer_caches.append(lc)
+
+    # ---- sizes --------------------------------------------------------------
+    def pages_for(self, tokens: int) -> int:
+        return (tokens + self.page_size - 1) // self.page_size
+
+    @property
+    def max_blocks_per_request(self) -> int:
+        return self.num_pages
+
+    def bytes_per_token(self) -> int:
+        """Cache bytes one token occupies over all groups and members."""
+        el = torch.empty((), dtype=self.dtype).element_size()
+        return sum(2 * g.spec.kv_heads * g.spec.head_dim * el * len(g.positions) for g in self.groups)
+
+    def free_pages(self) -> List[int]:
+        return [g.pool.num_free for g in self.groups]
+
+    @property
+    def num_free_slots(self) -> int:
+        return len(self._free_slots)
+
+    def live_requests(self) -> List[RequestCache]:
+        return list(self._requests.values())
+
+    # ---- a request's life ---------------------------------------------------
+    def admit(self, request_id) -> RequestCache:
+        """Takes a slot (zeroing its state rows); no pages yet."""
+        if request_id in self._requests:
+            raise CacheError(f"request {request_id!r} is already live")
+        if not self._free_slots:
+            raise OutOfPagesError(f"all {self.max_requests} request slots are taken")
+        slot = self._free_slots.pop()
+        for st in self._state_tensors:
+            st[slot].zero_()
+        rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups])
+        self._requests[request_id] = rc
+        return rc
+
+    def get(self, request_id) -> RequestCache:
+        try:
+            return self._requests[request_id]
+        except KeyError:
+            raise CacheError(f"request {request_id!r} is not live") from None
+
+    def has(self, request_id) -> bool:
+        return request_id in self._requests
+
+    def pages_needed(self, rc: RequestCache, new_tokens: int) -> List[int]:
+        """Per group: pages to add so that ``reserved + new_tokens`` tokens fit."""
+        total = self.pages_for(rc.reserved_tokens + new_tokens)
+        return [max(0, total - len(t)) for t in rc.tables]
+
+    def can_extend(self, rc: RequestCache, new_tokens: int) -> bool:
+        return all(n <= g.pool.num_free for n, g in zip(self.pages_needed(rc, new_tokens), self.groups))
+
+    def extend(self, rc: RequestCache, new_tokens: int) -> None:
+        """Holds pages for ``new_tokens`` more tokens, in every group or in none."""
+        self._check_live(rc)
+        if new_tokens < 0:
+            raise CacheError("extend: negative token count")
+        need = self.pages_needed(rc, new_tokens)
+        for n, g in zip(need, self.groups):
+            if n > g.pool.num_free:
+                raise OutOfPagesError(
+                    f"request {rc.request_id!r} needs {n} more pages, {g.pool.num_free} are free")
+        for n, g, table in zip(need, self.groups, rc.tables):
+            table.extend(g.pool.allocate_many(n))
+        rc.reserved_tokens += new_tokens
+
+    def commit(self, rc: RequestCache, new_tokens: int) -> None:
+        """The step ran: ``new_tokens`` more tokens are cached.  Pages of a
+        windowed group that no later query can reach are given back."""
+        self._check_live(rc)
+        if rc.num_tokens + new_tokens > rc.reserved_tokens:
+            raise CacheError("commit: more tokens than pages were held for")
+        rc.num_tokens += new_tokens
+        for g, table in zip(self.groups, rc.tables):
+            w = g.spec.window
+            if w <= 0:
+                continue
+            # the next query sits at position >= num_tokens and reads keys
+            # >= num_tokens - w + 1; page i holds [i*ps, (i+1)*ps)
+            first_needed = rc.num_tokens - w + 1
+            i = 0
+            while i < len(table) and (i + 1) * self.page_size <= first_needed:
+                if table[i] >= 0:
+                    g.pool.free(table[i])
+                    table[i] = -1
+                i += 1
+
+    def cancel_reservation(self, rc: RequestCache) -> None:
+        """Gives back pages held beyond the cached tokens (a step that did not run)."""
+        self._check_live(rc)
+        keep = self.pages_for(rc.num_tokens)
+        for g, table in zip(self.groups, rc.tables):
+            while len(table) > keep:
+                page = table.pop()
+                if page >= 0:
+                    g.pool.free(page)
+        rc.reserved_tokens = rc.num_tokens
+
+    def release(self, rc: RequestCache) -> None:
+        """The request ended (or is preempted): pages and slot go back."""
+        self._check_live(rc)
+        for g, table in zip(self.groups, rc.tables):
+            for page in table:
+                if page >= 0:
+                    g.pool.free(page)
+            table.clear()
+        self._free_slots.append(rc.slot)
+        rc.released = True
+        rc.num_tokens = rc.reserved_tokens = 0
+        del self._requests[rc.request_id]
+
+    def _check_live(self, rc: RequestCache) -> None:
+        if rc.released or self._requests.get(rc.request_id) is not rc:
+            raise CacheError(f"request {rc.request_id!r} is not live (released twice?)")
+
+    # ---- invariants, for tests ----------------------------------------------
+    def check_invariants(self) -> None:
+        """No page lost, none held twice, none both free and held."""
+        for gi, g in enumerate(self.groups):
+            held: Dict[int, object] = {}
+            for rc in self._requests.values():
+                for page in rc.tables[gi]:
+                    if page < 0:
+                        continue
+                    if page in held:
+                        raise CacheError(f"group {gi}: page {page} is held by "
+                                         f"{held[page]!r} and {rc.request_id!r}")
+                    held[page] = rc.request_id
+                    if not g.pool.is_in_use(page):
+                        raise CacheError(f"group {gi}: page {page} is held but marked free")
+            if len(held) != g.pool.num_used:
+                raise CacheError(f"group {gi}: {g.pool.num_used} pages are out, "
+                                 f"{len(held)} are in tables (a page was lost)")
+        slots = [rc.slot for rc in self._requests.values()]
+        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
+            raise CacheError("a request slot is held twice")
+        if len(slots) + len(self._free_slots) != self.max_requests:
+            raise CacheError("a request slot was lost")

@@ -1,0 +1,91 @@
+// Shared device helpers for the sm_100a kernels of this package.
+//
+// Conventions used by every exported function:
+//   * plain C ABI, pointers are device pointers, `stream` is a cudaStream_t
+//     passed as void*;
+//   * the return value is 0 on success, a positive cudaError_t from the
+//     launch, or a negative IB_ERR_* code when the arguments are refused;
+//   * nothing is allocated and nothing synchronises.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define IB_OK 0
+#define IB_ERR_BAD_ARG (-1)       // a size or pointer the kernel cannot take
+#define IB_ERR_UNSUPPORTED (-2)   // a configuration this build does not cover
+#define IB_ERR_TOO_LARGE (-3)     // beyond a stated maximum
+
+// Bits of the device-side error word that kernels may set (never trap).
+#define IB_FLAG_BAD_TOKEN 1u      // token id outside the vocabulary
+#define IB_FLAG_BAD_PAGE 2u       // block-table entry outside the pool
+#define IB_FLAG_WAIT_TIMEOUT 4u   // a bounded wait on a barrier gave up
+
+#define IB_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define IB_LAUNCH_CHECK()                         \
+    do {                                          \
+        cudaError_t e__ = cudaGetLastError();     \
+        if (e__ != cudaSuccess) return (int)e__;  \
+    } while (0)
+
+namespace ib {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` must hold 33 floats of shared memory.  The order of the additions
+// depends only on blockDim, never on other blocks.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+}  // namespace ib

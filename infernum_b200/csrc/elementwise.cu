@@ -1,0 +1,295 @@
+// Bandwidth-bound kernels of the decoder step: token embedding, residual add
+// fused with RMSNorm, rotary embedding fused with the write of K and V into
+// the paged cache, and SiLU(gate) * up.  All arithmetic is done in 32-bit and
+// rounded once at the store.
+//
+// What each computes follows the reference's kernels:
+//   embedding  out[t,:] = table[ids[t],:]            infernum-cuda/kernels/embed.cu:36-50
+//   rmsnorm    y = x * rsqrt(mean(x^2)+eps) * w      infernum-cuda/kernels/rmsnorm.cu:64-94
+//   add+norm   s = r + x; y = rmsnorm(s)             infernum-cuda/kernels/add_rmsnorm.cu:78-108
+//   rope       half-rotation pairs (j, j+rd/2)       infernum-cuda/kernels/rope.cu:25-41
+//   kv append  pool[table[p/bs]][p%bs] = k, v        infernum-cuda/kernels/append_kv_paged.cu:110-192
+//   silu*mul   g/(1+exp(-g)) * u                     infernum-cuda/kernels/silu.cu:105-116
+// Unlike the reference the residual stream stays in 32-bit between layers, and
+// rotation angles are computed in 32-bit from the position and the inverse
+// frequency (the reference rounds its tables to bf16).
+#include "common.cuh"
+
+using namespace ib;
+
+// ---------------------------------------------------------------------------
+// Embedding: residual[t, :] = table[ids[t], :] widened to 32-bit.
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                             float* __restrict__ out, int H, int V, unsigned* __restrict__ err) {
+    const int row = blockIdx.x;
+    const int id = ids[row];
+    float* o = out + (size_t)row * H;
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicOr(err, IB_FLAG_BAD_TOKEN);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const TW* src = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(src[i]);
+}
+
+IB_EXPORT int ib_embed(const int* ids, const void* table, int table_dtype, float* out, int n_rows,
+                       int H, int V, unsigned* err, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (H <= 0 || V <= 0 || !ids || !table || !out || !err) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == 0)
+        embed_kernel<float><<<n_rows, threads, 0, s>>>(ids, (const float*)table, out, H, V, err);
+    else if (table_dtype == 1)
+        embed_kernel<bf16><<<n_rows, threads, 0, s>>>(ids, (const bf16*)table, out, H, V, err);
+    else
+        return IB_ERR_UNSUPPORTED;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Residual add + RMSNorm.
+//   s = residual[src] (+ delta[src]);  if write_residual: residual[src] = s
+//   out[row] = s * rsqrt(mean(s^2) + eps) * weight
+// `row_idx` (optional) selects source rows, the output is then compact; it is
+// how the final norm runs only on the rows whose logits are wanted.
+// One block per row; the reduction order depends on H and blockDim only.
+// ---------------------------------------------------------------------------
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                   const TW* __restrict__ weight, TO* __restrict__ out,
+                                   const int* __restrict__ row_idx, int H, float eps,
+                                   int write_residual) {
+    __shared__ float scratch[33];
+    const int row = blockIdx.x;
+    const int src = row_idx ? row_idx[row] : row;
+    float* r = residual + (size_t)src * H;
+    const TD* d = delta ? delta + (size_t)src * H : nullptr;
+    TO* o = out + (size_t)row * H;
+
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (d) {
+            v += to_f32(d[i]);
+            if (write_residual) r[i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (d && !write_residual) v += to_f32(d[i]);
+        o[i] = from_f32<TO>((v * inv) * to_f32(weight[i]));
+    }
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float* residual, const void* delta, const void* weight,
+                              int weight_dtype, void* out, const int* row_idx, int n_rows, int H,
+                              float eps, int write_residual, cudaStream_t s) {
+    int threads = 256;
+    if (H >= 8192) threads = 1024;
+    else if (H >= 2048) threads = 512;
+    else if (H <= 256) threads = 64;
+    if (weight_dtype == 0)
+        add_rmsnorm_kernel<TD, float, TO><<<n_rows, threads, 0, s>>>(
+            residual, (const TD*)delta, (const float*)weight, (TO*)out, row_idx, H, eps,
+            write_residual);
+    else if (weight_dtype == 1)
+        add_rmsnorm_kernel<TD, bf16, TO><<<n_rows, threads, 0, s>>>(
+            residual, (const TD*)delta, (const bf16*)weight, (TO*)out, row_idx, H, eps,
+            write_residual);
+    else
+        return IB_ERR_UNSUPPORTED;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// act_dtype is the type of `delta` and of `out` (0 = f32, 1 = bf16).
+IB_EXPORT int ib_add_rmsnorm(float* residual, const void* delta, const void* weight,
+                             int weight_dtype, void* out, int act_dtype, const int* row_idx,
+                             int n_rows, int H, float eps, int write_residual, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (H <= 0 || !residual || !weight || !out || !(eps > 0.f)) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == 0)
+        return launch_add_rmsnorm<float, float>(residual, delta, weight, weight_dtype, out, row_idx,
+                                                n_rows, H, eps, write_residual, s);
+    if (act_dtype == 1)
+        return launch_add_rmsnorm<bf16, bf16>(residual, delta, weight, weight_dtype, out, row_idx,
+                                              n_rows, H, eps, write_residual, s);
+    return IB_ERR_UNSUPPORTED;
+}
+
+// residual[row] += delta[row] with no norm (used when a stream ends without one).
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                    size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) residual[i] += to_f32(delta[i]);
+}
+
+IB_EXPORT int ib_residual_add(float* residual, const void* delta, int act_dtype, long long n,
+                              void* stream) {
+    if (n <= 0) return IB_OK;
+    if (!residual || !delta) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (act_dtype == 0)
+        residual_add_kernel<float><<<blocks, 256, 0, s>>>(residual, (const float*)delta, (size_t)n);
+    else if (act_dtype == 1)
+        residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(residual, (const bf16*)delta, (size_t)n);
+    else
+        return IB_ERR_UNSUPPORTED;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Rotary embedding of q and k (in 32-bit), and the write of rotated k and of
+// v into the pages of the cache.
+//   qkv row layout: [ q: nh*hd | k: nkv*hd | v: nkv*hd ], row stride qkv_stride.
+//   q is rotated in place; k is rotated in place too (so the row can be
+//   checked) and copied to the pool; v is copied.
+//   pools: [num_pages, nkv, page_size, hd].
+//   A pair item p < rd/2 rotates elements (p, p + rd/2); items beyond cover
+//   the dims [rd, hd) that are not rotated.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, int qkv_stride,
+                                   const int* __restrict__ positions,
+                                   const int* __restrict__ row_entry,
+                                   const int* __restrict__ block_tables, int max_blocks,
+                                   const float* __restrict__ inv_freq, T* __restrict__ k_pool,
+                                   T* __restrict__ v_pool, int nh, int nkv, int hd, int rd,
+                                   int page_size, int num_pages, int write_kv,
+                                   unsigned* __restrict__ err) {
+    const int row = blockIdx.x;
+    const int half = hd / 2;
+    const int rhalf = rd / 2;
+    const int items_qk = (nh + nkv) * half;
+    const int items = items_qk + (write_kv ? nkv * half : 0);
+    const int pos = positions[row];
+    T* base = qkv + (size_t)row * qkv_stride;
+
+    long long slot_base = -1;  // element offset of (page, kv head 0, slot, 0)
+    if (write_kv) {
+        const int e = row_entry[row];
+        const int page = block_tables[(size_t)e * max_blocks + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
+        } else {
+            slot_base = ((long long)page * nkv * page_size + (pos % page_size)) * hd;
+        }
+    }
+    const long long head_step = (long long)page_size * hd;
+
+    for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < items; it += gridDim.y * blockDim.x) {
+        if (it < items_qk) {
+            const int head = it / half, p = it % half;
+            T* x = base + (size_t)head * hd;
+            int d0, d1;
+            float y0, y1;
+            if (p < rhalf) {
+                d0 = p;
+                d1 = p + rhalf;
+                const float angle = (float)pos * inv_freq[p];
+                float sn, cs;
+                sincosf(angle, &sn, &cs);
+                const float x0 = to_f32(x[d0]), x1 = to_f32(x[d1]);
+                y0 = x0 * cs - x1 * sn;
+                y1 = x0 * sn + x1 * cs;
+                x[d0] = from_f32<T>(y0);
+                x[d1] = from_f32<T>(y1);
+            } else {
+                d0 = rd + 2 * (p - rhalf);
+                d1 = d0 + 1;
+                y0 = to_f32(x[d0]);
+                y1 = to_f32(x[d1]);
+            }
+            if (head >= nh && slot_base >= 0) {
+                T* dst = k_pool + slot_base + (long long)(head - nh) * head_step;
+                dst[d0] = from_f32<T>(y0);
+                dst[d1] = from_f32<T>(y1);
+            }
+        } else if (slot_base >= 0) {
+            const int vi = it - items_qk;
+            const int g = vi / half, p = vi % half;
+            const T* x = base + (size_t)(nh + nkv + g) * hd;
+            T* dst = v_pool + slot_base + (long long)g * head_step;
+            dst[2 * p] = x[2 * p];
+            dst[2 * p + 1] = x[2 * p + 1];
+        }
+    }
+}
+
+IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int* positions,
+                             const int* row_entry, const int* block_tables, int max_blocks,
+                             const float* inv_freq, void* k_pool, void* v_pool, int n_rows, int nh,
+                             int nkv, int hd, int rd, int page_size, int num_pages, int write_kv,
+                             unsigned* err, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!qkv || !positions || !err || nh <= 0 || nkv < 0 || hd <= 0 || (hd & 1) || rd < 0 ||
+        rd > hd || (rd & 1))
+        return IB_ERR_BAD_ARG;
+    if (rd > 0 && !inv_freq) return IB_ERR_BAD_ARG;
+    if (write_kv && (!row_entry || !block_tables || !k_pool || !v_pool || page_size <= 0 ||
+                     max_blocks <= 0 || num_pages <= 0))
+        return IB_ERR_BAD_ARG;
+    if (qkv_stride < (nh + 2 * nkv) * hd && write_kv) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int items = (nh + nkv) * (hd / 2) + (write_kv ? nkv * (hd / 2) : 0);
+    const int threads = 128;
+    int by = (items + threads - 1) / threads;
+    if (by > 16) by = 16;
+    dim3 grid(n_rows, by);
+    if (act_dtype == 0)
+        rope_append_kernel<float><<<grid, threads, 0, s>>>(
+            (float*)qkv, qkv_stride, positions, row_entry, block_tables, max_blocks, inv_freq,
+            (float*)k_pool, (float*)v_pool, nh, nkv, hd, rd, page_size, num_pages, write_kv, err);
+    else if (act_dtype == 1)
+        rope_append_kernel<bf16><<<grid, threads, 0, s>>>(
+            (bf16*)qkv, qkv_stride, positions, row_entry, block_tables, max_blocks, inv_freq,
+            (bf16*)k_pool, (bf16*)v_pool, nh, nkv, hd, rd, page_size, num_pages, write_kv, err);
+    else
+        return IB_ERR_UNSUPPORTED;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU activation: out[t, i] = silu(x[t, i]) * x[t, I + i], x is [N, 2I].
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int I, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t row = idx / I;
+    const int i = (int)(idx % I);
+    const float g = to_f32(x[row * 2 * I + i]);
+    const float u = to_f32(x[row * 2 * I + I + i]);
+    const float act = g / (1.f + expf(-g));
+    out[idx] = from_f32<T>(act * u);
+}
+
+IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, int I, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !out || I <= 0) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)n_rows * I;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (act_dtype == 0)
+        silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)x, (float*)out, I, total);
+    else if (act_dtype == 1)
+        silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)x, (bf16*)out, I, total);
+    else
+        return IB_ERR_UNSUPPORTED;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

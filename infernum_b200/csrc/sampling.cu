@@ -1,0 +1,200 @@
+// Token selection from 32-bit logits, one block per row.
+//
+//  ib_argmax   greedy: the largest logit, the lowest index among equals.
+//              (the reference: infernum-cuda/kernels/argmax.cu:64-136)
+//  ib_sample   the reference's sampler (infernum-cuda/src/inner/cuda/ops/sample.rs:86-160),
+//              which runs on the host there, as one device kernel:
+//                1. repetition penalty over the recent tokens, applied once per
+//                   occurrence: logit > 0 ? logit / r : logit * r
+//                2. divide by the temperature, softmax with max subtraction
+//                3. nucleus: keep the most probable tokens whose mass first
+//                   reaches top_p (all tokens as probable as the last one kept)
+//                4. inverse CDF over the kept tokens with a uniform number u
+//              The reference walks the kept tokens in order of probability; this
+//              kernel walks them in order of index, which gives the same
+//              distribution without a sort.  u is supplied by the caller.
+#include "common.cuh"
+
+using namespace ib;
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int ld, int V,
+                              int* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* x = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int bi = V;  // "none yet": any real index is lower
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best || (v == best && i < bi)) {
+            best = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = bi;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : V;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) out[blockIdx.x] = bi < V ? bi : 0;
+    }
+}
+
+IB_EXPORT int ib_argmax(const float* logits, int ld, int n_rows, int V, int* out, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!logits || !out || V <= 0 || ld < V) return IB_ERR_BAD_ARG;
+    const int threads = V >= 8192 ? 1024 : 256;
+    argmax_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(logits, ld, V, out);
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// Per-row parameters of ib_sample (one struct per row, in device memory).
+struct SampleParams {
+    float temperature;  // > 0
+    float top_p;        // in (0, 1]; >= 1 keeps every token
+    float penalty;      // repetition penalty, 1 = off
+    float u;            // uniform number in [0, 1)
+    int n_recent;       // how many entries of this row's recent-token list count
+    int pad;
+};
+
+__global__ void sample_kernel(float* __restrict__ logits, int ld, int V,
+                              const SampleParams* __restrict__ params,
+                              const int* __restrict__ recent, int recent_ld,
+                              int* __restrict__ out) {
+    __shared__ float scratch[33];
+    __shared__ float chunk_sum[1024];
+    __shared__ int chosen;
+    const int row = blockIdx.x;
+    float* x = logits + (size_t)row * ld;
+    const SampleParams pr = params[row];
+    const int nt = blockDim.x;
+
+    // 1. repetition penalty, in place, once per occurrence, in list order.
+    if (threadIdx.x == 0 && pr.penalty != 1.f) {
+        const int* rt = recent + (size_t)row * recent_ld;
+        for (int i = 0; i < pr.n_recent; ++i) {
+            const int t = rt[i];
+            if (t >= 0 && t < V) {
+                const float v = x[t];
+                x[t] = v > 0.f ? v / pr.penalty : v * pr.penalty;
+            }
+        }
+    }
+    __syncthreads();
+
+    // 2. softmax statistics of logits / temperature.
+    const float inv_t = 1.f / pr.temperature;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += nt) mx = fmaxf(mx, x[i] * inv_t);
+    mx = block_max(mx, scratch);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < V; i += nt) sum += expf(x[i] * inv_t - mx);
+    sum = block_sum(sum, scratch);
+    const float inv_sum = 1.f / sum;
+
+    // 3. nucleus threshold: the largest probability t with mass{p >= t} >= top_p,
+    //    found by bisection on the bit pattern of t (positive floats order like
+    //    their bits), so t ends exactly on the probability of the last token kept.
+    float thresh = 0.f;
+    if (pr.top_p < 1.f) {
+        unsigned lo = 0u, hi = __float_as_uint(1.0f);  // mass(lo) >= top_p always
+        while (lo < hi) {
+            const unsigned mid = lo + (hi - lo + 1u) / 2u;
+            const float t = __uint_as_float(mid);
+            float mass = 0.f;
+            for (int i = threadIdx.x; i < V; i += nt) {
+                const float p = expf(x[i] * inv_t - mx) * inv_sum;
+                mass += p >= t ? p : 0.f;
+            }
+            mass = block_sum(mass, scratch);
+            if (mass >= pr.top_p) lo = mid; else hi = mid - 1u;
+        }
+        thresh = __uint_as_float(lo);
+    }
+
+    // 4. inverse CDF over kept tokens in index order.  Thread k owns the
+    //    contiguous range [k*per, (k+1)*per).
+    const int per = (V + nt - 1) / nt;
+    const int begin = min(V, threadIdx.x * per), end = min(V, begin + per);
+    float mine = 0.f;
+    for (int i = begin; i < end; ++i) {
+        const float p = expf(x[i] * inv_t - mx) * inv_sum;
+        mine += p >= thresh ? p : 0.f;
+    }
+    chunk_sum[threadIdx.x] = mine;
+    if (threadIdx.x == 0) chosen = -1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+        for (int k = 0; k < nt; ++k) total += chunk_sum[k];
+        const float target = pr.u * total;
+        float run = 0.f, excl = 0.f;
+        int owner = -1;
+        for (int k = 0; k < nt; ++k) {
+            if (chunk_sum[k] > 0.f) {
+                owner = k;  // the last non-empty chunk is the fallback
+                excl = run;
+                if (target < run + chunk_sum[k]) break;
+            }
+            run += chunk_sum[k];
+        }
+        scratch[0] = excl;
+        scratch[1] = target;
+        chosen = owner;
+    }
+    __syncthreads();
+    if (threadIdx.x == chosen) {
+        float run = scratch[0];
+        const float target = scratch[1];
+        int pick = -1, last_kept = -1;
+        for (int i = begin; i < end; ++i) {
+            const float p = expf(x[i] * inv_t - mx) * inv_sum;
+            if (p >= thresh) {
+                last_kept = i;
+                run += p;
+                if (target < run) {
+                    pick = i;
+                    break;
+                }
+            }
+        }
+        out[row] = pick >= 0 ? pick : (last_kept >= 0 ? last_kept : 0);
+    }
+    if (chosen < 0 && threadIdx.x == 0) out[row] = 0;
+}
+
+IB_EXPORT int ib_sample(float* logits, int ld, int n_rows, int V, const void* params,
+                        const int* recent, int recent_ld, int* out, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!logits || !params || !out || V <= 0 || ld < V) return IB_ERR_BAD_ARG;
+    if (recent_ld > 0 && !recent) return IB_ERR_BAD_ARG;
+    sample_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(
+        logits, ld, V, (const SampleParams*)params, recent, recent_ld, out);
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

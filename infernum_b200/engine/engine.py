@@ -1,0 +1,195 @@
+"""The token engine: requests in, tokens out.
+
+It plays the role of the reference's ``Engine``
+(infernum-runtime/src/engine.rs:39-170: ``new``/``with_config``, ``submit``,
+``generate``, ``generate_stream``) and of its worker loop (:177-238), but as a
+loop the caller drives: ``step()`` runs one scheduling round and one model
+step, ``generate*`` run until their requests are done.  Events have the
+reference's kinds: a token, finished(reason), error
+(infernum-runtime/src/scheduler.rs:37-44).
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..errors import InfernumError
+from ..sampling.params import GenerateOptions
+from ..sampling.sampler import Sampler, recent_window
+from .scheduler import BatchConfig, FinishReason, Scheduler, Sequence_, StepPlan
+from .step import ModelRunner, StepEntry
+
+
+@dataclass
+class GenerationEvent:
+    kind: str  # "token" | "finished" | "error"
+    token: Optional[int] = None
+    reason: Optional[FinishReason] = None
+    message: Optional[str] = None
+
+
+@dataclass
+class RequestHandle:
+    """A submitted request: its tokens so far and its events."""
+
+    seq: Sequence_
+    events: List[GenerationEvent] = field(default_factory=list)
+    _reported_finish: bool = False
+
+    @property
+    def id(self) -> int:
+        return self.seq.id
+
+    @property
+    def tokens(self) -> List[int]:
+        return list(self.seq.generated_ids)
+
+    @property
+    def finished(self) -> bool:
+        return self.seq.finished
+
+    @property
+    def finish_reason(self) -> Optional[FinishReason]:
+        return self.seq.finish_reason
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    preemptions: int = 0
+    generated_tokens: int = 0
+    step_seconds: float = 0.0
+
+
+class Engine:
+    def __init__(self, model, config: Optional[BatchConfig] = None):
+        self.model = model
+        self.config = config or BatchConfig()
+        cfg = self.config
+        rt = model.rt
+        self.cache = CacheManager(model.cache_needs(), page_size=cfg.block_size,
+                                  num_pages=cfg.num_blocks, max_requests=cfg.max_batch_size,
+                                  dtype=rt.dtype, device=rt.device)
+        self.runner = ModelRunner(model, self.cache, max_rows=cfg.max_tokens_per_step,
+                                  max_entries=cfg.max_batch_size)
+        max_len = cfg.max_model_len or model.spec.max_position
+        self.scheduler = Scheduler(cfg, self.cache, max_len)
+        self.sampler = Sampler(rt.device)
+        self.stats = EngineStats()
+        self._handles: Dict[int, RequestHandle] = {}
+
+    @classmethod
+    def with_config(cls, model, config: BatchConfig) -> "Engine":
+        return cls(model, config)
+
+    # ---- requests ---------------------------------------------------------------
+    def submit(self, prompt_ids: Sequence[int], options: Optional[GenerateOptions] = None) -> RequestHandle:
+        vocab = self.model.spec.vocab_size
+        for t in prompt_ids:
+            if not 0 <= int(t) < vocab:
+                raise InfernumError(f"token id {t} is outside the vocabulary of {vocab}")
+        seq = self.scheduler.add_request(prompt_ids, options or GenerateOptions())
+        handle = RequestHandle(seq)
+        self._handles[seq.id] = handle
+        return handle
+
+    def cancel(self, handle: RequestHandle) -> None:
+        self.scheduler.cancel(handle.seq)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ---- one iteration -------------------------------------------------------------
+    def step(self) -> List[Tuple[RequestHandle, GenerationEvent]]:
+        """One scheduling round and one model step; returns the new events."""
+        t0 = time.perf_counter()
+        plan = self.scheduler.schedule()
+        self.stats.preemptions = self.scheduler.num_preemptions
+        events: List[Tuple[RequestHandle, GenerationEvent]] = []
+        if plan.portions:
+            entries = [StepEntry(p.seq.cache, p.tokens, [p.count - 1] if p.wants_logits else [])
+                       for p in plan.portions]
+            logits = self.runner.step(entries)
+            self.scheduler.commit(plan)
+            wanting = [p for p in plan.portions if p.wants_logits]
+            if logits is not None and wanting:
+                choices = []
+                for p in wanting:
+                    sp = p.seq.options.sampling
+                    choices.append(None if sp is None else
+                                   (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
+                chosen = self.sampler.select(logits, choices)
+                host = torch.cat([chosen, self.runner.rt.err]).cpu().tolist()
+                if host[-1]:
+                    self.runner.check_errors()
+                for p, tok in zip(wanting, host[:-1]):
+                    handle = self._handles[p.seq.id]
+                    emitted = self.scheduler.append_token(p.seq, tok)
+                    if emitted is not None:
+                        self.stats.generated_tokens += 1
+                        ev = GenerationEvent("token", token=emitted)
+                        handle.events.append(ev)
+                        events.append((handle, ev))
+            for p in plan.portions:
+                if p.count == 1 and p.start >= len(p.seq.prompt_ids):
+                    self.stats.decode_tokens += 1
+                else:
+                    self.stats.prefill_tokens += p.count
+            self.stats.steps += 1
+        for handle in list(self._handles.values()):
+            if handle.seq.finished and not handle._reported_finish:
+                handle._reported_finish = True
+                if handle.seq.finish_reason == FinishReason.ERROR:
+                    ev = GenerationEvent("error", message=handle.seq.error)
+                else:
+                    ev = GenerationEvent("finished", reason=handle.seq.finish_reason)
+                handle.events.append(ev)
+                events.append((handle, ev))
+                del self._handles[handle.id]
+        self.stats.step_seconds += time.perf_counter() - t0
+        return events
+
+    def run_until_done(self, handles: Optional[Sequence[RequestHandle]] = None) -> None:
+        while self.has_work() and (handles is None or any(not h.finished for h in handles)):
+            self.step()
+        self.scheduler._reap()
+
+    # ---- the reference's entry points ------------------------------------------------
+    def generate(self, prompt_ids: Sequence[int], options: Optional[GenerateOptions] = None) -> List[int]:
+        """Prompt token ids in, generated token ids out."""
+        handle = self.submit(prompt_ids, options)
+        self.run_until_done([handle])
+        if handle.seq.finish_reason == FinishReason.ERROR:
+            raise InfernumError(handle.seq.error or "generation failed")
+        return handle.tokens
+
+    def generate_stream(self, prompt_ids: Sequence[int],
+                        options: Optional[GenerateOptions] = None) -> Iterator[int]:
+        handle = self.submit(prompt_ids, options)
+        while not handle.finished:
+            for h, ev in self.step():
+                if h is handle and ev.kind == "token":
+                    yield ev.token
+                elif h is handle and ev.kind == "error":
+                    raise InfernumError(ev.message or "generation failed")
+        self.scheduler._reap()
+
+    def generate_batch(self, prompts: Sequence[Sequence[int]],
+                       options=None) -> List[List[int]]:
+        """Several requests at once through continuous batching; ``options``
+        is one GenerateOptions for all or a list with one per prompt."""
+        if options is None or isinstance(options, GenerateOptions):
+            options = [options] * len(prompts)
+        handles = [self.submit(p, o) for p, o in zip(prompts, options)]
+        self.run_until_done(handles)
+        for h in handles:
+            if h.seq.finish_reason == FinishReason.ERROR:
+                raise InfernumError(h.seq.error or "generation failed")
+        return [h.tokens for h in handles]

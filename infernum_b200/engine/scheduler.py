@@ -1,0 +1,329 @@
+"""Continuous batching: admits requests, cuts prompts into portions under a
+token budget, decodes, finishes, frees - and decides what happens when pages
+run out.
+
+What is kept from the reference's scheduler
+(infernum-runtime/src/scheduler.rs:197-404): a FIFO ``waiting`` queue and a
+``running`` list; phases Waiting -> Prefill -> Decode -> Finished(reason);
+admission first come first served and never skipping the head of the queue;
+``max_batch_size`` running requests at most; ``max_prefill_tokens`` caps one
+request's portion; finished requests are removed and their pages freed at the
+start of the next scheduling round (:289-305).
+
+What is different: the reference emits only the first portion of a long prompt
+and never the rest (:341-352, ``continue_prefill`` has no caller), allocates a
+whole prompt's blocks at admission, and on exhaustion during decode silently
+drops the new block (infernum-runtime/src/engine.rs:476-480).  Here
+
+  * a request is a sequence of tokens (prompt, then what it generated) of which
+    a prefix is *computed* (in the cache); every step feeds the next portion,
+    and a decode step is simply a portion of one token;
+  * each step has a budget ``max_tokens_per_step``: decoding requests first
+    (one token each), then running prompts in admission order, then new
+    admissions;
+  * pages are taken per step for exactly the step's tokens;
+  * when a decoding request needs a page and none is free, the most recently
+    admitted running request is *preempted*: its pages and slot are given
+    back, and it returns to the front of the waiting queue to be recomputed
+    from its tokens so far.  Its output does not change: greedy selection is a
+    function of the logits, and a sampled token's random number is a function
+    of (seed, tokens generated so far).  A prompt portion that does not fit is
+    shortened or waits; only if nothing at all can run is a victim preempted
+    for it.  A request that can never fit is refused when it is added.
+"""
+
+from __future__ import annotations
+
+import enum
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, List, Optional, Sequence
+
+from ..cache.manager import CacheManager, RequestCache
+from ..errors import SchedulingError
+from ..sampling.params import GenerateOptions
+
+
+class FinishReason(enum.Enum):
+    STOP = "stop"  # the end-of-sequence token was selected
+    LENGTH = "length"  # max_new_tokens reached
+    CANCELLED = "cancelled"
+    ERROR = "error"
+
+
+class Phase(enum.Enum):
+    WAITING = "waiting"
+    PREFILL = "prefill"
+    DECODE = "decode"
+    FINISHED = "finished"
+
+
+@dataclass
+class BatchConfig:
+    """Engine limits; the first four are the reference's ``BatchConfig`` with
+    its defaults (infernum-runtime/src/scheduler.rs:73-95)."""
+
+    max_batch_size: int = 32
+    max_prefill_tokens: int = 512
+    block_size: int = 16
+    num_blocks: int = 1024
+    max_tokens_per_step: int = 2048
+    max_model_len: Optional[int] = None  # default: the model's max_position_embeddings
+
+
+@dataclass
+class Sequence_:
+    id: int
+    prompt_ids: List[int]
+    options: GenerateOptions
+    generated_ids: List[int] = field(default_factory=list)
+    phase: Phase = Phase.WAITING
+    finish_reason: Optional[FinishReason] = None
+    num_computed: int = 0  # tokens whose keys/values are in the cache
+    cache: Optional[RequestCache] = None
+    admitted_at: int = -1  # admission counter value, for "most recently admitted"
+    preemptions: int = 0
+    error: Optional[str] = None
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt_ids + self.generated_ids
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_ids) + len(self.generated_ids)
+
+    @property
+    def remaining(self) -> int:
+        return self.num_tokens - self.num_computed
+
+    @property
+    def finished(self) -> bool:
+        return self.phase == Phase.FINISHED
+
+
+@dataclass
+class Portion:
+    seq: Sequence_
+    start: int  # index of the first token fed
+    count: int
+    wants_logits: bool  # the portion reaches the end of the request's tokens
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.seq.tokens[self.start: self.start + self.count]
+
+
+@dataclass
+class StepPlan:
+    portions: List[Portion] = field(default_factory=list)
+    preempted: List[Sequence_] = field(default_factory=list)
+    admitted: List[Sequence_] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(p.count for p in self.portions)
+
+
+class Scheduler:
+    def __init__(self, config: BatchConfig, cache: CacheManager, max_model_len: int):
+        self.config = config
+        self.cache = cache
+        self.max_model_len = int(max_model_len)
+        self.waiting: Deque[Sequence_] = deque()
+        self.running: List[Sequence_] = []
+        self._next_id = 0
+        self._admissions = 0
+        self.num_preemptions = 0
+
+    # ---- requests --------------------------------------------------------------
+    def add_request(self, prompt_ids: Sequence[int], options: GenerateOptions) -> Sequence_:
+        prompt = [int(t) for t in prompt_ids]
+        if not prompt:
+            raise SchedulingError("a request needs at least one prompt token")
+        if options.max_new_tokens < 1:
+            raise SchedulingError("max_new_tokens must be at least 1")
+        total = len(prompt) + options.max_new_tokens
+        if total > self.max_model_len:
+            raise SchedulingError(
+                f"prompt ({len(prompt)}) + max_new_tokens ({options.max_new_tokens}) exceeds the "
+                f"longest sequence the engine takes ({self.max_model_len})")
+        # the last generated token is never fed, so total - 1 tokens are cached at most
+        if self.cache.pages_for(total - 1) > self.cache.num_pages:
+            raise SchedulingError(
+                f"the request needs {self.cache.pages_for(total - 1)} pages, the pool has "
+                f"{self.cache.num_pages}: it could never run")
+        seq = Sequence_(self._next_id, prompt, options)
+        self._next_id += 1
+        self.waiting.append(seq)
+        return seq
+
+    def cancel(self, seq: Sequence_) -> None:
+        if not seq.finished:
+            self._finish(seq, FinishReason.CANCELLED)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting) or any(not s.finished for s in self.running)
+
+    # ---- one scheduling round --------------------------------------------------
+    def schedule(self) -> StepPlan:
+        plan = StepPlan()
+        self._reap()
+        while True:
+            self._fill(plan)
+            if plan.portions or not self.running:
+                break
+            # Nothing fits although requests are running: make room.
+            victim = self._most_recent(exclude=None)
+            if len(self.running) == 1:
+                # cannot happen for a request that passed add_request; guard anyway
+                self._finish(victim, FinishReason.ERROR, "the page pool is too small for this request")
+                self._reap()
+                break
+            self._preempt(victim, plan)
+        return plan
+
+    def _fill(self, plan: StepPlan) -> None:
+        cfg = self.config
+        budget = cfg.max_tokens_per_step
+        plan.portions.clear()
+        scheduled = set()
+        # 1. decoding requests, oldest first; preempt the youngest for pages
+        for seq in sorted(self.running, key=lambda s: s.admitted_at):
+            if seq.finished or seq.phase != Phase.DECODE or seq.cache is None:
+                continue
+            if budget <= 0:
+                break
+            while not self.cache.can_extend(seq.cache, self._to_reserve(seq, 1)):
+                victim = self._most_recent(exclude=scheduled)
+                if victim is None:
+                    break
+                self._preempt(victim, plan)
+                if victim is seq:
+                    break
+            if seq.cache is None or not self.cache.can_extend(seq.cache, self._to_reserve(seq, 1)):
+                continue
+            self.cache.extend(seq.cache, self._to_reserve(seq, 1))
+            plan.portions.append(Portion(seq, seq.num_computed, 1, True))
+            scheduled.add(seq.id)
+            budget -= 1
+        # 2. running prompts (and recomputations), oldest first
+        for seq in sorted(self.running, key=lambda s: s.admitted_at):
+            if seq.finished or seq.phase != Phase.PREFILL or seq.cache is None:
+                continue
+            budget -= self._schedule_portion(seq, budget, plan)
+        # 3. admissions, first come first served, never skipping
+        #    (none in a round that preempted: the victim would come straight back)
+        while self.waiting and budget > 0 and len(self.running) < cfg.max_batch_size \
+                and self.cache.num_free_slots > 0 and not plan.preempted:
+            seq = self.waiting[0]
+            if seq.finished:  # cancelled while waiting
+                self.waiting.popleft()
+                continue
+            first = min(seq.remaining, cfg.max_prefill_tokens, budget)
+            fit = self._fit(None, first)
+            if fit < first and (self.running or fit <= 0):
+                break  # the head request's first portion does not fit: wait, skip nobody
+            self.waiting.popleft()
+            seq.cache = self.cache.admit(seq.id)
+            seq.phase = Phase.PREFILL
+            seq.num_computed = 0
+            seq.admitted_at = self._admissions
+            self._admissions += 1
+            self.running.append(seq)
+            plan.admitted.append(seq)
+            budget -= self._schedule_portion(seq, budget, plan)
+
+    def _to_reserve(self, seq: Sequence_, count: int) -> int:
+        """Tokens to add to the pages held so that ``count`` more can be computed."""
+        return max(0, seq.num_computed + count - seq.cache.reserved_tokens)
+
+    def _fit(self, rc: Optional[RequestCache], count: int) -> int:
+        """How many of ``count`` new tokens fit the free pages right now."""
+        ps = self.cache.page_size
+        free = min(self.cache.free_pages()) if self.cache.groups else 1 << 30
+        if rc is None:
+            return min(count, free * ps)
+        slack = max(len(t) for t in rc.tables) * ps - rc.reserved_tokens if rc.tables else 0
+        return min(count, slack + free * ps)
+
+    def _schedule_portion(self, seq: Sequence_, budget: int, plan: StepPlan) -> int:
+        if budget <= 0 or seq.remaining <= 0:
+            return 0
+        count = min(seq.remaining, self.config.max_prefill_tokens, budget)
+        count = self._fit(seq.cache, self._to_reserve(seq, count)) + \
+            (count - self._to_reserve(seq, count))
+        count = min(count, seq.remaining)
+        if count <= 0:
+            return 0
+        self.cache.extend(seq.cache, self._to_reserve(seq, count))
+        plan.portions.append(Portion(seq, seq.num_computed, count,
+                                     seq.num_computed + count == seq.num_tokens))
+        return count
+
+    # ---- after the step ran ------------------------------------------------------
+    def commit(self, plan: StepPlan, commit_cache: bool = False) -> None:
+        """The step ran: its tokens are cached.  The step function counts them
+        in the cache manager itself; ``commit_cache`` does it here for callers
+        that run no real step."""
+        for p in plan.portions:
+            seq = p.seq
+            if seq.cache is None:
+                continue
+            if commit_cache:
+                self.cache.commit(seq.cache, p.count)
+            seq.num_computed += p.count
+
+    def append_token(self, seq: Sequence_, token: int) -> Optional[int]:
+        """Takes the token selected for ``seq``; returns it if it is emitted.
+        End-of-sequence is neither stored nor emitted; the token selected
+        after the prompt counts as the first generated one
+        (infernum-runtime/src/engine.rs:445-481, 286-288)."""
+        if seq.finished:
+            return None
+        opts = seq.options
+        if opts.eos_token_id is not None and token == opts.eos_token_id and not opts.ignore_eos:
+            self._finish(seq, FinishReason.STOP)
+            return None
+        seq.generated_ids.append(int(token))
+        seq.phase = Phase.DECODE
+        if len(seq.generated_ids) >= opts.max_new_tokens:
+            self._finish(seq, FinishReason.LENGTH)
+        return int(token)
+
+    # ---- internals ---------------------------------------------------------------
+    def _most_recent(self, exclude) -> Optional[Sequence_]:
+        cands = [s for s in self.running
+                 if not s.finished and s.cache is not None and (not exclude or s.id not in exclude)]
+        return max(cands, key=lambda s: s.admitted_at) if cands else None
+
+    def _preempt(self, victim: Sequence_, plan: StepPlan) -> None:
+        plan.portions[:] = [p for p in plan.portions if p.seq is not victim]
+        self.cache.release(victim.cache)
+        victim.cache = None
+        victim.num_computed = 0
+        victim.phase = Phase.WAITING
+        victim.preemptions += 1
+        self.num_preemptions += 1
+        self.running.remove(victim)
+        self.waiting.appendleft(victim)
+        plan.preempted.append(victim)
+
+    def _finish(self, seq: Sequence_, reason: FinishReason, error: Optional[str] = None) -> None:
+        seq.phase = Phase.FINISHED
+        seq.finish_reason = reason
+        seq.error = error
+
+    def _reap(self) -> None:
+        """Removes finished requests and gives their pages and slots back."""
+        keep = []
+        for seq in self.running:
+            if seq.finished:
+                if seq.cache is not None:
+                    self.cache.release(seq.cache)
+                    seq.cache = None
+            else:
+                keep.append(seq)
+        self.running = keep
+        while self.waiting and self.waiting[0].finished:
+            self.waiting.popleft()

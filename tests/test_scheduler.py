@@ -1,0 +1,206 @@
+"""The scheduler's decisions with a fake step (no GPU): admission order, the
+token budget, portions, finishing, and what happens when pages run out."""
+from types import SimpleNamespace
+
+import pytest
+
+from infernum_b200.cache import CacheManager
+from infernum_b200.engine.scheduler import BatchConfig, FinishReason, Phase, Scheduler
+from infernum_b200.errors import SchedulingError
+from infernum_b200.parts.base import PagedCacheSpec
+from infernum_b200.sampling import GenerateOptions
+
+
+def make(num_blocks=64, block_size=4, max_batch=4, chunk=8, budget=16, max_len=256):
+    cfg = BatchConfig(max_batch_size=max_batch, max_prefill_tokens=chunk, block_size=block_size,
+                      num_blocks=num_blocks, max_tokens_per_step=budget)
+    need = SimpleNamespace(position=0, paged=PagedCacheSpec(1, 8, 0), state=None, cache_of=None)
+    cache = CacheManager([need], page_size=block_size, num_pages=num_blocks, max_requests=max_batch)
+    return Scheduler(cfg, cache, max_len), cache
+
+
+def fake_token(seq):
+    return (sum(seq.tokens) * 31 + len(seq.tokens)) % 97 + 3
+
+
+def run_step(sched, cache, log=None):
+    plan = sched.schedule()
+    cache.check_invariants()
+    for p in plan.portions:
+        assert p.tokens == p.seq.tokens[p.seq.num_computed: p.seq.num_computed + p.count]
+    sched.commit(plan, commit_cache=True)
+    for p in plan.portions:
+        if p.wants_logits:
+            sched.append_token(p.seq, fake_token(p.seq))
+    if log is not None:
+        log.append(plan)
+    return plan
+
+
+def drain(sched, cache, limit=10000):
+    log = []
+    while sched.has_work():
+        run_step(sched, cache, log)
+        assert len(log) < limit, "the scheduler does not terminate"
+    sched.schedule()  # reap
+    cache.check_invariants()
+    return log
+
+
+def solo_tokens(prompt, n_new):
+    sched, cache = make(num_blocks=256)
+    s = sched.add_request(prompt, GenerateOptions(max_new_tokens=n_new))
+    drain(sched, cache)
+    return s.generated_ids
+
+
+def test_first_come_first_served_and_batch_limit():
+    sched, cache = make(max_batch=2, budget=64, chunk=64)
+    seqs = [sched.add_request([1] * 5, GenerateOptions(max_new_tokens=3)) for _ in range(4)]
+    plan = run_step(sched, cache)
+    assert [p.seq.id for p in plan.portions] == [0, 1]
+    assert [s.phase for s in seqs] == [Phase.DECODE, Phase.DECODE, Phase.WAITING, Phase.WAITING]
+    log = drain(sched, cache)
+    assert all(s.finish_reason == FinishReason.LENGTH and len(s.generated_ids) == 3 for s in seqs)
+    first_seen = []
+    for plan in log:
+        for p in plan.portions:
+            if p.seq.id not in first_seen:
+                first_seen.append(p.seq.id)
+    assert first_seen == [0, 1, 2, 3] or first_seen == [2, 3]  # 0 and 1 started before the log
+
+
+def test_budget_decodes_first_then_portions():
+    sched, cache = make(budget=10, chunk=8, max_batch=4)
+    a = sched.add_request([2] * 3, GenerateOptions(max_new_tokens=50))
+    run_step(sched, cache)  # a prefilled, now decoding
+    b = sched.add_request(list(range(3, 33)), GenerateOptions(max_new_tokens=2))
+    plan = run_step(sched, cache)
+    assert [(p.seq.id, p.count, p.wants_logits) for p in plan.portions] == [(0, 1, True), (1, 8, False)]
+    plan = run_step(sched, cache)
+    assert [(p.seq.id, p.start, p.count) for p in plan.portions] == [(0, 4, 1), (1, 8, 8)]
+    c = sched.add_request([5] * 4, GenerateOptions(max_new_tokens=2))
+    plan = run_step(sched, cache)  # 1 decode + 8 of b + 1 left for c
+    assert [(p.seq.id, p.count) for p in plan.portions] == [(0, 1), (1, 8), (2, 1)]
+    assert plan.num_tokens == 10
+    plan = run_step(sched, cache)
+    # b's last 6 tokens finish its prompt: it wants logits; c continues
+    assert [(p.seq.id, p.count, p.wants_logits) for p in plan.portions] == \
+        [(0, 1, True), (1, 6, True), (2, 3, True)]
+    assert b.phase == Phase.DECODE and len(b.generated_ids) == 1
+    drain(sched, cache)
+
+
+def test_portions_cover_a_prompt_exactly_once():
+    sched, cache = make(budget=7, chunk=5)
+    prompt = list(range(10, 33))
+    s = sched.add_request(prompt, GenerateOptions(max_new_tokens=1))
+    log = drain(sched, cache)
+    fed = [t for plan in log for p in plan.portions for t in p.tokens]
+    assert fed == prompt
+    assert [p.count for plan in log for p in plan.portions] == [5, 5, 5, 5, 3]
+    assert s.finish_reason == FinishReason.LENGTH
+
+
+def test_eos_is_neither_stored_nor_emitted():
+    sched, cache = make()
+    s = sched.add_request([1, 2, 3], GenerateOptions(max_new_tokens=10, eos_token_id=50))
+    run_step(sched, cache)
+    assert sched.append_token(s, 7) == 7
+    assert sched.append_token(s, 50) is None
+    assert s.finish_reason == FinishReason.STOP and s.generated_ids[-1] == 7
+    t = sched.add_request([1], GenerateOptions(max_new_tokens=2, eos_token_id=50, ignore_eos=True))
+    assert sched.append_token(t, 50) == 50 and not t.finished
+    assert sched.append_token(t, 50) == 50 and t.finish_reason == FinishReason.LENGTH
+
+
+def test_requests_that_can_never_run_are_refused():
+    sched, _ = make(num_blocks=4, block_size=4, max_len=64)
+    with pytest.raises(SchedulingError, match="pages"):
+        sched.add_request([1] * 10, GenerateOptions(max_new_tokens=8))
+    with pytest.raises(SchedulingError, match="longest"):
+        sched.add_request([1] * 60, GenerateOptions(max_new_tokens=8))
+    with pytest.raises(SchedulingError):
+        sched.add_request([], GenerateOptions())
+    sched.add_request([1] * 10, GenerateOptions(max_new_tokens=7))  # 16 cached at most: fits
+
+
+def test_admission_waits_for_pages_without_skipping():
+    sched, cache = make(num_blocks=6, block_size=4, budget=64, chunk=64)
+    a = sched.add_request([1] * 16, GenerateOptions(max_new_tokens=2))
+    big = sched.add_request([2] * 12, GenerateOptions(max_new_tokens=2))
+    small = sched.add_request([3] * 2, GenerateOptions(max_new_tokens=2))
+    plan = run_step(sched, cache)
+    # a takes 4 pages; big's 3 pages do not fit in 2; small is not let past big
+    assert [p.seq.id for p in plan.portions] == [a.id]
+    assert big.phase == Phase.WAITING and small.phase == Phase.WAITING
+    drain(sched, cache)
+    assert all(s.finish_reason == FinishReason.LENGTH for s in (a, big, small))
+
+
+def test_pages_run_out_the_youngest_is_preempted_and_output_is_unchanged():
+    prompts = [[i + 1] * 9 for i in range(3)]
+    want = [solo_tokens(p, 14) for p in prompts]
+    # 3 requests x (9 + 13) tokens = 18 pages of 4 wanted, the pool has 12
+    sched, cache = make(num_blocks=12, block_size=4, budget=64, chunk=64, max_batch=3)
+    seqs = [sched.add_request(p, GenerateOptions(max_new_tokens=14)) for p in prompts]
+    log = drain(sched, cache)
+    assert sched.num_preemptions > 0
+    victims = [v.id for plan in log for v in plan.preempted]
+    assert victims and victims[0] == 2  # the most recently admitted goes first
+    assert seqs[0].preemptions == 0  # the oldest is never a victim here
+    assert [s.generated_ids for s in seqs] == want
+    assert cache.free_pages() == [12] and cache.num_free_slots == 3
+    assert cache.groups[0].pool.reuses > 0
+    # a preempted request is recomputed from its tokens so far, in portions
+    recompute = [p for plan in log for p in plan.portions if p.seq.id == 2 and p.start == 0]
+    assert len(recompute) >= 2
+
+
+def test_preempted_request_returns_to_the_front():
+    sched, cache = make(num_blocks=6, block_size=4, budget=64, chunk=64, max_batch=2)
+    a = sched.add_request([1] * 8, GenerateOptions(max_new_tokens=12))
+    b = sched.add_request([2] * 8, GenerateOptions(max_new_tokens=12))
+    c = sched.add_request([3] * 4, GenerateOptions(max_new_tokens=2))
+    log = []
+    while not b.preemptions:
+        run_step(sched, cache, log)
+    assert sched.waiting[0] is b and sched.waiting[1] is c
+    assert b.cache is None and b.num_computed == 0 and b.phase == Phase.WAITING
+    drain(sched, cache)
+    assert len(a.generated_ids) == 12 and len(b.generated_ids) == 12 and len(c.generated_ids) == 2
+
+
+def test_cancel_frees_pages():
+    sched, cache = make()
+    a = sched.add_request([1] * 9, GenerateOptions(max_new_tokens=20))
+    b = sched.add_request([2] * 30, GenerateOptions(max_new_tokens=20))
+    run_step(sched, cache)
+    sched.cancel(b)  # mid-prefill
+    run_step(sched, cache)
+    assert b.cache is None and b.finish_reason == FinishReason.CANCELLED
+    sched.cancel(a)  # mid-decode
+    drain(sched, cache)
+    assert cache.free_pages() == [64] and cache.num_free_slots == 4
+    w = sched.add_request([3] * 3, GenerateOptions(max_new_tokens=2))
+    sched.cancel(w)  # while waiting
+    assert not sched.has_work() or drain(sched, cache) is not None
+    assert w.finish_reason == FinishReason.CANCELLED and w.generated_ids == []
+
+
+def test_many_requests_random_lengths_all_finish():
+    import random
+    rng = random.Random(5)
+    sched, cache = make(num_blocks=40, block_size=4, budget=24, chunk=10, max_batch=4)
+    reqs = []
+    for i in range(25):
+        p = [rng.randrange(3, 90) for _ in range(rng.randint(1, 40))]
+        reqs.append((p, rng.randint(1, 30)))
+    seqs = [sched.add_request(p, GenerateOptions(max_new_tokens=n)) for p, n in reqs]
+    log = drain(sched, cache)
+    for plan in log:
+        assert plan.num_tokens <= 24
+        assert len({p.seq.id for p in plan.portions}) == len(plan.portions)
+    for s, (p, n) in zip(seqs, reqs):
+        assert s.generated_ids == solo_tokens(p, n)
+    assert cache.free_pages() == [40]
