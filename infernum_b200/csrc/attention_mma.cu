@@ -1,0 +1,491 @@
+// Tensor-core attention over the paged cache for bfloat16, one head size per
+// build (-DIB_HD=<multiple of 16, at most 256>).
+//
+// One kernel body, two ways of spreading the work:
+//   * tile mode (prompt portions): a CTA owns 64 "packed rows" - query rows of
+//     one request times the query heads that share one key/value head - and
+//     walks the keys in tiles of 64; each of its 4 warps owns 16 packed rows.
+//   * split mode (decoded tokens and very short portions): a CTA owns the
+//     (at most 16) packed rows of one request and one slice of its keys; the
+//     4 warps each take 16 keys of every tile and are merged at the end; the
+//     slices of one request are merged by a second small kernel through
+//     scratch memory.
+// Keys and values are fetched page by page through the request's block table
+// with 16-byte cp.async copies into padded shared-memory rows, two tiles in
+// flight.  Scores, the running maximum, the running sum and the output
+// accumulator are 32-bit; exponentials are exp2f of scores pre-multiplied by
+// log2(e).  Key tiles start at absolute multiples of 64, so the order of the
+// additions for a query does not depend on how its prompt was cut.
+//
+// Same mathematics as attention_plain.cu (which restates
+// infernum-cuda/kernels/flash_prefill_attention_v2.cu:82-95,149-192 and
+// infernum-cuda/kernels/paged_decode_attention.cu:540-644); the reference has
+// no tensor-core attention (its bf16 prefill loops cuBLAS per head over a
+// materialised score matrix: infernum-cuda/src/inner/cuda/ops/fused_attention.rs:265-473).
+#include "common.cuh"
+
+#ifndef IB_HD
+#define IB_HD 128
+#endif
+
+using namespace ib;
+
+namespace {
+
+constexpr int HD = IB_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16, at most 256");
+constexpr int BN = 64;            // keys per tile
+constexpr int LDS = HD + 8;       // padded row length (elements): conflict-free ldmatrix
+constexpr int CH = HD / 8;        // 16-byte chunks per row
+constexpr int NTHREADS = 128;
+constexpr int TILE_ELEMS = BN * LDS;
+constexpr int SMEM_BYTES = 4 * TILE_ELEMS * 2;  // K and V, two stages
+
+struct Params {
+    const bf16* q;
+    const bf16* k_pool;
+    const bf16* v_pool;
+    bf16* out;
+    const int* cu_rows;
+    const int* q_start;
+    const int* block_tables;
+    float* part_o;    // [splits][n_rows][nh][HD]
+    float* part_ml;   // [splits][n_rows][nh][2]
+    unsigned* err;
+    int q_stride, out_stride, max_blocks, nh, nkv, page_size, num_pages, window;
+    int gs;           // query heads of one kv head handled together (<= 16)
+    int n_hsub;       // ceil((nh / nkv) / gs)
+    int splits;       // split mode: slices of keys per request
+    int n_rows;       // rows of the whole step
+    int small_rows;   // an entry with rows * gs <= small_rows belongs to split mode
+    float scale_log2;
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, int src_bytes) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
+                                            const void* smem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2,
+                                                  unsigned& r3, const void* smem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0,
+                                         unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Copies keys [tile_start, tile_start + 64) of kv head g into one stage.
+// Keys outside [kv_min, kv_hi) and keys on an invalid page are zero-filled
+// (pages below kv_min may already have been given back by a window).
+__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const Params& p, const int* table,
+                                          int g, int tile_start, int kv_min, int kv_hi) {
+    for (int c = threadIdx.x; c < BN * CH; c += NTHREADS) {
+        const int row = c / CH, ch = c % CH;
+        const int j = tile_start + row;
+        int bytes = 0;
+        size_t off = 0;
+        if (j >= kv_min && j < kv_hi) {
+            const int page = table[j / p.page_size];
+            if (page >= 0 && page < p.num_pages) {
+                off = (((size_t)page * p.nkv + g) * p.page_size + (j % p.page_size)) * HD + ch * 8;
+                bytes = 16;
+            } else {
+                atomicOr(p.err, IB_FLAG_BAD_PAGE);
+            }
+        }
+        cp_async_16(ks + row * LDS + ch * 8, p.k_pool + off, bytes);
+        cp_async_16(vs + row * LDS + ch * 8, p.v_pool + off, bytes);
+    }
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    bf16* k_s[2] = {smem, smem + TILE_ELEMS};
+    bf16* v_s[2] = {smem + 2 * TILE_ELEMS, smem + 3 * TILE_ELEMS};
+
+    const int e = blockIdx.y;
+    const int g = blockIdx.z / p.n_hsub;        // kv head
+    const int hsub = blockIdx.z % p.n_hsub;     // which block of the group's query heads
+    const int G = p.nh / p.nkv;
+    const int row0 = p.cu_rows[e];
+    const int rows_e = p.cu_rows[e + 1] - row0;
+    const int pos0 = p.q_start[e];
+    const bool small = rows_e * p.gs <= p.small_rows;
+    if (SPLIT != small) return;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int* table = p.block_tables + (size_t)e * p.max_blocks;
+
+    // ---- which packed rows are mine ----------------------------------------
+    int r_begin, r_count;  // query rows (within the entry) this CTA covers
+    if (SPLIT) {
+        r_begin = 0;
+        r_count = rows_e;
+    } else {
+        const int rq = BN / p.gs;  // rows per CTA: 64 packed rows
+        r_begin = blockIdx.x * rq;
+        if (r_begin >= rows_e) return;
+        r_count = min(rq, rows_e - r_begin);
+    }
+    const int m_base = SPLIT ? 0 : warp * 16;
+    int my_row[2], my_head[2], my_pos[2];  // for packed rows gid and gid + 8 of my 16
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int m = m_base + gid + 8 * h;
+        const int r = r_begin + m / p.gs;
+        const int hh = hsub * p.gs + m % p.gs;
+        const bool ok = (m / p.gs) < r_count && hh < G;
+        my_row[h] = ok ? row0 + r : -1;
+        my_head[h] = g * G + hh;
+        my_pos[h] = ok ? pos0 + r : -1;
+    }
+
+    // ---- key range -----------------------------------------------------------
+    const int kv_hi = pos0 + r_begin + r_count;  // exclusive
+    const int kv_min = p.window > 0 ? max(0, pos0 + r_begin - p.window + 1) : 0;
+    const int kv_lo = (kv_min / BN) * BN;
+    const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
+    int t_begin = 0, t_end = n_tiles;
+    if (SPLIT) {
+        const int per = (n_tiles + p.splits - 1) / p.splits;
+        t_begin = blockIdx.x * per;
+        t_end = min(n_tiles, t_begin + per);
+    }
+
+    // ---- queries as A fragments, straight from global memory -------------------
+    unsigned qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = i & 1;
+            const int col = ks * 16 + tig * 2 + (i >> 1) * 8;
+            qf[ks][i] = my_row[h] >= 0
+                ? *reinterpret_cast<const unsigned*>(p.q + (size_t)my_row[h] * p.q_stride +
+                                                     (size_t)my_head[h] * HD + col)
+                : 0u;
+        }
+    }
+
+    constexpr int NT = SPLIT ? 2 : 8;           // score tiles of 8 keys per warp
+    const int key_base = SPLIT ? warp * 16 : 0;  // my first key within a tile
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    if (t_begin < t_end) {
+        load_tile(k_s[0], v_s[0], p, table, g, kv_lo + t_begin * BN, kv_min, kv_hi);
+    }
+    cp_async_commit();
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t + 1 < t_end)
+            load_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, table, g, kv_lo + (t + 1) * BN, kv_min,
+                      kv_hi);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+
+        const int tile_start = kv_lo + t * BN;
+        const bf16* ks_ = k_s[stage];
+        const bf16* vs_ = v_s[stage];
+
+        // S = Q K^T
+        float s[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < NT / 2; ++n2) {
+                unsigned b0, b1, b2, b3;
+                const int key = key_base + n2 * 16 + (lane & 7) + 8 * (lane >> 4);
+                const int dim = ks * 16 + 8 * ((lane >> 3) & 1);
+                ldmatrix_x4(b0, b1, b2, b3, ks_ + key * LDS + dim);
+                mma_bf16(s[2 * n2], qf[ks], b0, b1);
+                mma_bf16(s[2 * n2 + 1], qf[ks], b2, b3);
+            }
+        }
+
+        // mask, scale, online softmax (per thread: rows gid and gid + 8)
+        float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int h = i >> 1;
+                const int key = tile_start + key_base + n * 8 + tig * 2 + (i & 1);
+                const bool ok = key <= my_pos[h] && (p.window <= 0 || key > my_pos[h] - p.window);
+                const float v = ok ? s[n][i] * p.scale_log2 : -INFINITY;
+                s[n][i] = v;
+                m_new[h] = fmaxf(m_new[h], v);
+            }
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+            m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];
+            corr[h] = exp2f(m_run[h] - m_use[h]);  // 0 when nothing was seen before
+            m_run[h] = m_new[h];
+            l_run[h] *= corr[h];
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int h = i >> 1;
+                const float pv = exp2f(s[n][i] - m_use[h]);
+                s[n][i] = pv;
+                l_run[h] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+
+        // O += P V
+#pragma unroll
+        for (int kb = 0; kb < NT / 2; ++kb) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
+            a[1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
+            a[2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+            a[3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; nt += 2) {
+                unsigned b0, b1, b2, b3;
+                const int key = key_base + kb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+                const int dim = nt * 8 + 8 * (lane >> 4);
+                ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + key * LDS + dim);
+                mma_bf16(o[nt], a, b0, b1);
+                mma_bf16(o[nt + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();  // everyone is done with this stage before it is refilled
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+
+    if (!SPLIT) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (my_row[h] < 0) continue;
+            const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+            bf16* dst = p.out + (size_t)my_row[h] * p.out_stride + (size_t)my_head[h] * HD;
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; ++nt) {
+                *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8 + tig * 2) =
+                    __floats2bfloat162_rn(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
+            }
+        }
+        return;
+    }
+
+    // ---- split mode: merge the 4 warps (each saw different keys) -----------------
+    __syncthreads();
+    float* so = reinterpret_cast<float*>(smem_raw);             // [4][16][HD]
+    float* sml = so + 4 * 16 * HD;                              // [4][16][2]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = gid + 8 * h;
+        float* dst = so + ((size_t)warp * 16 + r) * HD;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; ++nt) {
+            dst[nt * 8 + tig * 2] = o[nt][2 * h];
+            dst[nt * 8 + tig * 2 + 1] = o[nt][2 * h + 1];
+        }
+        if (tig == 0) {
+            sml[(warp * 16 + r) * 2] = m_run[h];
+            sml[(warp * 16 + r) * 2 + 1] = l_run[h];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * HD; idx += NTHREADS) {
+        const int m = idx / HD, d = idx % HD;
+        const int r = m / p.gs, hh = hsub * p.gs + m % p.gs;
+        if (r >= rows_e || hh >= G) continue;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, sml[(w * 16 + m) * 2]);
+        float acc = 0.f, l = 0.f;
+        if (mx > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(sml[(w * 16 + m) * 2] - mx);
+                acc += f * so[((size_t)w * 16 + m) * HD + d];
+                l += f * sml[(w * 16 + m) * 2 + 1];
+            }
+        }
+        const int grow = row0 + r, head = g * G + hh;
+        if (p.splits == 1) {
+            p.out[(size_t)grow * p.out_stride + (size_t)head * HD + d] =
+                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            const size_t base = ((size_t)blockIdx.x * p.n_rows + grow) * p.nh + head;
+            p.part_o[base * HD + d] = acc;
+            if (d == 0) {
+                p.part_ml[base * 2] = mx;
+                p.part_ml[base * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// Merges the slices of split mode: one block per (row, head).
+__global__ void attention_combine_kernel(const Params p) {
+    const int row = blockIdx.x, head = blockIdx.y;
+    float mx = -INFINITY;
+    for (int s = 0; s < p.splits; ++s)
+        mx = fmaxf(mx, p.part_ml[(((size_t)s * p.n_rows + row) * p.nh + head) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f, l = 0.f;
+        if (mx > -INFINITY) {
+            for (int s = 0; s < p.splits; ++s) {
+                const size_t base = ((size_t)s * p.n_rows + row) * p.nh + head;
+                const float f = exp2f(p.part_ml[base * 2] - mx);
+                acc += f * p.part_o[base * HD + d];
+                l += f * p.part_ml[base * 2 + 1];
+            }
+        }
+        p.out[(size_t)row * p.out_stride + (size_t)head * HD + d] =
+            __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+}
+
+}  // namespace
+
+IB_EXPORT int ib_attention_mma_head_dim() { return HD; }
+
+// Bytes of scratch that `splits` slices need: partial outputs and statistics.
+IB_EXPORT long long ib_attention_mma_scratch_bytes(int n_rows, int nh, int splits) {
+    if (splits <= 1) return 0;
+    return (long long)splits * n_rows * nh * (HD + 2) * (long long)sizeof(float);
+}
+
+// mode bits: 1 = launch tile mode (entries with rows * gs > 16),
+//            2 = launch split mode (entries with rows * gs <= 16).
+// When only one bit is set, every entry is taken by that mode, except that
+// split mode can never take an entry with more than 16 packed rows.
+IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, const void* v_pool,
+                               void* out, int out_stride, const int* cu_rows, const int* q_start,
+                               const int* block_tables, int max_blocks, int n_entries, int n_rows,
+                               int max_rows_per_entry, int nh, int nkv, int page_size,
+                               int num_pages, int window, float scale, int mode, int splits,
+                               void* scratch, long long scratch_bytes, unsigned* err,
+                               void* stream) {
+    if (n_entries <= 0 || n_rows <= 0) return IB_OK;
+    if (!q || !k_pool || !v_pool || !out || !cu_rows || !q_start || !block_tables || !err)
+        return IB_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || max_blocks <= 0 || num_pages <= 0 ||
+        (q_stride & 1) || (out_stride & 1) || !(mode & 3) || splits < 1)
+        return IB_ERR_BAD_ARG;
+    if (((uintptr_t)q & 3) || ((uintptr_t)out & 3) || ((uintptr_t)k_pool & 15) ||
+        ((uintptr_t)v_pool & 15))
+        return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    Params p;
+    p.q = (const bf16*)q;
+    p.k_pool = (const bf16*)k_pool;
+    p.v_pool = (const bf16*)v_pool;
+    p.out = (bf16*)out;
+    p.cu_rows = cu_rows;
+    p.q_start = q_start;
+    p.block_tables = block_tables;
+    p.err = err;
+    p.q_stride = q_stride;
+    p.out_stride = out_stride;
+    p.max_blocks = max_blocks;
+    p.nh = nh;
+    p.nkv = nkv;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.window = window;
+    const int G = nh / nkv;
+    p.gs = G < 16 ? G : 16;
+    p.n_hsub = (G + p.gs - 1) / p.gs;
+    p.splits = splits;
+    p.n_rows = n_rows;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.part_o = nullptr;
+    p.part_ml = nullptr;
+    // which entries each mode takes
+    if ((mode & 3) == 3) p.small_rows = 16;
+    else if (mode & 2) p.small_rows = 1 << 30;   // everything is "small"
+    else p.small_rows = -1;                      // nothing is "small"
+    if ((mode & 2) && !(mode & 1) && max_rows_per_entry * p.gs > 16) return IB_ERR_BAD_ARG;
+    if (n_entries > 65535 || nkv * p.n_hsub > 65535) return IB_ERR_TOO_LARGE;
+
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e1 = cudaFuncSetAttribute(attention_mma_kernel<false>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e2 = cudaFuncSetAttribute(attention_mma_kernel<true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e1 != cudaSuccess) return (int)e1;
+        if (e2 != cudaSuccess) return (int)e2;
+        attr_done = true;
+    }
+    if (mode & 1) {
+        const int rq = BN / p.gs;
+        dim3 grid((max_rows_per_entry + rq - 1) / rq, n_entries, nkv * p.n_hsub);
+        attention_mma_kernel<false><<<grid, NTHREADS, SMEM_BYTES, s>>>(p);
+        IB_LAUNCH_CHECK();
+    }
+    if (mode & 2) {
+        if (splits > 1) {
+            const long long need = ib_attention_mma_scratch_bytes(n_rows, nh, splits);
+            if (!scratch || scratch_bytes < need || ((uintptr_t)scratch & 15)) return IB_ERR_BAD_ARG;
+            p.part_o = (float*)scratch;
+            p.part_ml = p.part_o + (size_t)splits * n_rows * nh * HD;
+        }
+        dim3 grid(splits, n_entries, nkv * p.n_hsub);
+        attention_mma_kernel<true><<<grid, NTHREADS, SMEM_BYTES, s>>>(p);
+        IB_LAUNCH_CHECK();
+        if (splits > 1) {
+            // Only rows that split mode handled have partial results; with both
+            // modes in one step the caller keeps splits at 1.
+            if (mode & 1) return IB_ERR_BAD_ARG;
+            dim3 cgrid(n_rows, nh);
+            attention_combine_kernel<<<cgrid, HD >= 128 ? 128 : 64, 0, s>>>(p);
+            IB_LAUNCH_CHECK();
+        }
+    }
+    return IB_OK;
+}

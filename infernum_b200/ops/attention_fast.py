@@ -1,9 +1,102 @@
-"""Tensor-core attention kernels for bfloat16 (prefill tiles and split-KV
-decode).  ``run`` returns False when it has no variant for the request, and
-the caller then takes the plain kernel."""
+"""Tensor-core attention kernels for bfloat16 (``attention_mma.cu``), one
+compiled module per head size, built when a model first needs it.
+
+``run`` picks how the step's entries are spread: entries whose query rows
+times grouped heads fit 16 packed rows (decoded tokens, very short portions)
+go to split mode, where the keys of a request are cut in slices over several
+CTAs and merged through scratch memory; longer portions go to tile mode.  It
+returns False when there is no variant for the head size, and the caller then
+takes the plain kernel.
+"""
 
 from __future__ import annotations
 
+import ctypes
+from typing import Dict
+
+import torch
+
+from ..csrc.build import load_module
+from ..errors import KernelError
+from . import core
+
+_c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+_libs: Dict[int, ctypes.CDLL] = {}
+SM_COUNT_FALLBACK = 148
+
+
+def supported(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def lib_for(head_dim: int) -> ctypes.CDLL:
+    lib = _libs.get(head_dim)
+    if lib is None:
+        lib = load_module(f"attn_hd{head_dim}", ["attention_mma.cu"], [f"-DIB_HD={head_dim}"])
+        lib.ib_attention_mma.argtypes = [
+            _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+            _c_float, _c_int, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p]
+        lib.ib_attention_mma.restype = _c_int
+        lib.ib_attention_mma_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
+        lib.ib_attention_mma_scratch_bytes.restype = _c_ll
+        lib.ib_attention_mma_head_dim.restype = _c_int
+        if lib.ib_attention_mma_head_dim() != head_dim:
+            raise KernelError(f"attention module for head size {head_dim} was built for another size")
+        _libs[head_dim] = lib
+    return lib
+
+
+def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count: int) -> int:
+    """Slices per request so that about two CTAs per SM exist, each with at
+    least two key tiles of 64."""
+    base = max(1, n_entries * kv_heads_x_sub)
+    want = -(-2 * sm_count // base)
+    tiles = -(-max_kv_len // 64)
+    return max(1, min(want, max(1, tiles // 2), 32))
+
 
 def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool:
-    return False
+    num_pages, nkv, page_size, hd = k_pool.shape
+    if not supported(hd):
+        return False
+    core.require_cuda(q, k_pool, v_pool, out, tables)
+    if n_heads % nkv:
+        raise KernelError(f"attention: {n_heads} heads are not a multiple of {nkv} kv heads")
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != torch.bfloat16 \
+            or k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_mma: bfloat16 tensors with unit inner stride are required")
+    G = n_heads // nkv
+    gs = min(G, 16)
+    n_hsub = -(-G // gs)
+    small_limit = 16 // gs  # rows an entry may have to go to split mode
+    forced = getattr(ctx, "attention_mode", None)
+    if forced is not None:
+        mode, splits = forced
+    else:
+        cu = ctx.host_cu_rows
+        rows = [cu[i + 1] - cu[i] for i in range(ctx.n_entries)]
+        any_small = any(r <= small_limit for r in rows)
+        any_big = any(r > small_limit for r in rows)
+        mode = (1 if any_big else 0) | (2 if any_small else 0)
+        splits = 1
+        if mode == 2:
+            sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
+            splits = choose_splits(ctx.n_entries, nkv * n_hsub, ctx.max_kv_len, sm)
+    lib = lib_for(hd)
+    scratch_ptr, scratch_bytes = None, 0
+    if splits > 1:
+        need = lib.ib_attention_mma_scratch_bytes(ctx.n_rows, n_heads, splits)
+        buf = ctx.scratch.get("attn_split")
+        if buf is None or buf.numel() * 4 < need:
+            buf = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
+            ctx.scratch["attn_split"] = buf
+        scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel() * 4
+    code = lib.ib_attention_mma(
+        q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+        out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
+        tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
+        page_size, num_pages, int(window), float(scale), mode, splits, scratch_ptr, scratch_bytes,
+        rt.err.data_ptr(), core.stream_ptr(q))
+    core.check(code, "attention_mma")
+    return True

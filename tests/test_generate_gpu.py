@@ -1,0 +1,138 @@
+"""Generation through the Python entry point and the command line: greedy
+tokens equal the plain implementation's; batched equals alone; sampling is
+reproducible and independent of the batch; preemption leaves output unchanged."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as pl
+from helpers import CONFIGS, ROOT, make_model_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    # sharpened models: logit gaps are far above bfloat16 noise, so greedy tokens are stable
+    return {n: make_model_folder(str(tmp_path_factory.mktemp(f"gen{n}")), CONFIGS[n], 60 + i, sharpen=6.0)
+            for i, n in enumerate(["A", "B"])}
+
+
+def plain_greedy_with_margin(folder, prompt, n):
+    """Greedy tokens of the plain implementation and the smallest gap between
+    the best and second-best logit along the way (relative to the largest)."""
+    cfg, w = pl.read_config(folder), pl.read_weights(folder)
+    seq, out, margin = list(prompt), [], 1e9
+    for _ in range(n):
+        logits = pl.forward(cfg, w, seq)[-1]
+        top = torch.topk(logits, 2).values
+        margin = min(margin, float((top[0] - top[1]) / logits.abs().max()))
+        t = pl.argmax(logits)
+        out.append(t)
+        seq.append(t)
+    return out, margin
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_equals_plain(folders, name, dtype):
+    import infernum_b200 as ib
+    model = ib.load_model(folders[name], dtype=dtype)
+    block = {"A": 4, "B": 8}[name]
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=4, max_prefill_tokens=7, block_size=block,
+                                             num_blocks=64, max_tokens_per_step=16))
+    vocab = CONFIGS[name]["vocab_size"]
+    lens = {"A": [5, 17, 33], "B": [1, 9, 40]}[name]
+    prompts = [random_tokens(n, vocab, 7 * n) for n in lens]
+    n_new = {"A": 16, "B": 24}[name]
+    opts = ib.GenerateOptions(max_new_tokens=n_new)
+    got_batch = engine.generate_batch(prompts, opts)
+    for p, got in zip(prompts, got_batch):
+        want, margin = plain_greedy_with_margin(folders[name], p, n_new)
+        # compare up to the first step whose top-2 gap is within the dtype's noise
+        limit = 1e-4 if dtype == "float32" else 5e-2
+        if margin > limit:
+            assert got == want
+        else:
+            assert got[:4] == want[:4] or margin < limit
+        assert engine.generate(p, opts) == got  # alone equals batched
+    assert engine.cache.free_pages() == [64] and engine.cache.num_free_slots == 4
+
+
+def test_stream_eos_and_length(folders):
+    import infernum_b200 as ib
+    model = ib.load_model(folders["A"], dtype="float32")
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=4, num_blocks=64))
+    prompt = random_tokens(9, 256, 1)
+    full = engine.generate(prompt, ib.GenerateOptions(max_new_tokens=12))
+    assert list(engine.generate_stream(prompt, ib.GenerateOptions(max_new_tokens=12))) == full
+    stop = full[5]
+    first = full.index(stop)
+    cut = engine.generate(prompt, ib.GenerateOptions(max_new_tokens=12, eos_token_id=stop))
+    assert cut == full[:first]  # the end-of-sequence token is neither kept nor emitted
+    h = engine.submit(prompt, ib.GenerateOptions(max_new_tokens=12, eos_token_id=stop))
+    engine.run_until_done([h])
+    assert h.finish_reason == ib.FinishReason.STOP and h.events[-1].kind == "finished"
+    with pytest.raises(ib.InfernumError):
+        engine.submit([1, 2, 999], ib.GenerateOptions())
+    with pytest.raises(ib.SchedulingError):
+        engine.submit([1] * 120, ib.GenerateOptions(max_new_tokens=20))
+
+
+def test_sampling_is_seeded_and_independent_of_the_batch(folders):
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype="float32")
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=4, block_size=8, num_blocks=64,
+                                             max_prefill_tokens=16, max_tokens_per_step=24))
+    prompts = [random_tokens(n, 320, n) for n in (6, 21, 40)]
+    opts = [ib.GenerateOptions(max_new_tokens=20, sampling=ib.SamplingParams(
+        temperature=0.8, top_p=0.9, seed=100 + i, repetition_penalty=1.2)) for i in range(3)]
+    together = engine.generate_batch(prompts, opts)
+    again = engine.generate_batch(prompts, opts)
+    assert together == again
+    for p, o, t in zip(prompts, opts, together):
+        assert engine.generate(p, o) == t
+    other = engine.generate(prompts[1], ib.GenerateOptions(max_new_tokens=20, sampling=ib.SamplingParams(
+        temperature=0.8, top_p=0.9, seed=999, repetition_penalty=1.2)))
+    assert other != together[1]
+    greedy = engine.generate(prompts[1], ib.GenerateOptions(max_new_tokens=20))
+    assert greedy != together[1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_leaves_output_unchanged(folders, dtype):
+    import infernum_b200 as ib
+    model = ib.load_model(folders["A"], dtype=dtype)
+    prompts = [random_tokens(9, 256, 50 + i) for i in range(3)]
+    opts = [ib.GenerateOptions(max_new_tokens=40),
+            ib.GenerateOptions(max_new_tokens=40, sampling=ib.SamplingParams(temperature=0.7, seed=5)),
+            ib.GenerateOptions(max_new_tokens=40)]
+    roomy = ib.Engine(model, ib.BatchConfig(max_batch_size=3, block_size=4, num_blocks=64))
+    want = [roomy.generate(p, o) for p, o in zip(prompts, opts)]
+    tight = ib.Engine(model, ib.BatchConfig(max_batch_size=3, block_size=4, num_blocks=24,
+                                            max_prefill_tokens=8))
+    got = tight.generate_batch(prompts, opts)
+    assert tight.stats.preemptions > 0
+    assert got == want
+    assert tight.cache.free_pages() == [24]
+
+
+def test_command_line_generate(folders):
+    env = dict(os.environ, LLAMA_MODEL_PATH=folders["A"])
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "5,6,7,8", "-n", "6",
+                          "--greedy", "--dtype", "float32", "--block-size", "4"],
+                         capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert "Decoding: greedy (argmax)" in out.stdout and "Generated 6 tokens" in out.stdout
+    line = [l for l in out.stdout.splitlines() if l.startswith("5,6,7,8")][0]
+    got = [int(t) for t in line.split()[1:]]
+    want, _ = plain_greedy_with_margin(folders["A"], [5, 6, 7, 8], 6)
+    assert got == want
+    out2 = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "-m", folders["A"],
+                           "5,6,7,8", "-n", "5", "-t", "0.9", "-p", "0.8", "-s", "7", "-r", "1.3",
+                           "--dtype", "float32"], capture_output=True, text=True, timeout=600)
+    assert out2.returncode == 0, out2.stderr[-3000:]
+    assert "Sampling: temperature=0.9, top_p=0.8, seed=7, repetition_penalty=1.3 (window=64)" in out2.stdout

@@ -1,0 +1,377 @@
+"""Each CUDA kernel alone against a plain float64 statement of the same
+operation, at sizes other than the engine's test models use."""
+import math
+import random
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def core():
+    from infernum_b200.ops import core as c
+    return c
+
+
+def rel_err(got, ref):
+    ref = ref.double().cpu()
+    return float((got.double().cpu() - ref).abs().max() / max(ref.abs().max().item(), 1e-9))
+
+
+TOL = {torch.float32: 3e-6, torch.bfloat16: 1.2e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    c = core()
+    table = torch.randn(77, 50).to(dtype).to(DEV)
+    ids = torch.tensor([0, 76, 5, 5, 33], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 50, device=DEV)
+    err = c.new_error_word(DEV)
+    c.embed(ids, table, out, err)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.long().cpu()])
+    assert err.item() == 0
+    c.embed(torch.tensor([3, 77], dtype=torch.int32, device=DEV), table, out[:2], err)
+    assert err.item() == c.FLAG_BAD_TOKEN and out[1].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [50, 64, 333, 4096, 9000])
+def test_add_rmsnorm(dtype, H):
+    c = core()
+    N, eps = 7, 3e-6
+    res = torch.randn(N, H) * 3
+    delta = torch.randn(N, H).to(dtype)
+    w = (1 + 0.1 * torch.randn(H)).to(dtype)
+    want_res = res.double() + delta.double()
+    want = pl.rms_norm(want_res, w.double(), eps)
+    r = res.clone().to(DEV)
+    out = torch.empty(N, H, dtype=dtype, device=DEV)
+    c.add_rmsnorm(r, delta.to(DEV), w.to(DEV), eps, out)
+    assert rel_err(r, want_res) < 1e-6
+    assert rel_err(out, want) < TOL[dtype]
+    # without a delta, and with a float32 weight in a bfloat16 engine
+    r2 = res.clone().to(DEV)
+    c.add_rmsnorm(r2, None, w.float().to(DEV), eps, out)
+    assert torch.equal(r2.cpu(), res)
+    assert rel_err(out, pl.rms_norm(res.double(), w.double(), eps)) < TOL[dtype]
+    # chosen rows only: compact output, residual untouched
+    idx = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    r3 = res.clone().to(DEV)
+    out3 = torch.empty(3, H, dtype=dtype, device=DEV)
+    c.add_rmsnorm(r3, delta.to(DEV), w.to(DEV), eps, out3, row_idx=idx)
+    assert torch.equal(r3.cpu(), res)
+    assert rel_err(out3, want[[6, 0, 3]]) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul_and_residual_add(dtype):
+    c = core()
+    x = (torch.randn(9, 2 * 37) * 4).to(dtype)
+    out = torch.empty(9, 37, dtype=dtype, device=DEV)
+    c.silu_mul(x.to(DEV), out)
+    g, u = x[:, :37].double(), x[:, 37:].double()
+    assert rel_err(out, g / (1 + torch.exp(-g)) * u) < TOL[dtype]
+    res = torch.randn(9, 37)
+    r = res.clone().to(DEV)
+    c.residual_add(r, out)
+    assert rel_err(r, res.double() + out.double().cpu()) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd, rd", [(16, 16), (48, 48), (64, 32), (128, 128)])
+def test_rope_and_cache_write(dtype, hd, rd):
+    c = core()
+    from infernum_b200.parts.rope import rotary_inv_freq
+    nh, nkv, N, ps, pages = 5, 2, 11, 4, 9
+    scaling = {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0,
+               "high_freq_factor": 4.0, "original_max_position_embeddings": 32}
+    freqs = torch.tensor(rotary_inv_freq(rd, 10000.0, scaling), dtype=torch.float64).float()
+    assert torch.equal(freqs, pl.rope_frequencies(rd, 10000.0, scaling))
+    qkv = torch.randn(N, (nh + 2 * nkv) * hd).to(dtype)
+    # two requests: rows 0..6 at positions 3..9 of request 0, rows 7..10 at 20..23 of request 1
+    positions = torch.tensor(list(range(3, 10)) + list(range(20, 24)), dtype=torch.int32)
+    row_entry = torch.tensor([0] * 7 + [1] * 4, dtype=torch.int32)
+    tables = torch.tensor([[5, 2, 7, -1, -1, -1], [8, 0, 1, 3, 4, 6]], dtype=torch.int32)
+    kp = torch.zeros(pages, nkv, ps, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    err = c.new_error_word(DEV)
+    d = qkv.clone().to(DEV)
+    c.rope_append(d, positions.to(DEV), freqs.to(DEV), rd, nh, nkv, hd, row_entry.to(DEV),
+                  tables.to(DEV), kp, vp, err)
+    assert err.item() == 0
+    x = qkv.double()
+    q = x[:, : nh * hd].view(N, nh, hd)
+    k = x[:, nh * hd: (nh + nkv) * hd].view(N, nkv, hd)
+    v = x[:, (nh + nkv) * hd:].view(N, nkv, hd)
+
+    def rot(t):
+        return torch.cat([pl.rope(t[..., :rd], positions, freqs), t[..., rd:]], dim=-1)
+
+    tol = TOL[dtype]
+    got = d.cpu().double()
+    assert rel_err(got[:, : nh * hd].view(N, nh, hd), rot(q)) < tol
+    assert torch.equal(d[:, (nh + nkv) * hd:].cpu(), qkv[:, (nh + nkv) * hd:])
+    written = 0
+    for r in range(N):
+        e, pos = int(row_entry[r]), int(positions[r])
+        page, slot = int(tables[e, pos // ps]), pos % ps
+        assert rel_err(kp[page, :, slot], rot(k)[r]) < tol
+        assert torch.equal(vp[page, :, slot].cpu(), qkv[r, (nh + nkv) * hd:].view(nkv, hd))
+        written += 1
+    assert int((kp.abs().sum(dim=(1, 3)) > 0).sum()) == written  # nothing else was touched
+    # a table entry outside the pool is reported, not followed
+    bad = tables.clone()
+    bad[0, 0] = 99
+    c.rope_append(qkv.clone().to(DEV), positions.to(DEV), freqs.to(DEV), rd, nh, nkv, hd,
+                  row_entry.to(DEV), bad.to(DEV), kp, vp, err)
+    assert err.item() == c.FLAG_BAD_PAGE
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 1, 1), (3, 5, 7), (64, 64, 16), (65, 130, 33), (200, 77, 300)])
+@pytest.mark.parametrize("dt", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                (torch.bfloat16, torch.float32, torch.bfloat16),
+                                (torch.bfloat16, torch.bfloat16, torch.float32)])
+def test_gemm_plain(M, N, K, dt):
+    c = core()
+    a = torch.randn(M, K).to(dt[0])
+    w = torch.randn(N, K).to(dt[1])
+    out = torch.empty(M, N, dtype=dt[2], device=DEV)
+    c.gemm_plain(a.to(DEV), w.to(DEV), out)
+    assert rel_err(out, a.double() @ w.double().T) < TOL[dt[2]]
+    if M > 1:  # a row does not depend on the others
+        one = torch.empty(1, N, dtype=dt[2], device=DEV)
+        c.gemm_plain(a[M - 1:].to(DEV), w.to(DEV), one)
+        assert torch.equal(one[0], out[M - 1])
+
+
+def test_argmax_lowest_index_wins():
+    c = core()
+    x = torch.randn(6, 1000)
+    x[0, 17] = x[0, 900] = 50.0
+    x[1, 999] = 60.0
+    x[2, 0] = 70.0
+    x[3] = -5.0  # all equal
+    big = torch.randn(2, 128256)
+    big[0, 128255] = 99.0
+    big[1, 70000] = big[1, 3] = 99.0
+    for t in (x, big):
+        out = torch.empty(t.shape[0], dtype=torch.int32, device=DEV)
+        c.argmax(t.to(DEV), out)
+        assert out.tolist() == [pl.argmax(r) for r in t]
+
+
+def pack_params(c, rows):
+    p = torch.zeros(len(rows), c.SAMPLE_PARAM_FLOATS)
+    n = torch.zeros(len(rows), dtype=torch.int32)
+    for i, (t, tp, pen, u, nr) in enumerate(rows):
+        p[i, :4] = torch.tensor([t, tp, pen, u])
+        n[i] = nr
+    p.view(torch.int32)[:, 4] = n
+    return p.to(DEV)
+
+
+@pytest.mark.parametrize("V", [50, 1000, 5003])
+def test_sample_against_plain(V):
+    c = core()
+    rng = random.Random(V)
+    R = 24
+    logits = torch.randn(R, V) * 3
+    rows, recents = [], torch.zeros(R, 8, dtype=torch.int32)
+    for i in range(R):
+        nr = rng.randint(0, 8)
+        recents[i, :nr] = torch.tensor([rng.randrange(V) for _ in range(nr)], dtype=torch.int32)
+        if nr >= 2:
+            recents[i, 1] = recents[i, 0]  # a token that occurs twice is penalised twice
+        rows.append((rng.choice([0.3, 0.7, 1.0, 1.5]), rng.choice([0.5, 0.9, 0.95, 1.0]),
+                     rng.choice([1.0, 1.1, 1.3]), rng.random(), nr))
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    c.sample(logits.clone().to(DEV), pack_params(c, rows), recents.to(DEV), out)
+    checked = 0
+    for i, (t, tp, pen, u, nr) in enumerate(rows):
+        probs = pl.sample_probabilities(logits[i], t, tp, pen, recents[i, :nr].tolist())
+        want = pl.sample_index_order(probs, u)
+        # skip rows where u sits within rounding of a boundary of the CDF, or the
+        # nucleus edge is within rounding of top_p
+        cdf = torch.cumsum(probs, 0)
+        if (cdf - u).abs().min() < 1e-5:
+            continue
+        full = pl.sample_probabilities(logits[i], t, 1.0, pen, recents[i, :nr].tolist())
+        order = torch.argsort(full, descending=True)
+        if tp < 1.0 and (torch.cumsum(full[order], 0) - tp).abs().min() < 1e-5:
+            continue
+        assert out[i].item() == want, f"row {i}: {rows[i]}"
+        checked += 1
+    assert checked >= R // 2
+
+
+def test_sample_distribution_over_many_draws():
+    c = core()
+    logits = torch.tensor([2.0, 1.0, 0.0, -1.0, 1.5, -3.0])
+    n = 4000
+    us = (torch.arange(n) + 0.5) / n
+    rows = [(0.8, 0.9, 1.0, float(u), 0) for u in us]
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    c.sample(logits.repeat(n, 1).to(DEV), pack_params(c, rows), None, out)
+    freq = torch.bincount(out.cpu().long(), minlength=6).double() / n
+    want = pl.sample_probabilities(logits, 0.8, 0.9, 1.0, [])
+    assert (freq - want).abs().max() < 2e-3 and freq[want == 0].sum() == 0
+
+
+# --------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------
+def paged_case(seqs_len, q_rows, nh, nkv, hd, ps, dtype, seed, extra_pages=5, scale_key=None):
+    """Requests with ``seqs_len[i]`` cached+new tokens of which the last
+    ``q_rows[i]`` are this step's rows.  Pages are handed out in a shuffled
+    order.  Returns what the kernels take plus the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    E = len(seqs_len)
+    n_pages = sum(-(-L // ps) for L in seqs_len) + extra_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    MB = max(-(-L // ps) for L in seqs_len)
+    tables = torch.full((E, MB), -1, dtype=torch.int32)
+    kp = torch.randn(n_pages, nkv, ps, hd, generator=g).to(dtype)  # stale data in unused slots
+    vp = torch.randn(n_pages, nkv, ps, hd, generator=g).to(dtype)
+    qs, refs, positions, row_entry, cu, q_start = [], [], [], [], [0], []
+    for e, (L, n) in enumerate(zip(seqs_len, q_rows)):
+        k = torch.randn(L, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(L, nkv, hd, generator=g).to(dtype)
+        q = torch.randn(L, nh, hd, generator=g).to(dtype)
+        if scale_key is not None:  # one far key stands out for the last query
+            j = scale_key if scale_key >= 0 else L + scale_key
+            k[j] = k[j] * 0 + q[L - 1, :: nh // nkv][:nkv] * 4.0
+        for i in range(-(-L // ps)):
+            tables[e, i] = perm.pop()
+            lo, hi = i * ps, min(L, (i + 1) * ps)
+            kp[tables[e, i], :, : hi - lo] = k[lo:hi].transpose(0, 1)
+            vp[tables[e, i], :, : hi - lo] = v[lo:hi].transpose(0, 1)
+        refs.append((q.double(), k.double(), v.double(), L - n))
+        qs.append(q[L - n:].reshape(n, nh * hd))
+        positions += list(range(L - n, L))
+        row_entry += [e] * n
+        cu.append(cu[-1] + n)
+        q_start.append(L - n)
+    q_all = torch.cat(qs)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    ctx = SimpleNamespace(n_rows=q_all.shape[0], n_entries=E, positions=i32(positions),
+                          row_entry=i32(row_entry), cu_rows=i32(cu), q_start=i32(q_start),
+                          host_cu_rows=cu, max_rows_per_entry=max(q_rows), max_kv_len=max(seqs_len),
+                          scratch={})
+    return q_all.to(DEV), kp.to(DEV), vp.to(DEV), tables.to(DEV), ctx, refs
+
+
+def plain_result(refs, window=0):
+    outs = []
+    for q, k, v, start in refs:
+        o = pl.attention(q, k, v, window=window)
+        outs.append(o[start:].reshape(o.shape[0] - start, -1))
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, nkv, hd, ps, window", [
+    (4, 2, 16, 4, 0), (3, 1, 32, 8, 0), (6, 6, 48, 16, 0), (8, 2, 128, 16, 0), (5, 5, 80, 2, 0),
+    (4, 1, 64, 4, 7), (2, 2, 256, 32, 0), (40, 1, 16, 4, 0),
+])
+def test_attention_plain(dtype, nh, nkv, hd, ps, window):
+    c = core()
+    q, kp, vp, tables, ctx, refs = paged_case([37, 1, 64, 5], [37, 1, 3, 2], nh, nkv, hd, ps, dtype, 1)
+    out = torch.empty(q.shape[0], nh * hd, dtype=dtype, device=DEV)
+    err = c.new_error_word(DEV)
+    c.attention_plain(q, kp, vp, out, ctx.positions, ctx.row_entry, tables, nh,
+                      1 / math.sqrt(hd), window, err)
+    assert err.item() == 0
+    assert rel_err(out, plain_result(refs, window)) < (2e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_plain_finds_a_far_key(dtype):
+    """Among hundreds of keys one far key carries the answer."""
+    c = core()
+    for key in (0, 3, -300, 129):
+        q, kp, vp, tables, ctx, refs = paged_case([700], [1], 4, 2, 32, 16, dtype, 2, scale_key=key)
+        out = torch.empty(1, 4 * 32, dtype=dtype, device=DEV)
+        c.attention_plain(q, kp, vp, out, ctx.positions, ctx.row_entry, tables, 4,
+                          1 / math.sqrt(32), 0, c.new_error_word(DEV))
+        want = plain_result(refs)
+        j = key if key >= 0 else 700 + key
+        v_far = refs[0][2][j]  # [nkv, hd]
+        assert (want.view(4, 32)[0] - v_far[0]).abs().max() < 0.2  # the answer is that key's value
+        # scores reach |s| ~ 23 here, and exp(s) carries the rounding of s itself:
+        # relative error ~ |s| * 2^-23 * (a few) ~ 1e-5 in float32
+        assert rel_err(out, want) < (3e-5 if dtype == torch.float32 else 1e-2)
+
+
+MMA_CASES = [
+    # nh, nkv, hd, ps, window, lengths, rows
+    (4, 2, 16, 4, 0, [37, 1, 64, 5], [37, 1, 3, 2]),        # mixed: tile and split entries
+    (3, 1, 32, 8, 0, [100, 130], [100, 2]),                  # G = 3 (not a power of two)
+    (8, 2, 128, 16, 0, [300, 77, 513], [1, 1, 1]),           # pure decode, slices
+    (8, 2, 128, 16, 0, [257, 64], [257, 64]),                # whole prompts
+    (6, 6, 48, 16, 0, [90, 33], [40, 33]),                   # G = 1, a portion with a cached prefix
+    (32, 1, 64, 16, 0, [150, 20], [1, 20]),                  # G = 32 > 16: head sub-blocks
+    (4, 1, 64, 4, 9, [80, 30, 12], [80, 1, 3]),              # a window
+    (2, 2, 256, 32, 0, [70], [70]),
+    (5, 5, 80, 2, 0, [45, 9], [5, 9]),
+    (4, 4, 112, 16, 0, [130], [1]),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES, ids=[f"nh{c[0]}kv{c[1]}hd{c[2]}ps{c[3]}w{c[4]}r{max(c[6])}" for c in MMA_CASES])
+def test_attention_mma_against_plain(case):
+    from infernum_b200.ops import attention_fast
+    from infernum_b200.parts.base import Runtime
+    nh, nkv, hd, ps, window, lens, rows = case
+    c = core()
+    q, kp, vp, tables, ctx, refs = paged_case(lens, rows, nh, nkv, hd, ps, torch.bfloat16, 3)
+    rt = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV))
+    out = torch.full((q.shape[0], nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert attention_fast.run(q, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), window, rt)
+    assert rt.err.item() == 0
+    want = plain_result(refs, window)
+    assert torch.isfinite(out).all()
+    assert rel_err(out, want) < 1e-2
+    twin = torch.empty_like(out)
+    c.attention_plain(q, kp, vp, twin, ctx.positions, ctx.row_entry, tables, nh,
+                      1 / math.sqrt(hd), window, rt.err)
+    assert rel_err(out, twin.double()) < 1e-2
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+def test_attention_mma_slices_agree(splits):
+    from infernum_b200.ops import attention_fast
+    from infernum_b200.parts.base import Runtime
+    c = core()
+    nh, nkv, hd = 8, 2, 128
+    q, kp, vp, tables, ctx, refs = paged_case([700, 64, 65, 1], [1, 1, 1, 1], nh, nkv, hd, 16,
+                                              torch.bfloat16, 4, scale_key=0)
+    ctx.attention_mode = (2, splits)
+    rt = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV))
+    out = torch.full((4, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert attention_fast.run(q, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt)
+    assert rel_err(out, plain_result(refs)) < 1e-2
+
+
+def test_attention_mma_edges_of_tiles_and_pages():
+    """Lengths around the 64-key tile and the page edge, one query each, with
+    the last key standing out: a tile or page that is dropped or read twice
+    changes the answer."""
+    from infernum_b200.ops import attention_fast
+    from infernum_b200.parts.base import Runtime
+    c = core()
+    nh, nkv, hd, ps = 4, 2, 64, 16
+    for L in (1, 15, 16, 17, 63, 64, 65, 127, 128, 129, 191, 193):
+        for n in (1, min(L, 3), L):
+            q, kp, vp, tables, ctx, refs = paged_case([L], [n], nh, nkv, hd, ps, torch.bfloat16,
+                                                      L * 7 + n, scale_key=-1)
+            rt = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV))
+            out = torch.full((n, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+            assert attention_fast.run(q, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt)
+            assert rel_err(out, plain_result(refs)) < 1e-2, (L, n)

@@ -1,0 +1,124 @@
+"""A toy mixer with state of its own, defined here, is registered, built and
+stepped without a change to the package: the registries, the model
+description, the cache manager's state slots and the step function carry it."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def define_toy():
+    from infernum_b200.parts import (LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleItem, StateSpec,
+                                     WeightSpec, register_mixer)
+    from infernum_b200.registry import register_architecture
+
+    @register_mixer("toy_running_mean")
+    class RunningMean(Mixer):
+        """y_t = W . (decay * s_{t-1} + x_t), s carried per request in its state slot."""
+
+        def __init__(self, params, rt):
+            super().__init__(params, rt)
+            self.h = params["hidden_size"]
+            self.decay = params["decay"]
+            self.name = params["prefix"] + "mix.weight"
+
+        def state_spec(self):
+            return StateSpec((self.h,), torch.float32)
+
+        def weight_specs(self):
+            return {self.name: WeightSpec((self.h, self.h))}
+
+        def bind(self, weights):
+            self.w = weights[self.name].float()
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            cu = ctx.host_cu_rows
+            slots = ctx.slot_ids.tolist()
+            for e in range(ctx.n_entries):  # rows of a request in order, state carried across steps
+                s = cache.state[slots[e]]
+                for r in range(cu[e], cu[e + 1]):
+                    s.mul_(self.decay).add_(x[r].float())
+                    out[r] = (self.w @ s).to(x.dtype)
+            return out
+
+    def build_spec(cfg):
+        H, V = cfg["hidden_size"], cfg["vocab_size"]
+        layers = []
+        for i in range(cfg["num_hidden_layers"]):
+            p = f"layers.{i}."
+            norm = lambda n: PartSpec("rmsnorm", {"hidden_size": H, "eps": 1e-5, "weight": p + n})  # noqa: E731
+            mixer = PartSpec("toy_running_mean", {"hidden_size": H, "decay": cfg["decay"], "prefix": p}) \
+                if i % 2 == 0 else PartSpec("attention", {
+                    "hidden_size": H, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
+                    "prefix": p + "attn.",
+                    "position": {"kind": "rotary", "params": {"head_dim": 16, "theta": 1e4}}})
+            layers.append(LayerSpec("prenorm", name=p, parts={
+                "norm1": norm("n1"), "mixer": mixer, "norm2": norm("n2"),
+                "ffn": PartSpec("swiglu", {"hidden_size": H, "intermediate_size": 2 * H, "prefix": p + "mlp."})}))
+        return ModelSpec(
+            hidden_size=H, vocab_size=V,
+            embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "weight": "emb"}),
+            layers=tuple(layers), schedule=tuple(ScheduleItem(i) for i in range(len(layers))),
+            final_norm=PartSpec("rmsnorm", {"hidden_size": H, "eps": 1e-5, "weight": "fn"}),
+            lm_head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "weight": "head", "tied_to": "emb"}),
+            max_position=128)
+
+    register_architecture("toy-state", lambda d: dict(d), build_spec)
+
+
+CFG = {"model_type": "toy-state", "hidden_size": 32, "vocab_size": 50, "num_hidden_layers": 3, "decay": 0.5}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_steps_like_a_whole_run(dtype, tmp_path):
+    import infernum_b200 as ib
+    from infernum_b200.cache import CacheManager
+    from infernum_b200.engine.step import ModelRunner, StepEntry
+    define_toy()
+    # through a model folder, so the loader and the registry see the new architecture too
+    folder = ib.write_random_model(str(tmp_path / "toy"), CFG, seed=3)
+    model = ib.load_model(folder, dtype=dtype)
+    needs = model.cache_needs()
+    assert needs[0].state is not None and needs[0].paged is None and needs[1].paged is not None
+
+    def run(cuts_a, cuts_b):
+        cache = CacheManager(needs, page_size=4, num_pages=24, max_requests=3,
+                             dtype=model.rt.dtype, device=DEV)
+        assert cache.layer_caches[0].state.shape == (3, 32) and cache.layer_caches[1].state is None
+        runner = ModelRunner(model, cache)
+        # a request that lived in the slot before leaves state behind: it must be zeroed
+        old = cache.admit("old")
+        runner.step([StepEntry(old, [1, 2, 3, 4, 5], [])])
+        cache.release(old)
+        seqs = {"a": [int(t) for t in torch.arange(30) % 50], "b": [int(t) for t in (torch.arange(17) * 7) % 50]}
+        cuts = {"a": list(cuts_a), "b": list(cuts_b)}
+        rcs = {k: cache.admit(k) for k in seqs}
+        fed = {k: 0 for k in seqs}
+        rows = {k: [] for k in seqs}
+        while any(cuts.values()):
+            entries, who = [], []
+            for k in seqs:
+                if cuts[k]:
+                    n = cuts[k].pop(0)
+                    entries.append(StepEntry(rcs[k], seqs[k][fed[k]: fed[k] + n], list(range(n))))
+                    fed[k] += n
+                    who.append((k, n))
+            logits = runner.step(entries)
+            off = 0
+            for k, n in who:
+                rows[k].append(logits[off: off + n])
+                off += n
+        runner.check_errors()
+        assert fed == {"a": 30, "b": 17}
+        return {k: torch.cat(v).cpu() for k, v in rows.items()}
+
+    whole = run([30], [17])
+    cut = run([7, 1, 2, 13, 1, 6], [2, 9, 1, 1, 4])
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    for k in whole:
+        assert torch.isfinite(whole[k]).all()
+        scale = whole[k].abs().max()
+        assert (whole[k] - cut[k]).abs().max() / scale < tol
+    assert (whole["a"][:17] - whole["b"]).abs().max() > 1e-3  # the two requests are not mixed up
