@@ -293,3 +293,26 @@ IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, i
     IB_LAUNCH_CHECK();
     return IB_OK;
 }
+
+// ---------------------------------------------------------------------------
+// After a decode step whose inputs live on the device: every request moves one
+// position on, and (optionally) the token just selected becomes the next input.
+// ---------------------------------------------------------------------------
+__global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __restrict__ selected,
+                                      int* __restrict__ positions, int* __restrict__ kv_len, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    positions[i] += 1;
+    kv_len[i] += 1;
+    if (selected) tokens[i] = selected[i];
+}
+
+IB_EXPORT int ib_decode_advance(int* tokens, const int* selected, int* positions, int* kv_len,
+                                int n, void* stream) {
+    if (n <= 0) return IB_OK;
+    if (!tokens || !positions || !kv_len) return IB_ERR_BAD_ARG;
+    decode_advance_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, selected,
+                                                                             positions, kv_len, n);
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

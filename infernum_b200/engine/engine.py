@@ -20,7 +20,8 @@ import torch
 from ..cache.manager import CacheManager
 from ..errors import InfernumError
 from ..sampling.params import GenerateOptions
-from ..sampling.sampler import Sampler, recent_window
+from ..sampling.sampler import Sampler, pack_choices, recent_window
+from .decode import DecodeSession
 from .scheduler import BatchConfig, FinishReason, Scheduler, Sequence_, StepPlan
 from .step import ModelRunner, StepEntry
 
@@ -84,6 +85,10 @@ class Engine:
         self.sampler = Sampler(rt.device)
         self.stats = EngineStats()
         self._handles: Dict[int, RequestHandle] = {}
+        self._session: Optional[DecodeSession] = None
+        self._last_decode_key = None
+        self.h2d_bytes = 0  # bytes of step inputs copied to the device so far
+        self.d2h_bytes = 0  # bytes of step results read back so far
 
     @classmethod
     def with_config(cls, model, config: BatchConfig) -> "Engine":
@@ -114,19 +119,29 @@ class Engine:
         self.stats.preemptions = self.scheduler.num_preemptions
         events: List[Tuple[RequestHandle, GenerationEvent]] = []
         if plan.portions:
-            entries = [StepEntry(p.seq.cache, p.tokens, [p.count - 1] if p.wants_logits else [])
-                       for p in plan.portions]
-            logits = self.runner.step(entries)
-            self.scheduler.commit(plan)
             wanting = [p for p in plan.portions if p.wants_logits]
-            if logits is not None and wanting:
-                choices = []
-                for p in wanting:
-                    sp = p.seq.options.sampling
-                    choices.append(None if sp is None else
-                                   (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
-                chosen = self.sampler.select(logits, choices)
+            choices = []
+            for p in wanting:
+                sp = p.seq.options.sampling
+                choices.append(None if sp is None else
+                               (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
+            session = self._decode_session(plan, choices)
+            if session is not None:
+                sample_params = pack_choices(choices, session.recent_width)[:2] \
+                    if session.any_sampling else None
+                chosen = session.step([p.tokens[0] for p in plan.portions], sample_params)
+                self.h2d_bytes += 4 * len(plan.portions)
+                logits = session.logits
+            else:
+                entries = [StepEntry(p.seq.cache, p.tokens, [p.count - 1] if p.wants_logits else [])
+                           for p in plan.portions]
+                logits = self.runner.step(entries)
+                self.h2d_bytes += self.runner.last_upload_bytes
+                chosen = self.sampler.select(logits, choices) if logits is not None and wanting else None
+            self.scheduler.commit(plan)
+            if chosen is not None:
                 host = torch.cat([chosen, self.runner.rt.err]).cpu().tolist()
+                self.d2h_bytes += 4 * len(host)
                 if host[-1]:
                     self.runner.check_errors()
                 for p, tok in zip(wanting, host[:-1]):
@@ -155,6 +170,24 @@ class Engine:
                 del self._handles[handle.id]
         self.stats.step_seconds += time.perf_counter() - t0
         return events
+
+    def _decode_session(self, plan: StepPlan, choices) -> Optional[DecodeSession]:
+        """The session to run this step with, when the step only decodes and the
+        same requests decoded in the step before; else None."""
+        if not self.config.cuda_graphs or any(p.count != 1 or not p.wants_logits for p in plan.portions):
+            self._session = None
+            self._last_decode_key = None
+            return None
+        key = tuple(p.seq.cache.request_id for p in plan.portions)
+        if self._session is not None and (self._session.key != key or not self._session.can_continue()):
+            self._session = None
+        if self._session is None and self._last_decode_key == key:
+            longest = max(p.seq.options.max_new_tokens - len(p.seq.generated_ids) for p in plan.portions)
+            self._session = DecodeSession(
+                self.runner, [p.seq.cache for p in plan.portions], [p.tokens[0] for p in plan.portions],
+                max_steps=longest + 1, use_graph=True, sampling_rows=[c is not None for c in choices])
+        self._last_decode_key = key
+        return self._session
 
     def run_until_done(self, handles: Optional[Sequence[RequestHandle]] = None) -> None:
         while self.has_work() and (handles is None or any(not h.finished for h in handles)):

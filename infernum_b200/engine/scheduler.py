@@ -69,6 +69,7 @@ class BatchConfig:
     num_blocks: int = 1024
     max_tokens_per_step: int = 2048
     max_model_len: Optional[int] = None  # default: the model's max_position_embeddings
+    cuda_graphs: bool = True  # replay a recorded graph while the same requests decode
 
 
 @dataclass

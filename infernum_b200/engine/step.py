@@ -79,6 +79,7 @@ class ModelRunner:
         self.vocab_size = model.spec.vocab_size
         self.steps_run = 0
         self.rows_run = 0
+        self.last_upload_bytes = 0
 
     # ---- building the inputs -------------------------------------------------
     def _build(self, entries: Sequence[StepEntry]) -> StepContext:
@@ -135,6 +136,7 @@ class ModelRunner:
         if self.device.type == "cuda":
             host = host.pin_memory()
         dev = host.to(self.device, non_blocking=True)
+        self.last_upload_bytes = host.numel() * 4
         views, off = [], 0
         for s in sizes:
             views.append(dev[off: off + s])

@@ -54,7 +54,8 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_argmax.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
         lib.ib_sample.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                                   _c_void_p, _c_void_p]
-        for fn in ("ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
+        lib.ib_decode_advance.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p]
+        for fn in ("ib_decode_advance", "ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
                    "ib_silu_mul", "ib_attention_plain", "ib_gemm_plain", "ib_argmax", "ib_sample"):
             getattr(lib, fn).restype = _c_int
         _lib = lib
@@ -73,8 +74,13 @@ def stream_ptr(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+LAUNCHES = 0  # kernels of this package launched so far (benchmarks report the count)
+
+
 def check(code: int, what: str) -> None:
+    global LAUNCHES
     if code == 0:
+        LAUNCHES += 1
         return
     if code < 0:
         raise KernelError(f"{what}: kernel refused its arguments ({_ERR_NAMES.get(code, code)})")
@@ -279,3 +285,14 @@ def sample(logits: torch.Tensor, params: torch.Tensor, recent: Optional[torch.Te
     check(core_lib().ib_sample(logits.data_ptr(), logits.stride(0), R, V, params.data_ptr(),
                                _ptr(recent), recent_ld, out.data_ptr(), stream_ptr(logits)),
           "sample")
+
+
+def decode_advance(tokens: torch.Tensor, selected: Optional[torch.Tensor], positions: torch.Tensor,
+                   kv_len: torch.Tensor) -> None:
+    """positions += 1, kv_len += 1, and tokens = selected when given."""
+    require_cuda(tokens, selected, positions, kv_len)
+    for t, name in ((tokens, "tokens"), (selected, "selected"), (positions, "positions"), (kv_len, "kv_len")):
+        _int32(t, name)
+    check(core_lib().ib_decode_advance(tokens.data_ptr(), _ptr(selected), positions.data_ptr(),
+                                       kv_len.data_ptr(), tokens.numel(), stream_ptr(tokens)),
+          "decode_advance")

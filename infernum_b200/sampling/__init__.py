@@ -1,2 +1,2 @@
 from .params import GenerateOptions, SamplingParams
-from .sampler import Sampler, recent_window, uniform_for
+from .sampler import Sampler, pack_choices, recent_window, uniform_for

@@ -49,6 +49,35 @@ def recent_window(tokens: Sequence[int], params: Optional[SamplingParams]) -> Se
     return tokens[len(tokens) - w:] if w else []
 
 
+def pack_choices(choices: Sequence[Optional[tuple]], width: Optional[int] = None):
+    """Host tensors for the sampling kernel: params [R, 6] float32 (temperature,
+    top_p, penalty, u, count of recent tokens as int bits, pad), recent tokens
+    [R, width] int32, and which rows sample at all."""
+    R = len(choices)
+    if width is None:
+        width = max([len(c[2]) for c in choices if c is not None] + [1])
+    params = torch.zeros((R, core.SAMPLE_PARAM_FLOATS), dtype=torch.float32)
+    recent = torch.zeros((R, width), dtype=torch.int32)
+    n_recent = torch.zeros(R, dtype=torch.int32)
+    mask = torch.zeros(R, dtype=torch.bool)
+    for i, c in enumerate(choices):
+        if c is None:
+            params[i, :3] = 1.0
+            continue
+        sp, n_gen, rec = c
+        rec = list(rec)[-width:]
+        params[i, 0] = sp.temperature
+        params[i, 1] = sp.top_p
+        params[i, 2] = sp.repetition_penalty
+        params[i, 3] = uniform_for(sp.seed, n_gen)
+        if rec:
+            recent[i, : len(rec)] = torch.tensor(rec, dtype=torch.int32)
+        n_recent[i] = len(rec)
+        mask[i] = True
+    params.view(torch.int32)[:, 4] = n_recent
+    return params, recent, mask
+
+
 class Sampler:
     """Selects one token per logits row.  ``choices[i]`` is None for greedy or
     a tuple (SamplingParams, n_generated, recent tokens)."""
@@ -63,27 +92,7 @@ class Sampler:
         core.argmax(logits, out)
         if all(c is None for c in choices):
             return out
-        width = max([len(c[2]) for c in choices if c is not None] + [1])
-        params = torch.zeros((R, core.SAMPLE_PARAM_FLOATS), dtype=torch.float32)
-        recent = torch.zeros((R, width), dtype=torch.int32)
-        n_recent = torch.zeros(R, dtype=torch.int32)
-        mask = torch.zeros(R, dtype=torch.bool)
-        for i, c in enumerate(choices):
-            if c is None:
-                params[i, 0] = 1.0
-                params[i, 1] = 1.0
-                params[i, 2] = 1.0
-                continue
-            sp, n_gen, rec = c
-            params[i, 0] = sp.temperature
-            params[i, 1] = sp.top_p
-            params[i, 2] = sp.repetition_penalty
-            params[i, 3] = uniform_for(sp.seed, n_gen)
-            if len(rec):
-                recent[i, : len(rec)] = torch.tensor(list(rec), dtype=torch.int32)
-            n_recent[i] = len(rec)
-            mask[i] = True
-        params.view(torch.int32)[:, 4] = n_recent
+        params, recent, mask = pack_choices(choices)
         dev = logits.device
         sampled = torch.empty(R, dtype=torch.int32, device=dev)
         core.sample(logits, params.to(dev), recent.to(dev), sampled)
