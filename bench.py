@@ -148,7 +148,7 @@ def make_requests(runner, cache, batch, prompt_len, vocab, seed, chunk=2048):
     return caches, first
 
 
-def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks=None):
+def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks=None, graph=True):
     """Device-timed decode: K steps of a DecodeSession that feeds itself."""
     import torch
 
@@ -163,7 +163,7 @@ def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks
                          dtype=model.rt.dtype, device=model.rt.device)
     runner = ModelRunner(model, cache, max_rows=4096, max_entries=max(batch, 1))
     caches, first = make_requests(runner, cache, batch, prompt_len, model.spec.vocab_size, seed)
-    session = DecodeSession(runner, caches, first, max_steps=steps + warmup + 4, use_graph=True)
+    session = DecodeSession(runner, caches, first, max_steps=steps + warmup + 4, use_graph=graph)
     for _ in range(max(warmup, 3)):
         session.step()
     torch.cuda.synchronize()
@@ -281,6 +281,9 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--skip-extras", action="store_true", help="only the headline decode run")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only and print its numbers (for profiling)")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -306,6 +309,14 @@ def main() -> int:
     torch.cuda.set_device(0)
     model = ib.random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0",
                             options={"sm_count": torch.cuda.get_device_properties(0).multi_processor_count})
+    if args.only == "decode":
+        r = time_decode(model, args.batch, args.prompt_len, args.steps, warmup, args.page_size, args.seed,
+                        graph=not args.no_cuda_graph)
+        print(json.dumps({"only": "decode", "batch": args.batch, **r}))
+        return 0
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", **time_prefill(model, cfg, layers, 2048, args.page_size, peaks)}))
+        return 0
     clocks = ClockSampler(0)
     clocks.start()
     try:

@@ -56,6 +56,7 @@ struct Params {
     int gs;           // query heads of one kv head handled together (<= 16)
     int n_hsub;       // ceil((nh / nkv) / gs)
     int splits;       // split mode: slices of keys per request
+    int page_shift;   // log2(page_size) when it is a power of two, else -1
     int n_rows;       // rows of the whole step
     int small_rows;   // an entry with rows * gs <= small_rows belongs to split mode
     float scale_log2;
@@ -95,27 +96,57 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Copies keys [tile_start, tile_start + 64) of kv head g into one stage.
-// Keys outside [kv_min, kv_hi) and keys on an invalid page are zero-filled
+// How a tile's 64 x CH chunks of 16 bytes are dealt to the 128 threads: chunk
+// c = tid + 128 * i, i < LOAD_ITERS, is row c / CH, column c % CH.
+constexpr int LOAD_ITERS = (BN * CH + NTHREADS - 1) / NTHREADS;
+
+// Element offset (into a pool) of key j of kv head g, or -1 when the key lies
+// outside [kv_min, kv_hi) or its block-table entry is not a page of the pool
 // (pages below kv_min may already have been given back by a window).
-__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const Params& p, const int* table,
-                                          int g, int tile_start, int kv_min, int kv_hi) {
-    for (int c = threadIdx.x; c < BN * CH; c += NTHREADS) {
+__device__ __forceinline__ long long key_offset(const Params& p, const int* table, int g, int j,
+                                                int kv_min, int kv_hi) {
+    if (j < kv_min || j >= kv_hi) return -1;
+    int pi, slot;
+    if (p.page_shift >= 0) {
+        pi = j >> p.page_shift;
+        slot = j & (p.page_size - 1);
+    } else {
+        pi = j / p.page_size;
+        slot = j - pi * p.page_size;
+    }
+    const int page = table[pi];
+    if (page < 0 || page >= p.num_pages) {
+        atomicOr(p.err, IB_FLAG_BAD_PAGE);
+        return -1;
+    }
+    return (((long long)page * p.nkv + g) * p.page_size + slot) * HD;
+}
+
+// Looks up where this thread's rows of a tile live (one block-table read per
+// row, all issued together so that their latencies overlap).
+__device__ __forceinline__ void locate_tile(long long (&off)[LOAD_ITERS], const Params& p,
+                                            const int* table, int g, int tile_start, int kv_min,
+                                            int kv_hi) {
+#pragma unroll
+    for (int i = 0; i < LOAD_ITERS; ++i) {
+        const int c = threadIdx.x + NTHREADS * i;
+        off[i] = c < BN * CH ? key_offset(p, table, g, tile_start + c / CH, kv_min, kv_hi) : -1;
+    }
+}
+
+// Copies one tile into a stage from the offsets found by locate_tile; rows
+// without a valid offset are zero-filled.
+__device__ __forceinline__ void copy_tile(bf16* ks, bf16* vs, const Params& p,
+                                          const long long (&off)[LOAD_ITERS]) {
+#pragma unroll
+    for (int i = 0; i < LOAD_ITERS; ++i) {
+        const int c = threadIdx.x + NTHREADS * i;
+        if (c >= BN * CH) break;
         const int row = c / CH, ch = c % CH;
-        const int j = tile_start + row;
-        int bytes = 0;
-        size_t off = 0;
-        if (j >= kv_min && j < kv_hi) {
-            const int page = table[j / p.page_size];
-            if (page >= 0 && page < p.num_pages) {
-                off = (((size_t)page * p.nkv + g) * p.page_size + (j % p.page_size)) * HD + ch * 8;
-                bytes = 16;
-            } else {
-                atomicOr(p.err, IB_FLAG_BAD_PAGE);
-            }
-        }
-        cp_async_16(ks + row * LDS + ch * 8, p.k_pool + off, bytes);
-        cp_async_16(vs + row * LDS + ch * 8, p.v_pool + off, bytes);
+        const bool ok = off[i] >= 0;
+        const size_t src = ok ? (size_t)off[i] + ch * 8 : 0;
+        cp_async_16(ks + row * LDS + ch * 8, p.k_pool + src, ok ? 16 : 0);
+        cp_async_16(vs + row * LDS + ch * 8, p.v_pool + src, ok ? 16 : 0);
     }
 }
 
@@ -198,17 +229,22 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
+    // The copies of tile t+1 are issued while tile t is computed, and the
+    // block-table reads for tile t+2 are issued before that, so neither latency
+    // sits on the critical path.
+    long long off[LOAD_ITERS];
     if (t_begin < t_end) {
-        load_tile(k_s[0], v_s[0], p, table, g, kv_lo + t_begin * BN, kv_min, kv_hi);
+        locate_tile(off, p, table, g, kv_lo + t_begin * BN, kv_min, kv_hi);
+        copy_tile(k_s[0], v_s[0], p, off);
     }
     cp_async_commit();
+    if (t_begin + 1 < t_end) locate_tile(off, p, table, g, kv_lo + (t_begin + 1) * BN, kv_min, kv_hi);
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) & 1;
-        if (t + 1 < t_end)
-            load_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, table, g, kv_lo + (t + 1) * BN, kv_min,
-                      kv_hi);
+        if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, off);
         cp_async_commit();
+        if (t + 2 < t_end) locate_tile(off, p, table, g, kv_lo + (t + 2) * BN, kv_min, kv_hi);
         cp_async_wait<1>();
         __syncthreads();
 
@@ -437,6 +473,9 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     p.page_size = page_size;
     p.num_pages = num_pages;
     p.window = window;
+    p.page_shift = -1;
+    for (int b = 0; b < 31; ++b)
+        if ((1 << b) == page_size) p.page_shift = b;
     const int G = nh / nkv;
     p.gs = G < 16 ? G : 16;
     p.n_hsub = (G + p.gs - 1) / p.gs;

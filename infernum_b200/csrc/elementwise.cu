@@ -89,10 +89,111 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     }
 }
 
+// Vectorised variant for H % 4 == 0: each thread owns up to NV groups of four
+// consecutive elements, keeps them in registers, and the row is read once.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned*>(&a);
+        raw.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename TD, typename TW, typename TO, int NV>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                       const TW* __restrict__ weight, TO* __restrict__ out,
+                                       const int* __restrict__ row_idx, int H, float eps,
+                                       int write_residual) {
+    __shared__ float scratch[33];
+    const int row = blockIdx.x;
+    const int src = row_idx ? row_idx[row] : row;
+    float* r = residual + (size_t)src * H;
+    const TD* d = delta ? delta + (size_t)src * H : nullptr;
+    TO* o = out + (size_t)row * H;
+    const int groups = H >> 2;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int gidx = threadIdx.x + k * blockDim.x;
+        if (gidx < groups) {
+            v[k] = Vec4<float>::load(r + 4 * gidx);
+            if (d) {
+                const float4 dv = Vec4<TD>::load(d + 4 * gidx);
+                v[k].x += dv.x; v[k].y += dv.y; v[k].z += dv.z; v[k].w += dv.w;
+                if (write_residual) Vec4<float>::store(r + 4 * gidx, v[k]);
+            }
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int gidx = threadIdx.x + k * blockDim.x;
+        if (gidx < groups) {
+            const float4 w = Vec4<TW>::load(weight + 4 * gidx);
+            Vec4<TO>::store(o + 4 * gidx, make_float4((v[k].x * inv) * w.x, (v[k].y * inv) * w.y,
+                                                      (v[k].z * inv) * w.z, (v[k].w * inv) * w.w));
+        }
+    }
+}
+
+template <typename TD, typename TW, typename TO>
+static bool try_launch_vec(float* residual, const void* delta, const void* weight, void* out,
+                           const int* row_idx, int n_rows, int H, float eps, int write_residual,
+                           cudaStream_t s) {
+    if (H % 4) return false;
+    if (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) return false;
+    const int groups = H / 4;
+    int threads = ((groups + 31) / 32) * 32;
+    int nv = 1;
+    while (threads > 1024 || (threads > 256 && nv < 2 && groups >= 2048)) {
+        nv *= 2;
+        threads = (((groups + nv - 1) / nv + 31) / 32) * 32;
+        if (nv > 8) return false;
+    }
+#define IB_VEC_LAUNCH(NV)                                                                        \
+    add_rmsnorm_vec_kernel<TD, TW, TO, NV><<<n_rows, threads, 0, s>>>(                           \
+        residual, (const TD*)delta, (const TW*)weight, (TO*)out, row_idx, H, eps, write_residual)
+    switch (nv) {
+        case 1: IB_VEC_LAUNCH(1); break;
+        case 2: IB_VEC_LAUNCH(2); break;
+        case 4: IB_VEC_LAUNCH(4); break;
+        case 8: IB_VEC_LAUNCH(8); break;
+        default: return false;
+    }
+#undef IB_VEC_LAUNCH
+    return true;
+}
+
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* residual, const void* delta, const void* weight,
                               int weight_dtype, void* out, const int* row_idx, int n_rows, int H,
                               float eps, int write_residual, cudaStream_t s) {
+    if (weight_dtype == 0 && try_launch_vec<TD, float, TO>(residual, delta, weight, out, row_idx, n_rows,
+                                                            H, eps, write_residual, s)) {
+        IB_LAUNCH_CHECK();
+        return IB_OK;
+    }
+    if (weight_dtype == 1 && try_launch_vec<TD, bf16, TO>(residual, delta, weight, out, row_idx, n_rows,
+                                                           H, eps, write_residual, s)) {
+        IB_LAUNCH_CHECK();
+        return IB_OK;
+    }
     int threads = 256;
     if (H >= 8192) threads = 1024;
     else if (H >= 2048) threads = 512;

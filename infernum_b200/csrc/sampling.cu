@@ -63,11 +63,113 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int ld, int V,
     }
 }
 
-IB_EXPORT int ib_argmax(const float* logits, int ld, int n_rows, int V, int* out, void* stream) {
+// Wide rows are cut in slices so that more than one CTA per row reads memory:
+// first the best (value, index) of every slice, then the best of those.
+__global__ void argmax_slice_kernel(const float* __restrict__ logits, int ld, int V, int slice,
+                                    float* __restrict__ part_val, int* __restrict__ part_idx) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* x = logits + (size_t)blockIdx.x * ld;
+    const int begin = blockIdx.y * slice, end = min(V, begin + slice);
+    float best = -INFINITY;
+    int bi = V;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best || (v == best && i < bi)) {
+            best = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = bi;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : V;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            part_val[blockIdx.x * gridDim.y + blockIdx.y] = best;
+            part_idx[blockIdx.x * gridDim.y + blockIdx.y] = bi;
+        }
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ part_val,
+                                    const int* __restrict__ part_idx, int n_slices, int V,
+                                    int* __restrict__ out) {
+    // one warp per row
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float best = -INFINITY;
+    int bi = V;
+    for (int i = lane; i < n_slices; i += 32) {
+        const float v = part_val[row * n_slices + i];
+        const int idx = part_idx[row * n_slices + i];
+        if (v > best || (v == best && idx < bi)) {
+            best = v;
+            bi = idx;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) out[row] = bi < V ? bi : 0;
+}
+
+#define IB_ARGMAX_MAX_SLICES 64
+
+// `scratch` (optional) holds n_rows * 64 floats followed by n_rows * 64 ints;
+// with it, wide rows are read by several CTAs each.
+IB_EXPORT int ib_argmax(const float* logits, int ld, int n_rows, int V, int* out, void* scratch,
+                        long long scratch_bytes, void* stream) {
     if (n_rows <= 0) return IB_OK;
     if (!logits || !out || V <= 0 || ld < V) return IB_ERR_BAD_ARG;
-    const int threads = V >= 8192 ? 1024 : 256;
-    argmax_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(logits, ld, V, out);
+    cudaStream_t s = (cudaStream_t)stream;
+    int slices = 1;
+    if (scratch && V >= 16384) {
+        slices = (V + 4095) / 4096;
+        if (slices > IB_ARGMAX_MAX_SLICES) slices = IB_ARGMAX_MAX_SLICES;
+        while (slices > 1 && (long long)n_rows * slices > 4096) slices /= 2;
+        if (scratch_bytes < (long long)n_rows * slices * 8) slices = 1;
+    }
+    if (slices <= 1) {
+        const int threads = V >= 8192 ? 1024 : 256;
+        argmax_kernel<<<n_rows, threads, 0, s>>>(logits, ld, V, out);
+        IB_LAUNCH_CHECK();
+        return IB_OK;
+    }
+    const int slice = (V + slices - 1) / slices;
+    float* pv = (float*)scratch;
+    int* pi = (int*)(pv + (size_t)n_rows * slices);
+    argmax_slice_kernel<<<dim3(n_rows, slices), 256, 0, s>>>(logits, ld, V, slice, pv, pi);
+    IB_LAUNCH_CHECK();
+    argmax_merge_kernel<<<n_rows, 32, 0, s>>>(pv, pi, slices, V, out);
     IB_LAUNCH_CHECK();
     return IB_OK;
 }

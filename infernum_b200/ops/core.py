@@ -51,7 +51,8 @@ def core_lib() -> ctypes.CDLL:
                                            _c_float, _c_void_p, _c_void_p]
         lib.ib_gemm_plain.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                                       _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
-        lib.ib_argmax.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
+        lib.ib_argmax.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll,
+                                  _c_void_p]
         lib.ib_sample.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                                   _c_void_p, _c_void_p]
         lib.ib_decode_advance.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p]
@@ -254,14 +255,27 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                    stream_ptr(out)), "gemm_plain")
 
 
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """Greedy selection per row: the largest logit, the lowest index among equals."""
     require_cuda(logits, out)
     _int32(out, "out")
     R, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.numel() != R:
         raise KernelError("argmax: logits must be float32 [R, V], out int32 [R]")
+    scratch_ptr, scratch_bytes = None, 0
+    if V >= 16384:
+        # partial results of the sliced kernel: 64 (value, index) pairs per row
+        key = (logits.device, R)
+        buf = _argmax_scratch.get(key)
+        if buf is None:
+            buf = torch.empty(R * 64 * 2, dtype=torch.int32, device=logits.device)
+            _argmax_scratch[key] = buf
+        scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel() * 4
     check(core_lib().ib_argmax(logits.data_ptr(), logits.stride(0), R, V, out.data_ptr(),
-                               stream_ptr(logits)), "argmax")
+                               scratch_ptr, scratch_bytes, stream_ptr(logits)), "argmax")
 
 
 SAMPLE_PARAM_FLOATS = 6  # temperature, top_p, penalty, u, n_recent (int bits), pad
