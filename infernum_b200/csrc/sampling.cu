@@ -174,6 +174,75 @@ IB_EXPORT int ib_argmax(const float* logits, int ld, int n_rows, int V, int* out
     return IB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// ib_argmax_noalloc: greedy selection for callers that cannot allocate.
+//
+// Who that is: code that is handed its input and output buffers by a host
+// application and nothing else - a sampling plug-in inside someone else's
+// serving loop, say - and that must stay off cudaMalloc on its hot path,
+// because cudaMalloc synchronises the whole device, and because an engine
+// like this one gives nearly all free memory to cache pages, so a late
+// allocation can simply fail.  ib_argmax needs a scratch buffer from its
+// caller to spread a wide row over several CTAs; this variant keeps that
+// scratch inside the library instead.
+//
+// The scratch is the file-scope device array below: 128 KiB, enough for
+// IB_NOALLOC_MAX_ROWS rows of 64 partial results.  Every GPU that loads this
+// library holds those 128 KiB until the process exits.  All calls share the
+// array and it keeps whatever the last call left; nothing in it has to start
+// at zero, because every partial result that is read was written by the same
+// call.  Two calls that overlap on the GPU (different streams, or different
+// host threads on one device) race on it: keep calls on one stream, or
+// serialise them.
+//
+// The first call on a device looks the array's address up (in host code the
+// array's name is only a stand-in for the symbol, not a device address) and
+// remembers it per device; that first call should come before any stream
+// capture begins.  The function calls no cudaMalloc, cudaFree or other
+// allocating routine.  It has no counterpart in the reference.
+// ---------------------------------------------------------------------------
+#define IB_NOALLOC_MAX_ROWS 256
+#define IB_NOALLOC_MAX_DEVICES 64
+#define IB_ERR_NOALLOC_SETUP (-4)
+
+static __device__ __align__(256) unsigned char
+    g_argmax_noalloc_scratch[IB_NOALLOC_MAX_ROWS * IB_ARGMAX_MAX_SLICES * 8];
+
+static void* g_argmax_noalloc_ptr[IB_NOALLOC_MAX_DEVICES] = {nullptr};
+
+IB_EXPORT int ib_argmax_noalloc_max_rows() { return IB_NOALLOC_MAX_ROWS; }
+
+IB_EXPORT int ib_argmax_noalloc(const float* logits, int ld, int n_rows, int V, int* out,
+                                void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!logits || !out || V <= 0 || ld < V) return IB_ERR_BAD_ARG;
+    if (n_rows > IB_NOALLOC_MAX_ROWS) return IB_ERR_TOO_LARGE;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= IB_NOALLOC_MAX_DEVICES) return IB_ERR_NOALLOC_SETUP;
+    if (!g_argmax_noalloc_ptr[dev]) {
+        // set-up, once per device, with that device current
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_argmax_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!ptr) return IB_ERR_NOALLOC_SETUP;
+        g_argmax_noalloc_ptr[dev] = ptr;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    int slices = (V + 4095) / 4096;
+    if (slices > IB_ARGMAX_MAX_SLICES) slices = IB_ARGMAX_MAX_SLICES;
+    if (slices < 1) slices = 1;
+    const int slice = (V + slices - 1) / slices;
+    float* pv = (float*)g_argmax_noalloc_ptr[dev];
+    int* pi = (int*)(pv + (size_t)n_rows * slices);
+    argmax_slice_kernel<<<dim3(n_rows, slices), 256, 0, s>>>(logits, ld, V, slice, pv, pi);
+    IB_LAUNCH_CHECK();
+    argmax_merge_kernel<<<n_rows, 32, 0, s>>>(pv, pi, slices, V, out);
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
 // Per-row parameters of ib_sample (one struct per row, in device memory).
 struct SampleParams {
     float temperature;  // > 0
