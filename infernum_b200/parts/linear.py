@@ -41,6 +41,10 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
     if M == 0:
         return out
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        if not BF16_ROUTES:
+            from ..ops import gemm_tc
+
+            BF16_ROUTES.append(gemm_tc.route)
         for route in BF16_ROUTES:
             if route(x, w, out):
                 return out

@@ -375,3 +375,40 @@ def test_attention_mma_edges_of_tiles_and_pages():
             out = torch.full((n, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
             assert attention_fast.run(q, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt)
             assert rel_err(out, plain_result(refs)) < 1e-2, (L, n)
+
+
+# --------------------------------------------------------------------------
+# the tcgen05 matrix product
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("T, N, K, splits", [
+    (1, 128, 64, 1), (16, 128, 256, 1), (8, 200, 120, 1), (33, 333, 200, 1), (64, 640, 1024, 2),
+    (100, 512, 1024, 1), (300, 256, 512, 1), (8, 1024, 4096, 8), (3, 320, 96, 1), (30, 300, 2048, 8),
+    (17, 130, 1000, 4), (257, 384, 264, 1),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(T, N, K, splits, out_dtype):
+    from infernum_b200.ops import gemm_tc
+    g = torch.Generator().manual_seed(T * 1000 + N)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    out = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
+    gemm_tc.gemm_tc(x.to(DEV), w.to(DEV), out, splits=splits)
+    assert gemm_tc.error_flags(DEV) == 0
+    assert rel_err(out, x.double() @ w.double().T) < (5e-3 if out_dtype == torch.bfloat16 else 2e-6)
+    # a row of tokens does not depend on the others in the batch
+    if T > 1:
+        one = torch.empty(1, N, dtype=out_dtype, device=DEV)
+        gemm_tc.gemm_tc(x[T - 1:].contiguous().to(DEV), w.to(DEV), one, splits=splits)
+        assert rel_err(one[0], out[T - 1]) < 1e-6 if out_dtype == torch.float32 else True
+
+
+def test_gemm_tcgen05_takes_strided_rows_and_refuses_what_tma_cannot_fetch():
+    from infernum_b200.ops import gemm_tc
+    big = torch.randn(10, 512).to(torch.bfloat16).to(DEV)
+    x = big[:, :256]  # row stride 512, 256 columns
+    w = torch.randn(140, 256).to(torch.bfloat16).to(DEV)
+    out = torch.empty(10, 140, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_tc(x, w, out)
+    assert rel_err(out, x.double().cpu() @ w.double().cpu().T) < 5e-3
+    assert not gemm_tc.eligible(big[:, :250], w[:, :250], out)  # K not a multiple of 8
+    assert not gemm_tc.eligible(big[:, 1:257], w, out)  # base not 16-byte aligned
