@@ -153,6 +153,8 @@ __device__ __forceinline__ void copy_tile(bf16* ks, bf16* vs, const Params& p,
 template <bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_trigger();
+    pdl_wait();  // queries, keys and values come from the kernels before this one
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_s[2] = {smem, smem + TILE_ELEMS};
     bf16* v_s[2] = {smem + 2 * TILE_ELEMS, smem + 3 * TILE_ELEMS};
@@ -406,6 +408,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
 
 // Merges the slices of split mode: one block per (row, head).
 __global__ void attention_combine_kernel(const Params p) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x, head = blockIdx.y;
     float mx = -INFINITY;
     for (int s = 0; s < p.splits; ++s)
@@ -504,7 +508,8 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     if (mode & 1) {
         const int rq = BN / p.gs;
         dim3 grid((max_rows_per_entry + rq - 1) / rq, n_entries, nkv * p.n_hsub);
-        attention_mma_kernel<false><<<grid, NTHREADS, SMEM_BYTES, s>>>(p);
+        cudaError_t le = launch_kernel(attention_mma_kernel<false>, grid, dim3(NTHREADS), SMEM_BYTES, s, p);
+        if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
     }
     if (mode & 2) {
@@ -515,14 +520,16 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
             p.part_ml = p.part_o + (size_t)splits * n_rows * nh * HD;
         }
         dim3 grid(splits, n_entries, nkv * p.n_hsub);
-        attention_mma_kernel<true><<<grid, NTHREADS, SMEM_BYTES, s>>>(p);
+        cudaError_t le = launch_kernel(attention_mma_kernel<true>, grid, dim3(NTHREADS), SMEM_BYTES, s, p);
+        if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
         if (splits > 1) {
             // Only rows that split mode handled have partial results; with both
             // modes in one step the caller keeps splits at 1.
             if (mode & 1) return IB_ERR_BAD_ARG;
             dim3 cgrid(n_rows, nh);
-            attention_combine_kernel<<<cgrid, HD >= 128 ? 128 : 64, 0, s>>>(p);
+            le = launch_kernel(attention_combine_kernel, cgrid, dim3(HD >= 128 ? 128 : 64), 0, s, p);
+            if (le != cudaSuccess) return (int)le;
             IB_LAUNCH_CHECK();
         }
     }

@@ -34,6 +34,39 @@ namespace ib {
 
 typedef __nv_bfloat16 bf16;
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with launch_kernel() may
+// begin while the kernel before it in the stream still runs.  It must call
+// pdl_wait() before it touches anything an earlier kernel wrote (and before
+// it writes anything an earlier kernel may read); what it does before that -
+// setting up barriers, fetching weights, which no kernel writes - overlaps
+// with its predecessor.  pdl_trigger() lets the next kernel in the stream do
+// the same with this one.  Without the launch attribute both are no-ops.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+inline int& pdl_flag() {
+    static int enabled = 1;
+    return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_flag() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 
@@ -89,3 +122,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 }  // namespace ib
+
+// Turns programmatic dependent launch on or off for this library (default on).
+extern "C" __attribute__((visibility("default"), weak)) int ib_set_pdl(int on) {
+    ib::pdl_flag() = on ? 1 : 0;
+    return 0;
+}

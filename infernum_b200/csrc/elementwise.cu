@@ -23,6 +23,8 @@ using namespace ib;
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int V, unsigned* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const int id = ids[row];
     float* o = out + (size_t)row * H;
@@ -42,9 +44,9 @@ IB_EXPORT int ib_embed(const int* ids, const void* table, int table_dtype, float
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == 0)
-        embed_kernel<float><<<n_rows, threads, 0, s>>>(ids, (const float*)table, out, H, V, err);
+        { cudaError_t le__ = launch_kernel(embed_kernel<float>, dim3(n_rows), dim3(threads), 0, s, ids, (const float*)table, out, H, V, err); if (le__ != cudaSuccess) return (int)le__; }
     else if (table_dtype == 1)
-        embed_kernel<bf16><<<n_rows, threads, 0, s>>>(ids, (const bf16*)table, out, H, V, err);
+        { cudaError_t le__ = launch_kernel(embed_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, ids, (const bf16*)table, out, H, V, err); if (le__ != cudaSuccess) return (int)le__; }
     else
         return IB_ERR_UNSUPPORTED;
     IB_LAUNCH_CHECK();
@@ -64,6 +66,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    const TW* __restrict__ weight, TO* __restrict__ out,
                                    const int* __restrict__ row_idx, int H, float eps,
                                    int write_residual) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int row = blockIdx.x;
     const int src = row_idx ? row_idx[row] : row;
@@ -117,6 +121,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
                                        const TW* __restrict__ weight, TO* __restrict__ out,
                                        const int* __restrict__ row_idx, int H, float eps,
                                        int write_residual) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int row = blockIdx.x;
     const int src = row_idx ? row_idx[row] : row;
@@ -166,9 +172,11 @@ static bool try_launch_vec(float* residual, const void* delta, const void* weigh
         threads = (((groups + nv - 1) / nv + 31) / 32) * 32;
         if (nv > 8) return false;
     }
-#define IB_VEC_LAUNCH(NV)                                                                        \
-    add_rmsnorm_vec_kernel<TD, TW, TO, NV><<<n_rows, threads, 0, s>>>(                           \
-        residual, (const TD*)delta, (const TW*)weight, (TO*)out, row_idx, H, eps, write_residual)
+#define IB_VEC_LAUNCH(NV)                                                                   \
+    launch_kernel(add_rmsnorm_vec_kernel<TD, TW, TO, NV>, dim3(n_rows), dim3(threads), 0, s, \
+                  residual, (const TD*)delta, (const TW*)weight, (TO*)out, row_idx, H, eps,  \
+                  write_residual)
+    // a failed launch is picked up by cudaGetLastError in the caller
     switch (nv) {
         case 1: IB_VEC_LAUNCH(1); break;
         case 2: IB_VEC_LAUNCH(2); break;
@@ -199,13 +207,13 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const void* we
     else if (H >= 2048) threads = 512;
     else if (H <= 256) threads = 64;
     if (weight_dtype == 0)
-        add_rmsnorm_kernel<TD, float, TO><<<n_rows, threads, 0, s>>>(
+        { cudaError_t le__ = launch_kernel(add_rmsnorm_kernel<TD, float, TO>, dim3(n_rows), dim3(threads), 0, s, 
             residual, (const TD*)delta, (const float*)weight, (TO*)out, row_idx, H, eps,
-            write_residual);
+            write_residual); if (le__ != cudaSuccess) return (int)le__; }
     else if (weight_dtype == 1)
-        add_rmsnorm_kernel<TD, bf16, TO><<<n_rows, threads, 0, s>>>(
+        { cudaError_t le__ = launch_kernel(add_rmsnorm_kernel<TD, bf16, TO>, dim3(n_rows), dim3(threads), 0, s, 
             residual, (const TD*)delta, (const bf16*)weight, (TO*)out, row_idx, H, eps,
-            write_residual);
+            write_residual); if (le__ != cudaSuccess) return (int)le__; }
     else
         return IB_ERR_UNSUPPORTED;
     IB_LAUNCH_CHECK();
@@ -232,6 +240,8 @@ IB_EXPORT int ib_add_rmsnorm(float* residual, const void* delta, const void* wei
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                     size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) residual[i] += to_f32(delta[i]);
 }
@@ -243,9 +253,9 @@ IB_EXPORT int ib_residual_add(float* residual, const void* delta, int act_dtype,
     cudaStream_t s = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (act_dtype == 0)
-        residual_add_kernel<float><<<blocks, 256, 0, s>>>(residual, (const float*)delta, (size_t)n);
+        { cudaError_t le__ = launch_kernel(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, s, residual, (const float*)delta, (size_t)n); if (le__ != cudaSuccess) return (int)le__; }
     else if (act_dtype == 1)
-        residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(residual, (const bf16*)delta, (size_t)n);
+        { cudaError_t le__ = launch_kernel(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, s, residual, (const bf16*)delta, (size_t)n); if (le__ != cudaSuccess) return (int)le__; }
     else
         return IB_ERR_UNSUPPORTED;
     IB_LAUNCH_CHECK();
@@ -271,6 +281,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int qkv_stride,
                                    T* __restrict__ v_pool, int nh, int nkv, int hd, int rd,
                                    int page_size, int num_pages, int write_kv,
                                    unsigned* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const int half = hd / 2;
     const int rhalf = rd / 2;
@@ -351,13 +363,13 @@ IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int
     if (by > 16) by = 16;
     dim3 grid(n_rows, by);
     if (act_dtype == 0)
-        rope_append_kernel<float><<<grid, threads, 0, s>>>(
+        { cudaError_t le__ = launch_kernel(rope_append_kernel<float>, dim3(grid), dim3(threads), 0, s, 
             (float*)qkv, qkv_stride, positions, row_entry, block_tables, max_blocks, inv_freq,
-            (float*)k_pool, (float*)v_pool, nh, nkv, hd, rd, page_size, num_pages, write_kv, err);
+            (float*)k_pool, (float*)v_pool, nh, nkv, hd, rd, page_size, num_pages, write_kv, err); if (le__ != cudaSuccess) return (int)le__; }
     else if (act_dtype == 1)
-        rope_append_kernel<bf16><<<grid, threads, 0, s>>>(
+        { cudaError_t le__ = launch_kernel(rope_append_kernel<bf16>, dim3(grid), dim3(threads), 0, s, 
             (bf16*)qkv, qkv_stride, positions, row_entry, block_tables, max_blocks, inv_freq,
-            (bf16*)k_pool, (bf16*)v_pool, nh, nkv, hd, rd, page_size, num_pages, write_kv, err);
+            (bf16*)k_pool, (bf16*)v_pool, nh, nkv, hd, rd, page_size, num_pages, write_kv, err); if (le__ != cudaSuccess) return (int)le__; }
     else
         return IB_ERR_UNSUPPORTED;
     IB_LAUNCH_CHECK();
@@ -369,6 +381,8 @@ IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int I, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t row = idx / I;
@@ -386,9 +400,9 @@ IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, i
     const size_t total = (size_t)n_rows * I;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (act_dtype == 0)
-        silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)x, (float*)out, I, total);
+        { cudaError_t le__ = launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)x, (float*)out, I, total); if (le__ != cudaSuccess) return (int)le__; }
     else if (act_dtype == 1)
-        silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)x, (bf16*)out, I, total);
+        { cudaError_t le__ = launch_kernel(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)x, (bf16*)out, I, total); if (le__ != cudaSuccess) return (int)le__; }
     else
         return IB_ERR_UNSUPPORTED;
     IB_LAUNCH_CHECK();
@@ -401,6 +415,8 @@ IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, i
 // ---------------------------------------------------------------------------
 __global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __restrict__ selected,
                                       int* __restrict__ positions, int* __restrict__ kv_len, int n) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     positions[i] += 1;
@@ -412,8 +428,8 @@ IB_EXPORT int ib_decode_advance(int* tokens, const int* selected, int* positions
                                 int n, void* stream) {
     if (n <= 0) return IB_OK;
     if (!tokens || !positions || !kv_len) return IB_ERR_BAD_ARG;
-    decode_advance_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, selected,
-                                                                             positions, kv_len, n);
+    { cudaError_t le__ = launch_kernel(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, tokens, selected,
+                                                                             positions, kv_len, n); if (le__ != cudaSuccess) return (int)le__; }
     IB_LAUNCH_CHECK();
     return IB_OK;
 }

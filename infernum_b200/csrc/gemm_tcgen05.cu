@@ -206,6 +206,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     __shared__ unsigned tmem_base_slot;
     __shared__ unsigned gave_up;
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t_tile = blockIdx.x;   // token tile: fastest, so neighbours share a weight tile
     const int n_tile = blockIdx.y;
@@ -238,10 +239,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         if (elect_one()) {
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
-            for (int i = 0; i < n_kblocks; ++i) {
+            // Weights are written by no kernel, so the first ring of weight
+            // tiles is fetched before waiting for the kernel that produces the
+            // tokens; only the token tiles have to wait for it.
+            const int first = min(STAGES, n_kblocks);
+            for (int i = 0; i < first; ++i) {
+                unsigned char* ws = smem + (size_t)i * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                tma_load_2d(ws, &map_w, &full_bar[i], (kb_begin + i) * BK, n_tile * BM);
+            }
+            pdl_wait();
+            for (int i = 0; i < first; ++i) {
+                unsigned char* xs = smem + (size_t)i * STAGE_BYTES + W_BYTES;
+                tma_load_2d(xs, &map_x, &full_bar[i], (kb_begin + i) * BK, t_tile * BN);
+            }
+            for (int i = first; i < n_kblocks; ++i) {
                 const int s = i % STAGES;
                 const unsigned round = i / STAGES;
-                if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+                if (!mbar_wait(&empty_bar[s], (round - 1) & 1)) {
                     atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
                     gave_up = 1;
                     break;
@@ -287,6 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         const int quad = warp & 3;
         const int row = quad * 32 + lane;          // weight row within the tile
         const int n = n_tile * BM + row;
+        pdl_wait();  // nothing is stored before the kernels ahead of this one are done
         bool ok = mbar_wait(&accum_bar, 0);
         if (!ok && lane == 0) {
             atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
@@ -419,13 +435,15 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = p.splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_flag() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN>, mw, mx, p);
     if (e != cudaSuccess) return (int)e;
     IB_LAUNCH_CHECK();

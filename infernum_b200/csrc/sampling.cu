@@ -19,6 +19,8 @@ using namespace ib;
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int ld, int V,
                               int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* x = logits + (size_t)blockIdx.x * ld;
@@ -67,6 +69,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int ld, int V,
 // first the best (value, index) of every slice, then the best of those.
 __global__ void argmax_slice_kernel(const float* __restrict__ logits, int ld, int V, int slice,
                                     float* __restrict__ part_val, int* __restrict__ part_idx) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* x = logits + (size_t)blockIdx.x * ld;
@@ -118,6 +122,8 @@ __global__ void argmax_slice_kernel(const float* __restrict__ logits, int ld, in
 __global__ void argmax_merge_kernel(const float* __restrict__ part_val,
                                     const int* __restrict__ part_idx, int n_slices, int V,
                                     int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     // one warp per row
     const int row = blockIdx.x, lane = threadIdx.x;
     float best = -INFINITY;
@@ -160,16 +166,21 @@ IB_EXPORT int ib_argmax(const float* logits, int ld, int n_rows, int V, int* out
     }
     if (slices <= 1) {
         const int threads = V >= 8192 ? 1024 : 256;
-        argmax_kernel<<<n_rows, threads, 0, s>>>(logits, ld, V, out);
+        cudaError_t le = launch_kernel(argmax_kernel, dim3(n_rows), dim3(threads), 0, s, logits, ld, V, out);
+        if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
         return IB_OK;
     }
     const int slice = (V + slices - 1) / slices;
     float* pv = (float*)scratch;
     int* pi = (int*)(pv + (size_t)n_rows * slices);
-    argmax_slice_kernel<<<dim3(n_rows, slices), 256, 0, s>>>(logits, ld, V, slice, pv, pi);
+    cudaError_t le = launch_kernel(argmax_slice_kernel, dim3(n_rows, slices), dim3(256), 0, s, logits, ld, V,
+                                   slice, pv, pi);
+    if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
-    argmax_merge_kernel<<<n_rows, 32, 0, s>>>(pv, pi, slices, V, out);
+    le = launch_kernel(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)pv, (const int*)pi,
+                       slices, V, out);
+    if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;
 }
