@@ -6,15 +6,18 @@
 //     one request times the query heads that share one key/value head - and
 //     walks the keys in tiles of 64; each of its 4 warps owns 16 packed rows.
 //   * split mode (decoded tokens and very short portions): a CTA owns the
-//     (at most 16) packed rows of one request and one slice of its keys; the
-//     4 warps each take 16 keys of every tile and are merged at the end; the
-//     slices of one request are merged by a second small kernel through
+//     (at most 8) packed rows of one request and one slice of its keys.  The
+//     product is turned around so that the many keys, not the few queries,
+//     ride on the 16-wide side of the MMA: S^T = K Q^T (keys x queries) and
+//     O^T = V^T P^T (head dims x queries), with the queries on the 8-wide side.
+//     The 4 warps each take 16 keys of every tile and are merged at the end;
+//     the slices of one request are merged by a second small kernel through
 //     scratch memory.
 // Keys and values are fetched page by page through the request's block table
 // with 16-byte cp.async copies into padded shared-memory rows, two tiles in
 // flight.  Scores, the running maximum, the running sum and the output
-// accumulator are 32-bit; exponentials are exp2f of scores pre-multiplied by
-// log2(e).  Key tiles start at absolute multiples of 64, so the order of the
+// accumulator are 32-bit; exponentials are 2^x (ex2.approx, 32-bit) of scores
+// pre-multiplied by log2(e).  Key tiles start at absolute multiples of 64, so the order of the
 // additions for a query does not depend on how its prompt was cut.
 //
 // Same mathematics as attention_plain.cu (which restates
@@ -53,8 +56,10 @@ struct Params {
     float* part_ml;   // [splits][n_rows][nh][2]
     unsigned* err;
     int q_stride, out_stride, max_blocks, nh, nkv, page_size, num_pages, window;
-    int gs;           // query heads of one kv head handled together (<= 16)
-    int n_hsub;       // ceil((nh / nkv) / gs)
+    int gs;           // tile mode: query heads of one kv head handled together (<= 16)
+    int n_hsub;       // tile mode: ceil((nh / nkv) / gs)
+    int gs_split;     // split mode: the same with at most 8
+    int n_hsub_split;
     int splits;       // split mode: slices of keys per request
     int page_shift;   // log2(page_size) when it is a power of two, else -1
     int n_rows;       // rows of the whole step
@@ -90,6 +95,18 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
         "{%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x in 32-bit with the hardware approximation (relative error about 2^-22).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// Transposes an 8x8 matrix of 16-bit values held one row per 4 lanes.
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
+    unsigned r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+    return r;
 }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -150,8 +167,8 @@ __device__ __forceinline__ void copy_tile(bf16* ks, bf16* vs, const Params& p,
     }
 }
 
-template <bool SPLIT>
-__global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p) {
+// Tile mode.
+__global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_trigger();
     pdl_wait();  // queries, keys and values come from the kernels before this one
@@ -166,25 +183,18 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
     const int row0 = p.cu_rows[e];
     const int rows_e = p.cu_rows[e + 1] - row0;
     const int pos0 = p.q_start[e];
-    const bool small = rows_e * p.gs <= p.small_rows;
-    if (SPLIT != small) return;
+    if (rows_e * p.gs_split <= p.small_rows) return;  // split mode takes this entry
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int* table = p.block_tables + (size_t)e * p.max_blocks;
 
     // ---- which packed rows are mine ----------------------------------------
-    int r_begin, r_count;  // query rows (within the entry) this CTA covers
-    if (SPLIT) {
-        r_begin = 0;
-        r_count = rows_e;
-    } else {
-        const int rq = BN / p.gs;  // rows per CTA: 64 packed rows
-        r_begin = blockIdx.x * rq;
-        if (r_begin >= rows_e) return;
-        r_count = min(rq, rows_e - r_begin);
-    }
-    const int m_base = SPLIT ? 0 : warp * 16;
+    const int rq = BN / p.gs;  // query rows (within the entry) per CTA: 64 packed rows
+    const int r_begin = blockIdx.x * rq;
+    if (r_begin >= rows_e) return;
+    const int r_count = min(rq, rows_e - r_begin);
+    const int m_base = warp * 16;
     int my_row[2], my_head[2], my_pos[2];  // for packed rows gid and gid + 8 of my 16
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -202,12 +212,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
     const int kv_min = p.window > 0 ? max(0, pos0 + r_begin - p.window + 1) : 0;
     const int kv_lo = (kv_min / BN) * BN;
     const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
-    int t_begin = 0, t_end = n_tiles;
-    if (SPLIT) {
-        const int per = (n_tiles + p.splits - 1) / p.splits;
-        t_begin = blockIdx.x * per;
-        t_end = min(n_tiles, t_begin + per);
-    }
+    const int t_begin = 0, t_end = n_tiles;
 
     // ---- queries as A fragments, straight from global memory -------------------
     unsigned qf[HD / 16][4];
@@ -224,8 +229,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
         }
     }
 
-    constexpr int NT = SPLIT ? 2 : 8;           // score tiles of 8 keys per warp
-    const int key_base = SPLIT ? warp * 16 : 0;  // my first key within a tile
+    constexpr int NT = 8;       // score tiles of 8 keys per warp
+    constexpr int key_base = 0;
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -291,7 +296,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
             m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
             m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
             m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];
-            corr[h] = exp2f(m_run[h] - m_use[h]);  // 0 when nothing was seen before
+            corr[h] = fast_exp2(m_run[h] - m_use[h]);  // 0 when nothing was seen before
             m_run[h] = m_new[h];
             l_run[h] *= corr[h];
         }
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int h = i >> 1;
-                const float pv = exp2f(s[n][i] - m_use[h]);
+                const float pv = fast_exp2(s[n][i] - m_use[h]);
                 s[n][i] = pv;
                 l_run[h] += pv;
             }
@@ -341,54 +346,209 @@ __global__ void __launch_bounds__(NTHREADS) attention_mma_kernel(const Params p)
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
 
-    if (!SPLIT) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            if (my_row[h] < 0) continue;
-            const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
-            bf16* dst = p.out + (size_t)my_row[h] * p.out_stride + (size_t)my_head[h] * HD;
-#pragma unroll
-            for (int nt = 0; nt < HD / 8; ++nt) {
-                *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8 + tig * 2) =
-                    __floats2bfloat162_rn(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
-            }
-        }
-        return;
-    }
-
-    // ---- split mode: merge the 4 warps (each saw different keys) -----------------
-    __syncthreads();
-    float* so = reinterpret_cast<float*>(smem_raw);             // [4][16][HD]
-    float* sml = so + 4 * 16 * HD;                              // [4][16][2]
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const int r = gid + 8 * h;
-        float* dst = so + ((size_t)warp * 16 + r) * HD;
+        if (my_row[h] < 0) continue;
+        const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+        bf16* dst = p.out + (size_t)my_row[h] * p.out_stride + (size_t)my_head[h] * HD;
 #pragma unroll
         for (int nt = 0; nt < HD / 8; ++nt) {
-            dst[nt * 8 + tig * 2] = o[nt][2 * h];
-            dst[nt * 8 + tig * 2 + 1] = o[nt][2 * h + 1];
+            *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8 + tig * 2) =
+                __floats2bfloat162_rn(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
         }
-        if (tig == 0) {
-            sml[(warp * 16 + r) * 2] = m_run[h];
-            sml[(warp * 16 + r) * 2 + 1] = l_run[h];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Split mode.  Packed query columns n in [0, 8): n = r * gs + hh (query row r of
+// the entry, head hh of the kv head's group, gs = min(group, 8)).
+//   S^T[key, n]  = sum_d K[key, d] Q[n, d]          M = 16 keys of this warp, N = 8, K = HD
+//   O^T[d, n]   += sum_key V[key, d] P[key, n]      M = HD, N = 8, K = 16 keys
+// K rows feed the A operand through ldmatrix, V rows through ldmatrix.trans,
+// Q sits in registers as the B operand, and P goes from the accumulator layout
+// to the B layout with two movmatrix transposes.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_trigger();
+    pdl_wait();  // queries, keys and values come from the kernels before this one
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    bf16* k_s[2] = {smem, smem + TILE_ELEMS};
+    bf16* v_s[2] = {smem + 2 * TILE_ELEMS, smem + 3 * TILE_ELEMS};
+
+    const int e = blockIdx.y;
+    const int g = blockIdx.z / p.n_hsub_split;
+    const int hsub = blockIdx.z % p.n_hsub_split;
+    const int G = p.nh / p.nkv;
+    const int gs = p.gs_split;
+    const int row0 = p.cu_rows[e];
+    const int rows_e = p.cu_rows[e + 1] - row0;
+    const int pos0 = p.q_start[e];
+    if (rows_e * gs > p.small_rows) return;  // tile mode takes this entry
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int* table = p.block_tables + (size_t)e * p.max_blocks;
+
+    // ---- key range of this slice -------------------------------------------------
+    const int kv_hi = pos0 + rows_e;
+    const int kv_min = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int kv_lo = (kv_min / BN) * BN;
+    const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
+    const int per = (n_tiles + p.splits - 1) / p.splits;
+    const int t_begin = blockIdx.x * per;
+    const int t_end = min(n_tiles, t_begin + per);
+
+    long long off[LOAD_ITERS];
+    if (t_begin < t_end) {
+        locate_tile(off, p, table, g, kv_lo + t_begin * BN, kv_min, kv_hi);
+        copy_tile(k_s[0], v_s[0], p, off);
+    }
+    cp_async_commit();
+    if (t_begin + 1 < t_end) locate_tile(off, p, table, g, kv_lo + (t_begin + 1) * BN, kv_min, kv_hi);
+
+    // ---- queries as B fragments (column n = gid), while the first tile flies ----------
+    unsigned qf[HD / 16][2];
+    {
+        const int r = gid / gs, hh = hsub * gs + gid % gs;
+        const bool ok = r < rows_e && hh < G;
+        const bf16* qp = p.q + (size_t)(row0 + (ok ? r : 0)) * p.q_stride + (size_t)(g * G + (ok ? hh : 0)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            qf[ks][0] = ok ? *reinterpret_cast<const unsigned*>(qp + ks * 16 + tig * 2) : 0u;
+            qf[ks][1] = ok ? *reinterpret_cast<const unsigned*>(qp + ks * 16 + 8 + tig * 2) : 0u;
+        }
+    }
+    // positions of my two score columns (n = tig*2, tig*2 + 1); -1: not a query
+    int col_pos[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int n = tig * 2 + h;
+        const int r = n / gs, hh = hsub * gs + n % gs;
+        col_pos[h] = (r < rows_e && hh < G) ? pos0 + r : -1;
+    }
+
+    float o[HD / 16][4];  // O^T: rows = head dims, my columns tig*2, tig*2 + 1
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int key_base = warp * 16;
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, off);
+        cp_async_commit();
+        if (t + 2 < t_end) locate_tile(off, p, table, g, kv_lo + (t + 2) * BN, kv_min, kv_hi);
+        cp_async_wait<1>();
+        __syncthreads();
+
+        const int tile_start = kv_lo + t * BN;
+        const bf16* ks_ = k_s[stage];
+        const bf16* vs_ = v_s[stage];
+
+        // S^T for my 16 keys
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            unsigned a[4];
+            const int key = key_base + (lane & 7) + 8 * ((lane >> 3) & 1);
+            const int dim = ks * 16 + 8 * (lane >> 4);
+            ldmatrix_x4(a[0], a[1], a[2], a[3], ks_ + key * LDS + dim);
+            mma_bf16(sc, a, qf[ks][0], qf[ks][1]);
+        }
+        // mask and scale: sc[0], sc[1] belong to key gid, sc[2], sc[3] to key gid + 8
+        float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = i & 1;
+            const int key = tile_start + key_base + gid + 8 * (i >> 1);
+            const bool ok = key <= col_pos[h] && (p.window <= 0 || key > col_pos[h] - p.window);
+            sc[i] = ok ? sc[i] * p.scale_log2 : -INFINITY;
+            m_new[h] = fmaxf(m_new[h], sc[i]);
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            // the keys of a column are spread over the lanes with the same tig
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 4));
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 8));
+            m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 16));
+            m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];
+            corr[h] = fast_exp2(m_run[h] - m_use[h]);
+            m_run[h] = m_new[h];
+            l_run[h] *= corr[h];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            sc[i] = fast_exp2(sc[i] - m_use[i & 1]);
+            l_run[i & 1] += sc[i];
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 16; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[1];
+            o[i][2] *= corr[0];
+            o[i][3] *= corr[1];
+        }
+        // P^T as the B operand: (keys tig*2, tig*2+1 ; column gid), then keys + 8
+        const unsigned b0 = movmatrix_trans(pack_bf16(sc[0], sc[1]));
+        const unsigned b1 = movmatrix_trans(pack_bf16(sc[2], sc[3]));
+        // O^T += V^T P^T
+#pragma unroll
+        for (int mt = 0; mt < HD / 16; ++mt) {
+            unsigned a[4];
+            const int mi = lane >> 3;
+            const int key = key_base + (lane & 7) + 8 * (mi >> 1);
+            const int dim = mt * 16 + 8 * (mi & 1);
+            ldmatrix_x4_trans(a[0], a[1], a[2], a[3], vs_ + key * LDS + dim);
+            mma_bf16(o[mt], a, b0, b1);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
+    }
+
+    // ---- merge the 4 warps (each saw different keys) -----------------------------
+    __syncthreads();
+    float* so = reinterpret_cast<float*>(smem_raw);   // [4][8][HD]
+    float* sml = so + 4 * 8 * HD;                     // [4][8][2]
+#pragma unroll
+    for (int mt = 0; mt < HD / 16; ++mt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int n = tig * 2 + (i & 1);
+            const int d = mt * 16 + gid + 8 * (i >> 1);
+            so[((size_t)warp * 8 + n) * HD + d] = o[mt][i];
+        }
+    }
+    if (gid == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            sml[(warp * 8 + tig * 2 + h) * 2] = m_run[h];
+            sml[(warp * 8 + tig * 2 + h) * 2 + 1] = l_run[h];
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 16 * HD; idx += NTHREADS) {
-        const int m = idx / HD, d = idx % HD;
-        const int r = m / p.gs, hh = hsub * p.gs + m % p.gs;
+    for (int idx = threadIdx.x; idx < 8 * HD; idx += NTHREADS) {
+        const int n = idx / HD, d = idx % HD;
+        const int r = n / gs, hh = hsub * gs + n % gs;
         if (r >= rows_e || hh >= G) continue;
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, sml[(w * 16 + m) * 2]);
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, sml[(w * 8 + n) * 2]);
         float acc = 0.f, l = 0.f;
         if (mx > -INFINITY) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float f = exp2f(sml[(w * 16 + m) * 2] - mx);
-                acc += f * so[((size_t)w * 16 + m) * HD + d];
-                l += f * sml[(w * 16 + m) * 2 + 1];
+                const float f = fast_exp2(sml[(w * 8 + n) * 2] - mx);
+                acc += f * so[((size_t)w * 8 + n) * HD + d];
+                l += f * sml[(w * 8 + n) * 2 + 1];
             }
         }
         const int grow = row0 + r, head = g * G + hh;
@@ -439,10 +599,10 @@ IB_EXPORT long long ib_attention_mma_scratch_bytes(int n_rows, int nh, int split
     return (long long)splits * n_rows * nh * (HD + 2) * (long long)sizeof(float);
 }
 
-// mode bits: 1 = launch tile mode (entries with rows * gs > 16),
-//            2 = launch split mode (entries with rows * gs <= 16).
-// When only one bit is set, every entry is taken by that mode, except that
-// split mode can never take an entry with more than 16 packed rows.
+// mode bits: 1 = launch tile mode, 2 = launch split mode.  With both, an entry
+// whose rows times min(group, 8) is at most 8 goes to split mode and the rest
+// to tile mode; with one bit every entry is taken by that mode, except that
+// split mode can never take an entry with more than 8 packed rows.
 IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                void* out, int out_stride, const int* cu_rows, const int* q_start,
                                const int* block_tables, int max_blocks, int n_entries, int n_rows,
@@ -483,23 +643,25 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     const int G = nh / nkv;
     p.gs = G < 16 ? G : 16;
     p.n_hsub = (G + p.gs - 1) / p.gs;
+    p.gs_split = G < 8 ? G : 8;
+    p.n_hsub_split = (G + p.gs_split - 1) / p.gs_split;
     p.splits = splits;
     p.n_rows = n_rows;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.part_o = nullptr;
     p.part_ml = nullptr;
     // which entries each mode takes
-    if ((mode & 3) == 3) p.small_rows = 16;
+    if ((mode & 3) == 3) p.small_rows = 8;
     else if (mode & 2) p.small_rows = 1 << 30;   // everything is "small"
     else p.small_rows = -1;                      // nothing is "small"
-    if ((mode & 2) && !(mode & 1) && max_rows_per_entry * p.gs > 16) return IB_ERR_BAD_ARG;
+    if ((mode & 2) && !(mode & 1) && max_rows_per_entry * p.gs_split > 8) return IB_ERR_BAD_ARG;
     if (n_entries > 65535 || nkv * p.n_hsub > 65535) return IB_ERR_TOO_LARGE;
 
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e1 = cudaFuncSetAttribute(attention_mma_kernel<false>,
+        cudaError_t e1 = cudaFuncSetAttribute(attention_tile_kernel,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        cudaError_t e2 = cudaFuncSetAttribute(attention_mma_kernel<true>,
+        cudaError_t e2 = cudaFuncSetAttribute(attention_split_kernel,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e1 != cudaSuccess) return (int)e1;
         if (e2 != cudaSuccess) return (int)e2;
@@ -508,7 +670,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     if (mode & 1) {
         const int rq = BN / p.gs;
         dim3 grid((max_rows_per_entry + rq - 1) / rq, n_entries, nkv * p.n_hsub);
-        cudaError_t le = launch_kernel(attention_mma_kernel<false>, grid, dim3(NTHREADS), SMEM_BYTES, s, p);
+        cudaError_t le = launch_kernel(attention_tile_kernel, grid, dim3(NTHREADS), SMEM_BYTES, s, p);
         if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
     }
@@ -519,8 +681,8 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
             p.part_o = (float*)scratch;
             p.part_ml = p.part_o + (size_t)splits * n_rows * nh * HD;
         }
-        dim3 grid(splits, n_entries, nkv * p.n_hsub);
-        cudaError_t le = launch_kernel(attention_mma_kernel<true>, grid, dim3(NTHREADS), SMEM_BYTES, s, p);
+        dim3 grid(splits, n_entries, nkv * p.n_hsub_split);
+        cudaError_t le = launch_kernel(attention_split_kernel, grid, dim3(NTHREADS), SMEM_BYTES, s, p);
         if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
         if (splits > 1) {

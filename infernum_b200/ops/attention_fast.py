@@ -2,7 +2,7 @@
 compiled module per head size, built when a model first needs it.
 
 ``run`` picks how the step's entries are spread: entries whose query rows
-times grouped heads fit 16 packed rows (decoded tokens, very short portions)
+times grouped heads fit 8 packed rows (decoded tokens, very short portions)
 go to split mode, where the keys of a request are cut in slices over several
 CTAs and merged through scratch memory; longer portions go to tile mode.  It
 returns False when there is no variant for the head size, and the caller then
@@ -48,10 +48,13 @@ def lib_for(head_dim: int) -> ctypes.CDLL:
 
 
 def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count: int) -> int:
-    """Slices per request so that about two CTAs per SM exist, each with at
-    least two key tiles of 64."""
+    """Slices per request.  Three CTAs fit an SM; with fewer than about four
+    rounds of CTAs the last, partly filled round costs as much as a full one
+    (64 requests x 8 kv heads = 512 CTAs on 444 places took two rounds), so
+    requests are cut until there are at least four rounds, each slice keeping
+    at least two key tiles of 64."""
     base = max(1, n_entries * kv_heads_x_sub)
-    want = -(-2 * sm_count // base)
+    want = -(-4 * 3 * sm_count // base)
     tiles = -(-max_kv_len // 64)
     return max(1, min(want, max(1, tiles // 2), 32))
 
@@ -67,9 +70,9 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
             or k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_mma: bfloat16 tensors with unit inner stride are required")
     G = n_heads // nkv
-    gs = min(G, 16)
+    gs = min(G, 8)  # split mode packs rows x grouped heads on the 8-wide side of the MMA
     n_hsub = -(-G // gs)
-    small_limit = 16 // gs  # rows an entry may have to go to split mode
+    small_limit = 8 // gs  # rows an entry may have to go to split mode
     forced = getattr(ctx, "attention_mode", None)
     if forced is not None:
         mode, splits = forced
