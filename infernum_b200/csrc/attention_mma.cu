@@ -117,51 +117,46 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // c = tid + 128 * i, i < LOAD_ITERS, is row c / CH, column c % CH.
 constexpr int LOAD_ITERS = (BN * CH + NTHREADS - 1) / NTHREADS;
 
-// Element offset (into a pool) of key j of kv head g, or -1 when the key lies
-// outside [kv_min, kv_hi) or its block-table entry is not a page of the pool
-// (pages below kv_min may already have been given back by a window).
-__device__ __forceinline__ long long key_offset(const Params& p, const int* table, int g, int j,
-                                                int kv_min, int kv_hi) {
-    if (j < kv_min || j >= kv_hi) return -1;
-    int pi, slot;
-    if (p.page_shift >= 0) {
-        pi = j >> p.page_shift;
-        slot = j & (p.page_size - 1);
-    } else {
-        pi = j / p.page_size;
-        slot = j - pi * p.page_size;
-    }
-    const int page = table[pi];
-    if (page < 0 || page >= p.num_pages) {
-        atomicOr(p.err, IB_FLAG_BAD_PAGE);
-        return -1;
-    }
-    return (((long long)page * p.nkv + g) * p.page_size + slot) * HD;
-}
+// Where this thread's rows of a tile live: the raw block-table entries.  The
+// loads are issued here and first used by copy_tile one iteration later, so
+// their latency is off the critical path.  (Nothing here may depend on the
+// loaded value, or the wait for it would move here.)
+struct TileRows {
+    int page[LOAD_ITERS];   // block-table entry of the row's page (unchecked)
+    int tile_start;
+};
 
-// Looks up where this thread's rows of a tile live (one block-table read per
-// row, all issued together so that their latencies overlap).
-__device__ __forceinline__ void locate_tile(long long (&off)[LOAD_ITERS], const Params& p,
-                                            const int* table, int g, int tile_start, int kv_min,
-                                            int kv_hi) {
+__device__ __forceinline__ void locate_tile(TileRows& tr, const Params& p, const int* table,
+                                            int tile_start) {
+    tr.tile_start = tile_start;
 #pragma unroll
     for (int i = 0; i < LOAD_ITERS; ++i) {
         const int c = threadIdx.x + NTHREADS * i;
-        off[i] = c < BN * CH ? key_offset(p, table, g, tile_start + c / CH, kv_min, kv_hi) : -1;
+        const int j = tile_start + c / CH;
+        int pi = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
+        pi = min(pi, p.max_blocks - 1);
+        tr.page[i] = table[pi];
     }
 }
 
-// Copies one tile into a stage from the offsets found by locate_tile; rows
-// without a valid offset are zero-filled.
-__device__ __forceinline__ void copy_tile(bf16* ks, bf16* vs, const Params& p,
-                                          const long long (&off)[LOAD_ITERS]) {
+// Copies one tile into a stage.  Rows outside [kv_min, kv_hi) - pages below
+// kv_min may already have been given back by a window - and rows whose
+// block-table entry is not a page of the pool are zero-filled.
+__device__ __forceinline__ void copy_tile(bf16* ks, bf16* vs, const Params& p, const TileRows& tr,
+                                          int g, int kv_min, int kv_hi) {
 #pragma unroll
     for (int i = 0; i < LOAD_ITERS; ++i) {
         const int c = threadIdx.x + NTHREADS * i;
         if (c >= BN * CH) break;
         const int row = c / CH, ch = c % CH;
-        const bool ok = off[i] >= 0;
-        const size_t src = ok ? (size_t)off[i] + ch * 8 : 0;
+        const int j = tr.tile_start + row;
+        const int slot = p.page_shift >= 0 ? (j & (p.page_size - 1)) : (j % p.page_size);
+        const int page = tr.page[i];
+        const bool in_range = j >= kv_min && j < kv_hi;
+        const bool ok = in_range && page >= 0 && page < p.num_pages;
+        if (in_range && !ok) atomicOr(p.err, IB_FLAG_BAD_PAGE);
+        const size_t src =
+            ok ? ((((size_t)page * p.nkv + g) * p.page_size + slot) * HD + ch * 8) : 0;
         cp_async_16(ks + row * LDS + ch * 8, p.k_pool + src, ok ? 16 : 0);
         cp_async_16(vs + row * LDS + ch * 8, p.v_pool + src, ok ? 16 : 0);
     }
@@ -191,7 +186,9 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
 
     // ---- which packed rows are mine ----------------------------------------
     const int rq = BN / p.gs;  // query rows (within the entry) per CTA: 64 packed rows
-    const int r_begin = blockIdx.x * rq;
+    // the last rows of a prompt see the most keys: their CTAs go first, so the
+    // long ones do not straggle at the end of the grid
+    const int r_begin = ((int)gridDim.x - 1 - (int)blockIdx.x) * rq;
     if (r_begin >= rows_e) return;
     const int r_count = min(rq, rows_e - r_begin);
     const int m_base = warp * 16;
@@ -239,19 +236,19 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
     // The copies of tile t+1 are issued while tile t is computed, and the
     // block-table reads for tile t+2 are issued before that, so neither latency
     // sits on the critical path.
-    long long off[LOAD_ITERS];
+    TileRows tr;
     if (t_begin < t_end) {
-        locate_tile(off, p, table, g, kv_lo + t_begin * BN, kv_min, kv_hi);
-        copy_tile(k_s[0], v_s[0], p, off);
+        locate_tile(tr, p, table, kv_lo + t_begin * BN);
+        copy_tile(k_s[0], v_s[0], p, tr, g, kv_min, kv_hi);
     }
     cp_async_commit();
-    if (t_begin + 1 < t_end) locate_tile(off, p, table, g, kv_lo + (t_begin + 1) * BN, kv_min, kv_hi);
+    if (t_begin + 1 < t_end) locate_tile(tr, p, table, kv_lo + (t_begin + 1) * BN);
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) & 1;
-        if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, off);
+        if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, tr, g, kv_min, kv_hi);
         cp_async_commit();
-        if (t + 2 < t_end) locate_tile(off, p, table, g, kv_lo + (t + 2) * BN, kv_min, kv_hi);
+        if (t + 2 < t_end) locate_tile(tr, p, table, kv_lo + (t + 2) * BN);
         cp_async_wait<1>();
         __syncthreads();
 
@@ -276,18 +273,31 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
             }
         }
 
-        // mask, scale, online softmax (per thread: rows gid and gid + 8)
+        // mask, scale, online softmax (per thread: rows gid and gid + 8).  Tiles
+        // wholly below the diagonal of every row of this CTA need no mask.
         float m_new[2] = {m_run[0], m_run[1]};
+        const bool need_mask = p.window > 0 || tile_start + BN - 1 > pos0 + r_begin;
+        if (need_mask) {
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
+            for (int n = 0; n < NT; ++n) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int h = i >> 1;
-                const int key = tile_start + key_base + n * 8 + tig * 2 + (i & 1);
-                const bool ok = key <= my_pos[h] && (p.window <= 0 || key > my_pos[h] - p.window);
-                const float v = ok ? s[n][i] * p.scale_log2 : -INFINITY;
-                s[n][i] = v;
-                m_new[h] = fmaxf(m_new[h], v);
+                for (int i = 0; i < 4; ++i) {
+                    const int h = i >> 1;
+                    const int key = tile_start + key_base + n * 8 + tig * 2 + (i & 1);
+                    const bool ok = key <= my_pos[h] && (p.window <= 0 || key > my_pos[h] - p.window);
+                    const float v = ok ? s[n][i] * p.scale_log2 : -INFINITY;
+                    s[n][i] = v;
+                    m_new[h] = fmaxf(m_new[h], v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    s[n][i] *= p.scale_log2;
+                    m_new[i >> 1] = fmaxf(m_new[i >> 1], s[n][i]);
+                }
             }
         }
         float corr[2], m_use[2];
@@ -399,13 +409,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
     const int t_begin = blockIdx.x * per;
     const int t_end = min(n_tiles, t_begin + per);
 
-    long long off[LOAD_ITERS];
+    TileRows tr;
     if (t_begin < t_end) {
-        locate_tile(off, p, table, g, kv_lo + t_begin * BN, kv_min, kv_hi);
-        copy_tile(k_s[0], v_s[0], p, off);
+        locate_tile(tr, p, table, kv_lo + t_begin * BN);
+        copy_tile(k_s[0], v_s[0], p, tr, g, kv_min, kv_hi);
     }
     cp_async_commit();
-    if (t_begin + 1 < t_end) locate_tile(off, p, table, g, kv_lo + (t_begin + 1) * BN, kv_min, kv_hi);
+    if (t_begin + 1 < t_end) locate_tile(tr, p, table, kv_lo + (t_begin + 1) * BN);
 
     // ---- queries as B fragments (column n = gid), while the first tile flies ----------
     unsigned qf[HD / 16][2];
@@ -436,9 +446,9 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) & 1;
-        if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, off);
+        if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, tr, g, kv_min, kv_hi);
         cp_async_commit();
-        if (t + 2 < t_end) locate_tile(off, p, table, g, kv_lo + (t + 2) * BN, kv_min, kv_hi);
+        if (t + 2 < t_end) locate_tile(tr, p, table, kv_lo + (t + 2) * BN);
         cp_async_wait<1>();
         __syncthreads();
 

@@ -342,6 +342,82 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int qkv_stride,
     }
 }
 
+// bf16 variant that moves 16 bytes at a time: an item is 8 consecutive pairs
+// (elements j..j+7 and j+rd/2..j+rd/2+7 of one head), 8 unrotated elements, or
+// 8 elements of v.  Needs rd % 16 == 0, hd % 8 == 0 and 16-byte aligned rows.
+__global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
+                                        const int* __restrict__ positions,
+                                        const int* __restrict__ row_entry,
+                                        const int* __restrict__ block_tables, int max_blocks,
+                                        const float* __restrict__ inv_freq, bf16* __restrict__ k_pool,
+                                        bf16* __restrict__ v_pool, int nh, int nkv, int hd, int rd,
+                                        int page_size, int num_pages, int write_kv,
+                                        unsigned* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int rot_items = rd >> 4;             // per head: items of 8 pairs
+    const int pass_items = (hd - rd) >> 3;     // per head: items of 8 unrotated elements
+    const int per_head = rot_items + pass_items;
+    const int items_qk = (nh + nkv) * per_head;
+    const int v_items = write_kv ? nkv * (hd >> 3) : 0;
+    const int items = items_qk + v_items;
+    const int pos = positions[row];
+    bf16* base = qkv + (size_t)row * qkv_stride;
+
+    long long slot_base = -1;
+    if (write_kv) {
+        const int e = row_entry[row];
+        const int page = block_tables[(size_t)e * max_blocks + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
+        } else {
+            slot_base = ((long long)page * nkv * page_size + (pos % page_size)) * hd;
+        }
+    }
+    const long long head_step = (long long)page_size * hd;
+    const int half = rd >> 1;
+
+    for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < items; it += gridDim.y * blockDim.x) {
+        if (it < items_qk) {
+            const int head = it / per_head, p = it % per_head;
+            bf16* x = base + (size_t)head * hd;
+            bf16* dst = (head >= nh && slot_base >= 0)
+                            ? k_pool + slot_base + (long long)(head - nh) * head_step : nullptr;
+            if (p < rot_items) {
+                const int j = p << 3;
+                uint4 a4 = *reinterpret_cast<const uint4*>(x + j);
+                uint4 b4 = *reinterpret_cast<const uint4*>(x + j + half);
+                __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a4);
+                __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b4);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 xa = __bfloat1622float2(a2[k]), xb = __bfloat1622float2(b2[k]);
+                    float s0, c0, s1, c1;
+                    sincosf((float)pos * inv_freq[j + 2 * k], &s0, &c0);
+                    sincosf((float)pos * inv_freq[j + 2 * k + 1], &s1, &c1);
+                    a2[k] = __floats2bfloat162_rn(xa.x * c0 - xb.x * s0, xa.y * c1 - xb.y * s1);
+                    b2[k] = __floats2bfloat162_rn(xa.x * s0 + xb.x * c0, xa.y * s1 + xb.y * c1);
+                }
+                *reinterpret_cast<uint4*>(x + j) = a4;
+                *reinterpret_cast<uint4*>(x + j + half) = b4;
+                if (dst) {
+                    *reinterpret_cast<uint4*>(dst + j) = a4;
+                    *reinterpret_cast<uint4*>(dst + j + half) = b4;
+                }
+            } else if (dst) {
+                const int d0 = rd + ((p - rot_items) << 3);
+                *reinterpret_cast<uint4*>(dst + d0) = *reinterpret_cast<const uint4*>(x + d0);
+            }
+        } else if (slot_base >= 0) {
+            const int vi = it - items_qk;
+            const int g = vi / (hd >> 3), d0 = (vi % (hd >> 3)) << 3;
+            *reinterpret_cast<uint4*>(v_pool + slot_base + (long long)g * head_step + d0) =
+                *reinterpret_cast<const uint4*>(base + (size_t)(nh + nkv + g) * hd + d0);
+        }
+    }
+}
+
 IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int* positions,
                              const int* row_entry, const int* block_tables, int max_blocks,
                              const float* inv_freq, void* k_pool, void* v_pool, int n_rows, int nh,
@@ -361,6 +437,19 @@ IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int
     const int threads = 128;
     int by = (items + threads - 1) / threads;
     if (by > 16) by = 16;
+    if (act_dtype == 1 && rd % 16 == 0 && hd % 8 == 0 && qkv_stride % 8 == 0 &&
+        !(((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15)) {
+        const int vitems = (nh + nkv) * ((rd >> 4) + ((hd - rd) >> 3)) + (write_kv ? nkv * (hd >> 3) : 0);
+        int vby = (vitems + threads - 1) / threads;
+        if (vby > 8) vby = 8;
+        cudaError_t le = launch_kernel(rope_append_vec8_kernel, dim3(n_rows, vby), dim3(threads), 0, s,
+                                       (bf16*)qkv, qkv_stride, positions, row_entry, block_tables,
+                                       max_blocks, inv_freq, (bf16*)k_pool, (bf16*)v_pool, nh, nkv, hd,
+                                       rd, page_size, num_pages, write_kv, err);
+        if (le != cudaSuccess) return (int)le;
+        IB_LAUNCH_CHECK();
+        return IB_OK;
+    }
     dim3 grid(n_rows, by);
     if (act_dtype == 0)
         { cudaError_t le__ = launch_kernel(rope_append_kernel<float>, dim3(grid), dim3(threads), 0, s, 
@@ -393,18 +482,55 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
     out[idx] = from_f32<T>(act * u);
 }
 
+// Eight outputs per thread with 16-byte loads and stores (I % 8 == 0).
+__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int I,
+                                     size_t total_vec) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= total_vec) return;
+    const int per_row = I >> 3;
+    const size_t row = v / per_row;
+    const int i = (int)(v % per_row) << 3;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(x + row * 2 * I + i);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(x + row * 2 * I + I + i);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+        o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + row * I + i) = o4;
+}
+
 IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, int I, void* stream) {
     if (n_rows <= 0) return IB_OK;
     if (!x || !out || I <= 0) return IB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)n_rows * I;
+    if (act_dtype == 1 && I % 8 == 0 && !(((uintptr_t)x | (uintptr_t)out) & 15)) {
+        const size_t total_vec = total / 8;
+        cudaError_t le = launch_kernel(silu_mul_vec8_kernel, dim3((unsigned)((total_vec + 255) / 256)),
+                                       dim3(256), 0, s, (const bf16*)x, (bf16*)out, I, total_vec);
+        if (le != cudaSuccess) return (int)le;
+        IB_LAUNCH_CHECK();
+        return IB_OK;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (act_dtype == 0)
-        { cudaError_t le__ = launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)x, (float*)out, I, total); if (le__ != cudaSuccess) return (int)le__; }
-    else if (act_dtype == 1)
-        { cudaError_t le__ = launch_kernel(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)x, (bf16*)out, I, total); if (le__ != cudaSuccess) return (int)le__; }
-    else
+    if (act_dtype == 0) {
+        cudaError_t le = launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s,
+                                       (const float*)x, (float*)out, I, total);
+        if (le != cudaSuccess) return (int)le;
+    } else if (act_dtype == 1) {
+        cudaError_t le = launch_kernel(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s,
+                                       (const bf16*)x, (bf16*)out, I, total);
+        if (le != cudaSuccess) return (int)le;
+    } else {
         return IB_ERR_UNSUPPORTED;
+    }
     IB_LAUNCH_CHECK();
     return IB_OK;
 }
