@@ -42,7 +42,9 @@ constexpr int LDS = HD + 8;       // padded row length (elements): conflict-free
 constexpr int CH = HD / 8;        // 16-byte chunks per row
 constexpr int NTHREADS = 128;
 constexpr int TILE_ELEMS = BN * LDS;
-constexpr int SMEM_BYTES = 4 * TILE_ELEMS * 2;  // K and V, two stages
+constexpr int SMEM_BYTES = 4 * TILE_ELEMS * 2;  // tile mode: K and V, two stages
+constexpr int SPLIT_STAGES = 3;
+constexpr int SPLIT_SMEM_BYTES = SPLIT_STAGES * 2 * TILE_ELEMS * 2;
 
 struct Params {
     const bf16* q;
@@ -383,8 +385,9 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
     pdl_trigger();
     pdl_wait();  // queries, keys and values come from the kernels before this one
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    bf16* k_s[2] = {smem, smem + TILE_ELEMS};
-    bf16* v_s[2] = {smem + 2 * TILE_ELEMS, smem + 3 * TILE_ELEMS};
+    // a ring of SPLIT_STAGES stages, each one K tile followed by one V tile
+    auto k_stage = [&](int st) { return smem + (size_t)st * 2 * TILE_ELEMS; };
+    auto v_stage = [&](int st) { return smem + (size_t)st * 2 * TILE_ELEMS + TILE_ELEMS; };
 
     const int e = blockIdx.y;
     const int g = blockIdx.z / p.n_hsub_split;
@@ -409,13 +412,19 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
     const int t_begin = blockIdx.x * per;
     const int t_end = min(n_tiles, t_begin + per);
 
+    // Two tiles are in flight while a third is computed: with little arithmetic
+    // per byte, what limits this kernel is how many bytes each SM has under way.
     TileRows tr;
-    if (t_begin < t_end) {
-        locate_tile(tr, p, table, kv_lo + t_begin * BN);
-        copy_tile(k_s[0], v_s[0], p, tr, g, kv_min, kv_hi);
+#pragma unroll
+    for (int pre = 0; pre < SPLIT_STAGES - 1; ++pre) {
+        if (t_begin + pre < t_end) {
+            locate_tile(tr, p, table, kv_lo + (t_begin + pre) * BN);
+            copy_tile(k_stage(pre), v_stage(pre), p, tr, g, kv_min, kv_hi);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
-    if (t_begin + 1 < t_end) locate_tile(tr, p, table, kv_lo + (t_begin + 1) * BN);
+    if (t_begin + SPLIT_STAGES - 1 < t_end)
+        locate_tile(tr, p, table, kv_lo + (t_begin + SPLIT_STAGES - 1) * BN);
 
     // ---- queries as B fragments (column n = gid), while the first tile flies ----------
     unsigned qf[HD / 16][2];
@@ -445,16 +454,19 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
     const int key_base = warp * 16;
 
     for (int t = t_begin; t < t_end; ++t) {
-        const int stage = (t - t_begin) & 1;
-        if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, tr, g, kv_min, kv_hi);
+        const int stage = (t - t_begin) % SPLIT_STAGES;
+        cp_async_wait<SPLIT_STAGES - 2>();  // tile t has landed
+        __syncthreads();                    // and everyone is done with tile t - 1
+        if (t + SPLIT_STAGES - 1 < t_end) {
+            const int nst = (t - t_begin + SPLIT_STAGES - 1) % SPLIT_STAGES;  // the stage of tile t - 1
+            copy_tile(k_stage(nst), v_stage(nst), p, tr, g, kv_min, kv_hi);
+        }
         cp_async_commit();
-        if (t + 2 < t_end) locate_tile(tr, p, table, kv_lo + (t + 2) * BN);
-        cp_async_wait<1>();
-        __syncthreads();
+        if (t + SPLIT_STAGES < t_end) locate_tile(tr, p, table, kv_lo + (t + SPLIT_STAGES) * BN);
 
         const int tile_start = kv_lo + t * BN;
-        const bf16* ks_ = k_s[stage];
-        const bf16* vs_ = v_s[stage];
+        const bf16* ks_ = k_stage(stage);
+        const bf16* vs_ = v_stage(stage);
 
         // S^T for my 16 keys
         float sc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -513,7 +525,6 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
             ldmatrix_x4_trans(a[0], a[1], a[2], a[3], vs_ + key * LDS + dim);
             mma_bf16(o[mt], a, b0, b1);
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
 
@@ -672,7 +683,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
         cudaError_t e1 = cudaFuncSetAttribute(attention_tile_kernel,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaError_t e2 = cudaFuncSetAttribute(attention_split_kernel,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SPLIT_SMEM_BYTES);
         if (e1 != cudaSuccess) return (int)e1;
         if (e2 != cudaSuccess) return (int)e2;
         attr_done = true;
@@ -692,7 +703,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
             p.part_ml = p.part_o + (size_t)splits * n_rows * nh * HD;
         }
         dim3 grid(splits, n_entries, nkv * p.n_hsub_split);
-        cudaError_t le = launch_kernel(attention_split_kernel, grid, dim3(NTHREADS), SMEM_BYTES, s, p);
+        cudaError_t le = launch_kernel(attention_split_kernel, grid, dim3(NTHREADS), SPLIT_SMEM_BYTES, s, p);
         if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
         if (splits > 1) {

@@ -48,15 +48,19 @@ def lib_for(head_dim: int) -> ctypes.CDLL:
 
 
 def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count: int) -> int:
-    """Slices per request.  Three CTAs fit an SM; with fewer than about four
-    rounds of CTAs the last, partly filled round costs as much as a full one
-    (64 requests x 8 kv heads = 512 CTAs on 444 places took two rounds), so
-    requests are cut until there are at least four rounds, each slice keeping
-    at least two key tiles of 64."""
+    """Slices per request, by a small cost model.  Two CTAs fit an SM (three
+    stages of keys and values each), CTAs run in rounds of ``2 * sm_count``,
+    and a CTA costs its key tiles plus about three tiles' worth of start-up and
+    merging; the slice count with the cheapest rounds x cost wins."""
     base = max(1, n_entries * kv_heads_x_sub)
-    want = -(-4 * 3 * sm_count // base)
-    tiles = -(-max_kv_len // 64)
-    return max(1, min(want, max(1, tiles // 2), 32))
+    slots = 2 * sm_count
+    tiles = max(1, -(-max_kv_len // 64))
+    best, best_cost = 1, None
+    for s in range(1, min(32, tiles) + 1):
+        cost = -(-base * s // slots) * (-(-tiles // s) + 3)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool:
