@@ -10,9 +10,10 @@
 //     product is turned around so that the many keys, not the few queries,
 //     ride on the 16-wide side of the MMA: S^T = K Q^T (keys x queries) and
 //     O^T = V^T P^T (head dims x queries), with the queries on the 8-wide side.
-//     The 4 warps each take 16 keys of every tile and are merged at the end;
-//     the slices of one request are merged by a second small kernel through
-//     scratch memory.
+//     The 4 warps each take 16 keys of every tile and are merged at the end.
+//     Up to 8 slices of one request are the CTAs of one thread-block cluster
+//     and are merged through distributed shared memory; more slices are merged
+//     by a second small kernel through scratch memory.
 // Keys and values are fetched page by page through the request's block table
 // with 16-byte cp.async copies into padded shared-memory rows, two tiles in
 // flight.  Scores, the running maximum, the running sum and the output
@@ -66,6 +67,7 @@ struct Params {
     int page_shift;   // log2(page_size) when it is a power of two, else -1
     int n_rows;       // rows of the whole step
     int small_rows;   // an entry with rows * gs <= small_rows belongs to split mode
+    int cluster_merge;  // split mode: the slices of a request are the CTAs of one cluster
     float scale_log2;
 };
 
@@ -97,6 +99,19 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
         "{%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Reads a float from the shared memory of CTA `rank` of this cluster, at the
+// address `local` has in this CTA.
+__device__ __forceinline__ float ld_peer_smem(const float* local, unsigned rank) {
+    unsigned laddr = (unsigned)__cvta_generic_to_shared(local), raddr;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(raddr) : "r"(laddr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
 }
 // 2^x in 32-bit with the hardware approximation (relative error about 2^-22).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -539,6 +554,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
     __syncthreads();
     float* so = reinterpret_cast<float*>(smem_raw);   // [4][8][HD]
     float* sml = so + 4 * 8 * HD;                     // [4][8][2]
+    float* fin = sml + 4 * 8 * 2;                     // [8][HD]   this CTA's result (cluster merge)
+    float* finml = fin + 8 * HD;                      // [8][2]
 #pragma unroll
     for (int mt = 0; mt < HD / 16; ++mt) {
 #pragma unroll
@@ -576,6 +593,12 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
         if (p.splits == 1) {
             p.out[(size_t)grow * p.out_stride + (size_t)head * HD + d] =
                 __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else if (p.cluster_merge) {
+            fin[n * HD + d] = acc;
+            if (d == 0) {
+                finml[n * 2] = mx;
+                finml[n * 2 + 1] = l;
+            }
         } else {
             const size_t base = ((size_t)blockIdx.x * p.n_rows + grow) * p.nh + head;
             p.part_o[base * HD + d] = acc;
@@ -584,6 +607,35 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
                 p.part_ml[base * 2 + 1] = l;
             }
         }
+    }
+    if (p.splits > 1 && p.cluster_merge) {
+        // The slices of this request are the CTAs of my cluster.  Each has its
+        // result in its own shared memory; after a cluster barrier each CTA merges
+        // a share of the (column, dim) elements over all slices, in slice order,
+        // reading the peers' shared memory directly.
+        cluster_sync_all();
+        const int total = 8 * HD;
+        const int share = (total + p.splits - 1) / p.splits;
+        const int begin = (int)blockIdx.x * share, end = min(total, begin + share);
+        for (int idx = begin + threadIdx.x; idx < end; idx += NTHREADS) {
+            const int n = idx / HD, d = idx % HD;
+            const int r = n / gs, hh = hsub * gs + n % gs;
+            if (r >= rows_e || hh >= G) continue;
+            float mx = -INFINITY;
+            for (int sidx = 0; sidx < p.splits; ++sidx)
+                mx = fmaxf(mx, ld_peer_smem(finml + n * 2, (unsigned)sidx));
+            float acc = 0.f, l = 0.f;
+            if (mx > -INFINITY) {
+                for (int sidx = 0; sidx < p.splits; ++sidx) {
+                    const float f = fast_exp2(ld_peer_smem(finml + n * 2, (unsigned)sidx) - mx);
+                    acc += f * ld_peer_smem(fin + n * HD + d, (unsigned)sidx);
+                    l += f * ld_peer_smem(finml + n * 2 + 1, (unsigned)sidx);
+                }
+            }
+            p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(g * G + hh) * HD + d] =
+                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        }
+        cluster_sync_all();  // nobody leaves while a peer may still read its result
     }
 }
 
@@ -671,6 +723,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.part_o = nullptr;
     p.part_ml = nullptr;
+    p.cluster_merge = 0;
     // which entries each mode takes
     if ((mode & 3) == 3) p.small_rows = 8;
     else if (mode & 2) p.small_rows = 1 << 30;   // everything is "small"
@@ -696,20 +749,41 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
         IB_LAUNCH_CHECK();
     }
     if (mode & 2) {
-        if (splits > 1) {
+        // only rows that split mode handled could be merged: with both modes in
+        // one step the caller keeps splits at 1
+        if (splits > 1 && (mode & 1)) return IB_ERR_BAD_ARG;
+        if (splits > 8) {
             const long long need = ib_attention_mma_scratch_bytes(n_rows, nh, splits);
             if (!scratch || scratch_bytes < need || ((uintptr_t)scratch & 15)) return IB_ERR_BAD_ARG;
             p.part_o = (float*)scratch;
             p.part_ml = p.part_o + (size_t)splits * n_rows * nh * HD;
         }
         dim3 grid(splits, n_entries, nkv * p.n_hsub_split);
+        p.cluster_merge = (splits > 1 && splits <= 8) ? 1 : 0;
+        if (p.cluster_merge) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(NTHREADS);
+            cfg.dynamicSmemBytes = SPLIT_SMEM_BYTES;
+            cfg.stream = s;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = splits;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = pdl_flag() ? 2 : 1;
+            cudaError_t le = cudaLaunchKernelEx(&cfg, attention_split_kernel, p);
+            if (le != cudaSuccess) return (int)le;
+            IB_LAUNCH_CHECK();
+            return IB_OK;
+        }
         cudaError_t le = launch_kernel(attention_split_kernel, grid, dim3(NTHREADS), SPLIT_SMEM_BYTES, s, p);
         if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
         if (splits > 1) {
-            // Only rows that split mode handled have partial results; with both
-            // modes in one step the caller keeps splits at 1.
-            if (mode & 1) return IB_ERR_BAD_ARG;
             dim3 cgrid(n_rows, nh);
             le = launch_kernel(attention_combine_kernel, cgrid, dim3(HD >= 128 ? 128 : 64), 0, s, p);
             if (le != cudaSuccess) return (int)le;

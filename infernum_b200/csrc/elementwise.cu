@@ -466,25 +466,32 @@ IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int
 }
 
 // ---------------------------------------------------------------------------
-// SwiGLU activation: out[t, i] = silu(x[t, i]) * x[t, I + i], x is [N, 2I].
+// SwiGLU activation: out[t, i] = silu(gate_i) * up_i, x is [N, 2I].
+// Where gate and up sit in a row of x is given by `blk`: the row is cut in
+// pieces of 2*blk values, each blk gates followed by their blk ups.  blk = I is
+// the plain layout [all gates | all ups]; blk = 64 is the layout of a product
+// whose weight rows were interleaved 64 by 64 (so that one 128-row tile of the
+// tcgen05 product holds gates and their ups).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int I, int blk,
+                                size_t total) {
     pdl_trigger();
     pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t row = idx / I;
     const int i = (int)(idx % I);
-    const float g = to_f32(x[row * 2 * I + i]);
-    const float u = to_f32(x[row * 2 * I + I + i]);
+    const size_t gi = row * 2 * I + (size_t)(i / blk) * 2 * blk + (i % blk);
+    const float g = to_f32(x[gi]);
+    const float u = to_f32(x[gi + blk]);
     const float act = g / (1.f + expf(-g));
     out[idx] = from_f32<T>(act * u);
 }
 
-// Eight outputs per thread with 16-byte loads and stores (I % 8 == 0).
+// Eight outputs per thread with 16-byte loads and stores (I and blk multiples of 8).
 __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int I,
-                                     size_t total_vec) {
+                                     int blk, size_t total_vec) {
     pdl_trigger();
     pdl_wait();
     const size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -492,8 +499,9 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ x, bf16* __restric
     const int per_row = I >> 3;
     const size_t row = v / per_row;
     const int i = (int)(v % per_row) << 3;
-    const uint4 g4 = *reinterpret_cast<const uint4*>(x + row * 2 * I + i);
-    const uint4 u4 = *reinterpret_cast<const uint4*>(x + row * 2 * I + I + i);
+    const size_t gi = row * 2 * I + (size_t)(i / blk) * 2 * blk + (i % blk);
+    const uint4 g4 = *reinterpret_cast<const uint4*>(x + gi);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(x + gi + blk);
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
     uint4 o4;
@@ -506,15 +514,16 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ x, bf16* __restric
     *reinterpret_cast<uint4*>(out + row * I + i) = o4;
 }
 
-IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, int I, void* stream) {
+IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, int I, int blk,
+                          void* stream) {
     if (n_rows <= 0) return IB_OK;
-    if (!x || !out || I <= 0) return IB_ERR_BAD_ARG;
+    if (!x || !out || I <= 0 || blk <= 0 || I % blk) return IB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)n_rows * I;
-    if (act_dtype == 1 && I % 8 == 0 && !(((uintptr_t)x | (uintptr_t)out) & 15)) {
+    if (act_dtype == 1 && I % 8 == 0 && blk % 8 == 0 && !(((uintptr_t)x | (uintptr_t)out) & 15)) {
         const size_t total_vec = total / 8;
         cudaError_t le = launch_kernel(silu_mul_vec8_kernel, dim3((unsigned)((total_vec + 255) / 256)),
-                                       dim3(256), 0, s, (const bf16*)x, (bf16*)out, I, total_vec);
+                                       dim3(256), 0, s, (const bf16*)x, (bf16*)out, I, blk, total_vec);
         if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
         return IB_OK;
@@ -522,11 +531,11 @@ IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, i
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (act_dtype == 0) {
         cudaError_t le = launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s,
-                                       (const float*)x, (float*)out, I, total);
+                                       (const float*)x, (float*)out, I, blk, total);
         if (le != cudaSuccess) return (int)le;
     } else if (act_dtype == 1) {
         cudaError_t le = launch_kernel(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s,
-                                       (const bf16*)x, (bf16*)out, I, total);
+                                       (const bf16*)x, (bf16*)out, I, blk, total);
         if (le != cudaSuccess) return (int)le;
     } else {
         return IB_ERR_UNSUPPORTED;

@@ -136,6 +136,9 @@ __device__ __forceinline__ void tmem_ld16(unsigned addr, unsigned (&r)[16]) {
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void epilogue_bar_sync() {
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
@@ -186,6 +189,7 @@ struct GemmParams {
     int splits;           // slices of K = CTAs per cluster (1, 2, 4 or 8)
     int kblocks_per_split;
     int out_f32;
+    int swiglu;           // 1: W rows are 64 gates then their 64 ups per tile; out is [T, N/2]
 };
 
 template <int BN>
@@ -311,7 +315,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         tc_fence_after();
         const unsigned taddr = tmem_base + ((unsigned)(quad * 32) << 16);
         const int t0 = t_tile * BN;
-        if (p.splits == 1) {
+        if (p.swiglu) {
+            // Rows 0..63 of the tile are gates, rows 64..127 their ups (splits == 1).
+            // The up lanes park their values in shared memory (the stages are free:
+            // every MMA has completed), the gate lanes fetch them and store
+            // silu(gate) * up.  out is [T, N / 2], column n_tile * 64 + row.
+            float* xch = reinterpret_cast<float*>(smem);  // [BN][64]
+            if (row >= 64 && ok && n_kblocks > 0) {
+#pragma unroll
+                for (int c = 0; c < BN; c += 16) {
+                    unsigned v[16];
+                    tmem_ld16(taddr + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) xch[(c + j) * 64 + (row - 64)] = __uint_as_float(v[j]);
+                }
+            }
+            epilogue_bar_sync();
+            const int col = n_tile * 64 + row;
+            if (row < 64 && ok && n_kblocks > 0 && col < p.N / 2) {
+#pragma unroll
+                for (int c = 0; c < BN; c += 16) {
+                    unsigned v[16];
+                    tmem_ld16(taddr + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c + j;
+                        if (t < p.T) {
+                            const float g = __uint_as_float(v[j]);
+                            const float u = xch[(c + j) * 64 + row];
+                            ((bf16*)p.out)[(size_t)t * p.ldo + col] =
+                                __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                        }
+                    }
+                }
+            }
+        } else if (p.splits == 1) {
             if (ok && n_kblocks > 0) {
 #pragma unroll
                 for (int c = 0; c < BN; c += 16) {
@@ -423,6 +463,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams
                   int n_tiles, cudaStream_t s) {
     constexpr int smem = num_stages(BN) * stage_bytes(BN) + 1024;
     static_assert(BN * BM * 4 <= num_stages(BN) * stage_bytes(BN), "partial tile must fit the stages");
+    if (p.swiglu && BN > 64) return IB_ERR_UNSUPPORTED;  // the exchange buffer is sized for small token tiles
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>,
@@ -463,21 +504,24 @@ IB_EXPORT int ib_gemm_tc_token_tile(int T) {
 
 // out[T, N] = X[T, K] . W[N, K]^T, bf16 operands, out bf16 (out_f32 = 0) or float32.
 // ldx, ldw, ldo: row strides in elements.  `splits` (1, 2, 4 or 8) cuts K over
-// the CTAs of a cluster; other values are rounded down.
+// the CTAs of a cluster; other values are rounded down.  swiglu = 1: W holds, per
+// 128 rows, 64 gate rows followed by their 64 up rows; out is [T, N / 2] bf16 with
+// out[t, 64 b + r] = silu(x . W[128 b + r]) * (x . W[128 b + 64 + r]); K is not split.
 IB_EXPORT int ib_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
-                         int out_f32, int T, int N, int K, int splits, unsigned* err,
+                         int out_f32, int T, int N, int K, int splits, int swiglu, unsigned* err,
                          void* stream) {
     if (T <= 0 || N <= 0) return IB_OK;
     if (!x || !w || !out || !err || K <= 0) return IB_ERR_BAD_ARG;
     // TMA: 16-byte aligned bases and row strides
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx % 8) || (ldw % 8) || ldx < K || ldw < K ||
-        ldo < N)
+        ldo < (swiglu ? N / 2 : N))
         return IB_ERR_UNSUPPORTED;
+    if (swiglu && (N % 128 || out_f32)) return IB_ERR_UNSUPPORTED;
     const int bn = ib_gemm_tc_token_tile(T);
     const int t_tiles = (T + bn - 1) / bn, n_tiles = (N + BM - 1) / BM;
     const int kblocks = (K + BK - 1) / BK;
     int sp = 1;
-    while (sp * 2 <= splits && sp * 2 <= 8 && sp * 2 <= kblocks) sp *= 2;
+    while (!swiglu && sp * 2 <= splits && sp * 2 <= 8 && sp * 2 <= kblocks) sp *= 2;
     if (n_tiles > 65535) return IB_ERR_TOO_LARGE;
     GemmParams p;
     p.out = out;
@@ -489,6 +533,7 @@ IB_EXPORT int ib_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* o
     p.splits = sp;
     p.kblocks_per_split = (kblocks + sp - 1) / sp;
     p.out_f32 = out_f32;
+    p.swiglu = swiglu ? 1 : 0;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, ldw, BM);
     if (rc != IB_OK) return rc;

@@ -57,7 +57,8 @@ def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count
     tiles = max(1, -(-max_kv_len // 64))
     best, best_cost = 1, None
     for s in range(1, min(32, tiles) + 1):
-        cost = -(-base * s // slots) * (-(-tiles // s) + 3)
+        # more than 8 slices cannot be one cluster: a second kernel merges them
+        cost = -(-base * s // slots) * (-(-tiles // s) + 3 + (4 if s > 8 else 0))
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
@@ -92,7 +93,7 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
             splits = choose_splits(ctx.n_entries, nkv * n_hsub, ctx.max_kv_len, sm)
     lib = lib_for(hd)
     scratch_ptr, scratch_bytes = None, 0
-    if splits > 1:
+    if splits > 8:
         need = lib.ib_attention_mma_scratch_bytes(ctx.n_rows, n_heads, splits)
         buf = ctx.scratch.get("attn_split")
         if buf is None or buf.numel() * 4 < need:

@@ -44,7 +44,7 @@ def core_lib() -> ctypes.CDLL:
                                        _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                        _c_void_p]
-        lib.ib_silu_mul.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_silu_mul.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]
         lib.ib_attention_plain.argtypes = [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                                            _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -199,15 +199,21 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[t
                                     stream_ptr(qkv)), "rope_append")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: Optional[int] = None) -> None:
+    """out = silu(gate) * up for rows [N, 2I].  ``block`` says where gates and
+    ups sit in a row: None for [all gates | all ups], else pieces of ``block``
+    gates followed by their ``block`` ups."""
     require_cuda(gate_up, out)
     N, two_i = gate_up.shape
     if two_i % 2 or out.shape != (N, two_i // 2) or out.dtype != gate_up.dtype \
             or not gate_up.is_contiguous() or not out.is_contiguous():
         raise KernelError("silu_mul: gate_up [N, 2I] and out [N, I] must be contiguous, same dtype")
-    check(core_lib().ib_silu_mul(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), N,
-                                 two_i // 2, stream_ptr(out)), "silu_mul")
+    I = two_i // 2
+    blk = I if block is None else int(block)
+    if blk <= 0 or I % blk:
+        raise KernelError(f"silu_mul: block {blk} does not divide the width {I}")
+    check(core_lib().ib_silu_mul(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), N, I,
+                                 blk, stream_ptr(out)), "silu_mul")
 
 
 def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

@@ -36,7 +36,7 @@ def lib() -> ctypes.CDLL:
     if _lib is None:
         l = load_module("gemm_tc", ["gemm_tcgen05.cu"])
         l.ib_gemm_tc.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
         l.ib_gemm_tc.restype = _c_int
         l.ib_gemm_tc_token_tile.argtypes = [_c_int]
         l.ib_gemm_tc_token_tile.restype = _c_int
@@ -74,8 +74,10 @@ def eligible(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
-            err: Optional[torch.Tensor] = None) -> None:
-    """Runs the tcgen05 kernel; raises KernelError if the operands do not fit it."""
+            err: Optional[torch.Tensor] = None, swiglu: bool = False) -> None:
+    """Runs the tcgen05 kernel; raises KernelError if the operands do not fit it.
+    ``swiglu``: ``w`` holds, per 128 rows, 64 gate rows then their 64 up rows, and
+    ``out`` [T, N/2] receives silu(gate) * up (at most 64 tokens)."""
     core.require_cuda(x, w, out)
     T, K = x.shape
     N = w.shape[0]
@@ -83,7 +85,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
         splits = choose_splits(T, N, K, POLICY["sm_count"])
     code = lib().ib_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
                             out.stride(0), 1 if out.dtype == torch.float32 else 0, T, N, K, splits,
-                            (err if err is not None else _error_word(x.device)).data_ptr(),
+                            1 if swiglu else 0, (err if err is not None else _error_word(x.device)).data_ptr(),
                             core.stream_ptr(x))
     core.check(code, "gemm_tc")
 
@@ -97,6 +99,20 @@ def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     if not eligible(x, w, out):
         return False
     gemm_tc(x, w, out)
+    return True
+
+
+def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor) -> bool:
+    """The gate/up product with SiLU(gate) * up applied in its epilogue, when
+    the policy and the operands allow; ``out`` is [T, I]."""
+    mode = POLICY["mode"]
+    if mode in ("none", "cublas", "library") or x.shape[0] > min(POLICY["max_tokens"], 64):
+        return False
+    if w_interleaved.shape[0] % 128 or out.dtype != torch.bfloat16:
+        return False
+    if not eligible(x, w_interleaved, out):
+        return False
+    gemm_tc(x, w_interleaved, out, splits=1, swiglu=True)
     return True
 
 

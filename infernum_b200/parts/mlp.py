@@ -1,7 +1,12 @@
 """SwiGLU feed-forward: ``d = (silu(x Wg^T) * (x Wu^T)) Wd^T`` with
 ``silu(g) = g / (1 + exp(-g))`` evaluated in 32-bit
 (infernum-llama/src/graph_builder.rs:498-501; infernum-cuda/kernels/silu.cu:105-116).
-Gate and up are one product with the row-concatenated weight ``[Wg; Wu]``.
+Gate and up are one product.  When the intermediate size is a multiple of 64
+the fused weight interleaves them 64 rows by 64 rows ([g0..g63, u0..u63,
+g64..g127, u64..u127, ...]), so that one 128-row tile of the tcgen05 product
+holds gates and their ups and SiLU(gate) * up can be applied in its epilogue;
+otherwise it is the plain concatenation ``[Wg; Wu]``.  Only the fused copy is
+kept.
 
 Parameters: ``hidden_size``, ``intermediate_size``, ``prefix`` (checkpoint
 prefix, e.g. "model.layers.0.mlp.").
@@ -42,14 +47,26 @@ class SwiGLU(FeedForward):
         up = weights[self.prefix + "up_proj.weight"]
         if gate.dtype != up.dtype:
             raise ConfigError(f"{self.prefix}: gate and up projections are stored in different dtypes")
-        self.gate_up = Linear(torch.cat([gate, up], dim=0))
+        i, h = self.intermediate_size, self.hidden_size
+        self.block = None  # None: [all gates | all ups]; 64: interleaved 64 by 64
+        if i % 64 == 0:
+            fused = torch.stack([gate.view(i // 64, 64, h), up.view(i // 64, 64, h)], dim=1)
+            self.gate_up = Linear(fused.reshape(2 * i, h))
+            self.block = 64
+        else:
+            self.gate_up = Linear(torch.cat([gate, up], dim=0))
         self.down = Linear(weights[self.prefix + "down_proj.weight"])
 
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes + self.down.nbytes
 
     def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:
-        gu = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=gu.dtype, device=gu.device)
-        core.silu_mul(gu, act)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+        fused = False
+        if self.block == 64 and x.dtype == torch.bfloat16 and self.gate_up.weight.dtype == torch.bfloat16:
+            from ..ops import gemm_tc
+
+            fused = gemm_tc.swiglu_route(x, self.gate_up.weight, act)
+        if not fused:
+            core.silu_mul(self.gate_up(x), act, block=self.block)
         return self.down(act)

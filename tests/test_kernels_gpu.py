@@ -412,3 +412,26 @@ def test_gemm_tcgen05_takes_strided_rows_and_refuses_what_tma_cannot_fetch():
     assert rel_err(out, x.double().cpu() @ w.double().cpu().T) < 5e-3
     assert not gemm_tc.eligible(big[:, :250], w[:, :250], out)  # K not a multiple of 8
     assert not gemm_tc.eligible(big[:, 1:257], w, out)  # base not 16-byte aligned
+
+
+@pytest.mark.parametrize("T, I, K", [(1, 128, 64), (8, 256, 512), (33, 192, 200), (64, 1024, 1024)])
+def test_gemm_tcgen05_with_swiglu_epilogue(T, I, K):
+    """Weight rows interleaved 64 gates / 64 ups per tile; the epilogue stores silu(gate) * up."""
+    from infernum_b200.ops import gemm_tc
+    g = torch.Generator().manual_seed(I + T)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    wu = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([wg.view(I // 64, 64, K), wu.view(I // 64, 64, K)], dim=1).reshape(2 * I, K)
+    out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_tc(x.to(DEV), w.contiguous().to(DEV), out, splits=1, swiglu=True)
+    assert gemm_tc.error_flags(DEV) == 0
+    gate, up = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = gate / (1 + torch.exp(-gate)) * up
+    assert rel_err(out, want) < 6e-3
+    # the stand-alone kernel reads the same interleaved layout
+    c = core()
+    gu = (x.double() @ w.double().T).to(torch.bfloat16).to(DEV)
+    out2 = torch.empty(T, I, dtype=torch.bfloat16, device=DEV)
+    c.silu_mul(gu, out2, block=64)
+    assert rel_err(out2, want) < 2e-2
