@@ -34,18 +34,31 @@ def _peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
-def _time(fns: List[Callable[[], None]], reps: int, warmup: int) -> float:
-    """Mean microseconds per call, cycling through ``fns``."""
+def _time(fns: List[Callable[[], None]], reps: int, warmup: int, graph: bool = True) -> float:
+    """Mean microseconds per call, cycling through ``fns``.  With ``graph`` the
+    launches are recorded once in a CUDA graph and the replay is timed, so that
+    short kernels are not measured at the speed of the host."""
     import torch
 
-    for i in range(warmup):
+    for i in range(max(warmup, len(fns))):
         fns[i % len(fns)]()
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(reps):
-        fns[i % len(fns)]()
-    end.record()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(reps):
+                fns[i % len(fns)]()
+        g.replay()
+        torch.cuda.synchronize()
+        start.record()
+        g.replay()
+        end.record()
+    else:
+        start.record()
+        for i in range(reps):
+            fns[i % len(fns)]()
+        end.record()
     torch.cuda.synchronize()
     return start.elapsed_time(end) * 1000.0 / reps
 
@@ -91,6 +104,7 @@ def main(argv=None) -> int:
     ap.add_argument("--reps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--library", action="store_true", help="gemm: time the library product instead")
+    ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a graph")
     args = ap.parse_args(argv)
 
     import torch
@@ -120,7 +134,7 @@ def main(argv=None) -> int:
                 ctx.attention_mode = (2, args.splits)
             fns.append(lambda q=q, kp=kp, vp=vp, tables=tables, ctx=ctx: attention_fast.run(
                 q, kp, vp, outs, ctx, tables, nh, scale, 0, rt))
-        us = _time(fns, args.reps, args.warmup)
+        us = _time(fns, args.reps, args.warmup, not args.no_graph)
         if decode:
             nbytes = batch * kv_len * nkv * hd * 2 * 2
             out.update(batch=batch, kv_len=kv_len, us=us, gbs=nbytes / us / 1e3,
@@ -139,7 +153,7 @@ def main(argv=None) -> int:
             fns = [lambda w=w: torch.mm(x, w.t(), out=o) for w in ws]
         else:
             fns = [lambda w=w: gemm_tc.gemm_tc(x, w, o, splits=args.splits or None) for w in ws]
-        us = _time(fns, args.reps, args.warmup)
+        us = _time(fns, args.reps, args.warmup, not args.no_graph)
         nbytes, flops = N * K * 2 + T * K * 2 + T * N * 2, 2.0 * T * N * K
         out.update(tokens=T, n=N, k=K, us=us, gbs=nbytes / us / 1e3, tflops=flops / us / 1e6,
                    frac_of_hbm=nbytes / us / 1e3 / peaks["hbm_gbs"],
@@ -153,7 +167,7 @@ def main(argv=None) -> int:
         w = torch.ones(H, dtype=torch.bfloat16, device=dev)
         o = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         fns = [lambda r=r, d=d: core.add_rmsnorm(r, d, w, 1e-5, o) for r, d in zip(res, delta)]
-        us = _time(fns, args.reps, args.warmup)
+        us = _time(fns, args.reps, args.warmup, not args.no_graph)
         nbytes = T * H * (4 + 2 + 4 + 2)
         out.update(tokens=T, hidden=H, us=us, gbs=nbytes / us / 1e3,
                    frac_of_hbm=nbytes / us / 1e3 / peaks["hbm_gbs"])
@@ -170,7 +184,7 @@ def main(argv=None) -> int:
         tables = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
         inv = torch.rand(hd // 2, device=dev)
         fns = [lambda: core.rope_append(qkv, pos, inv, hd, nh, nkv, hd, ent, tables, kp, vp, rt.err)]
-        us = _time(fns, args.reps, args.warmup)
+        us = _time(fns, args.reps, args.warmup, not args.no_graph)
         nbytes = T * ((nh + nkv) * hd * 2 * 2 + nkv * hd * 2 + 2 * nkv * hd * 2)
         out.update(tokens=T, us=us, gbs=nbytes / us / 1e3, frac_of_hbm=nbytes / us / 1e3 / peaks["hbm_gbs"])
     elif args.kernel == "silu":
@@ -179,7 +193,7 @@ def main(argv=None) -> int:
         xs = [torch.randn(T, 2 * I, device=dev).to(torch.bfloat16) for _ in range(n)]
         o = torch.empty(T, I, dtype=torch.bfloat16, device=dev)
         fns = [lambda x=x: core.silu_mul(x, o) for x in xs]
-        us = _time(fns, args.reps, args.warmup)
+        us = _time(fns, args.reps, args.warmup, not args.no_graph)
         nbytes = T * I * 6
         out.update(tokens=T, intermediate=I, us=us, gbs=nbytes / us / 1e3,
                    frac_of_hbm=nbytes / us / 1e3 / peaks["hbm_gbs"])

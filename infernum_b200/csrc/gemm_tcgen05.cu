@@ -404,9 +404,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
             for (int c = c_begin; c < c_end; ++c) {
                 const int t = t0 + c;
                 if (t >= p.T) break;
+                // all loads first (they are independent), then the sum in slice order
+                float part[8];
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx)
+                    part[sidx] = sidx < p.splits ? ld_peer_smem(red + c * BM + row, (unsigned)sidx) : 0.f;
                 float acc = 0.f;
-                for (int sidx = 0; sidx < p.splits; ++sidx)
-                    acc += ld_peer_smem(red + c * BM + row, (unsigned)sidx);
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) acc += part[sidx];
                 if (n < p.N) {
                     if (p.out_f32) ((float*)p.out)[(size_t)t * p.ldo + n] = acc;
                     else ((bf16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(acc);
@@ -503,8 +508,8 @@ IB_EXPORT int ib_gemm_tc_token_tile(int T) {
 }
 
 // out[T, N] = X[T, K] . W[N, K]^T, bf16 operands, out bf16 (out_f32 = 0) or float32.
-// ldx, ldw, ldo: row strides in elements.  `splits` (1, 2, 4 or 8) cuts K over
-// the CTAs of a cluster; other values are rounded down.  swiglu = 1: W holds, per
+// ldx, ldw, ldo: row strides in elements.  `splits` (1..8) cuts K over the
+// CTAs of a cluster.  swiglu = 1: W holds, per
 // 128 rows, 64 gate rows followed by their 64 up rows; out is [T, N / 2] bf16 with
 // out[t, 64 b + r] = silu(x . W[128 b + r]) * (x . W[128 b + 64 + r]); K is not split.
 IB_EXPORT int ib_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
@@ -520,8 +525,9 @@ IB_EXPORT int ib_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* o
     const int bn = ib_gemm_tc_token_tile(T);
     const int t_tiles = (T + bn - 1) / bn, n_tiles = (N + BM - 1) / BM;
     const int kblocks = (K + BK - 1) / BK;
-    int sp = 1;
-    while (!swiglu && sp * 2 <= splits && sp * 2 <= 8 && sp * 2 <= kblocks) sp *= 2;
+    int sp = splits < 1 ? 1 : (splits > 8 ? 8 : splits);  // a cluster holds at most 8 CTAs
+    if (sp > kblocks) sp = kblocks;
+    if (swiglu) sp = 1;
     if (n_tiles > 65535) return IB_ERR_TOO_LARGE;
     GemmParams p;
     p.out = out;
@@ -530,8 +536,8 @@ IB_EXPORT int ib_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* o
     p.N = N;
     p.K = K;
     p.ldo = ldo;
-    p.splits = sp;
     p.kblocks_per_split = (kblocks + sp - 1) / sp;
+    p.splits = (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;  // no empty slice
     p.out_f32 = out_f32;
     p.swiglu = swiglu ? 1 : 0;
     CUtensorMap mw, mx;

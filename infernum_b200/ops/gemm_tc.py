@@ -53,15 +53,20 @@ def _error_word(device) -> torch.Tensor:
 
 
 def choose_splits(T: int, N: int, K: int, sm_count: int) -> int:
-    """Slices of K (1, 2, 4 or 8: the CTAs of one cluster) so that the grid
-    covers the SMs, each slice with at least four blocks of 64 k."""
+    """Slices of K (1..8, the CTAs of one cluster).  Two CTAs fit an SM; the
+    largest slice count is taken whose grid still fits one round with some room
+    for the placement of whole clusters (measured on the 8B shapes: 48 tiles x 5
+    and 32 tiles x 8 run in one round, 48 x 6 does not), each slice keeping at
+    least four blocks of 64 k."""
     bn = lib().ib_gemm_tc_token_tile(T)
     tiles = -(-N // BM) * -(-T // bn)
     kblocks = -(-K // BK)
-    splits = 1
-    while tiles * splits < sm_count and splits < 8 and kblocks // (splits * 2) >= 4:
-        splits *= 2
-    return splits
+    room = int(0.87 * 2 * sm_count)
+    best = 1
+    for s in range(2, 9):
+        if tiles * s <= room and kblocks // s >= 4:
+            best = s
+    return best
 
 
 def eligible(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
