@@ -1,0 +1,222 @@
+"""``bench``: throughput of a model through the engine, in the manner of the
+reference's example (infernum-examples/examples/bench.rs:72-158, 1035-1036):
+
+    bench MODEL [N_GEN] [--dtype bf16|f32]
+
+``MODEL`` is a model folder, or one of the shapes ``8b``, ``1b``, ``13b``,
+``tinyA``, ``tinyB`` with random weights.  The default workload is the
+reference's: an 8-token prompt, ``N_GEN`` (128) greedy tokens timed from the
+host, and a 512-token prompt timed as prefill; it prints
+``N tokens in S s = R tok/s``.  Two more workloads exercise the scheduler:
+
+    --workload mixed      64 requests (``--requests``), prompt lengths uniform in
+                          [16, 4096], prompts fed 512 tokens at a time beside the
+                          decoding requests, 128 new tokens each, temperature 0.8
+    --workload pressure   32 requests of 2,048 prompt + 512 greedy tokens with a
+                          page pool too small for all of them, so that requests
+                          are preempted and recomputed; every request's tokens
+                          must equal its run alone
+
+``--requests``, ``--prompt-len``, ``--new-tokens``, ``--num-blocks`` scale a
+workload down; ``--layers`` cuts the number of layers of a random shape.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import random
+import sys
+import time
+from typing import List, Optional
+
+SHAPES = {
+    "8b": {"num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+           "vocab_size": 128256, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                            "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+           "tie_word_embeddings": False, "max_position_embeddings": 8192},
+    "1b": {"num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+           "vocab_size": 128256, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+           "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                            "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+           "tie_word_embeddings": True, "max_position_embeddings": 8192},
+    "13b": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40,
+            "num_key_value_heads": 40, "head_dim": 128, "intermediate_size": 13824,
+            "vocab_size": 32000, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+            "tie_word_embeddings": False, "max_position_embeddings": 4096},
+    "tinyA": {"num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4,
+              "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 176, "vocab_size": 256,
+              "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+              "max_position_embeddings": 128},
+    "tinyB": {"num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 3,
+              "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 256, "vocab_size": 320,
+              "rope_theta": 500000.0, "rms_norm_eps": 1e-6,
+              "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                               "high_freq_factor": 4.0, "original_max_position_embeddings": 64},
+              "tie_word_embeddings": False, "max_position_embeddings": 256},
+}
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="bench", description=__doc__,
+                                 formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("model", help="model folder, or a shape name: " + ", ".join(SHAPES))
+    ap.add_argument("n_gen", nargs="?", type=int, default=128, help="tokens to generate")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "bfloat16", "float32"])
+    ap.add_argument("--workload", default="single", choices=["single", "mixed", "pressure"])
+    ap.add_argument("--requests", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--new-tokens", type=int, default=None)
+    ap.add_argument("--num-blocks", type=int, default=None)
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
+    return ap
+
+
+def load(args):
+    import infernum_b200 as ib
+
+    dtype = {"bf16": "bfloat16", "f32": "float32"}.get(args.dtype, args.dtype)
+    if args.model in SHAPES:
+        cfg = dict(SHAPES[args.model], model_type="llama")
+        if args.layers:
+            cfg["num_hidden_layers"] = args.layers
+        model = ib.random_model(cfg, seed=args.seed, dtype=dtype)
+    else:
+        model = ib.load_model(args.model, dtype=dtype)
+    print(f"Model loaded: {len(model.layers)} layers, {model.spec.hidden_size} hidden, dtype={args.dtype}",
+          file=sys.stderr)
+    return model
+
+
+def run_single(model, args) -> dict:
+    import torch
+
+    import infernum_b200 as ib
+
+    vocab = model.spec.vocab_size
+    prompt = [t % vocab for t in (1, 15043, 29892, 920, 526, 366, 2599, 13)]  # bench.rs:138
+    n_gen = args.n_gen
+    prefill_tokens = min(512, model.spec.max_position - 1)
+    blocks = (max(prefill_tokens, len(prompt) + n_gen) + 1) // args.block_size + 4
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=1, block_size=args.block_size,
+                                             num_blocks=blocks, max_prefill_tokens=2048,
+                                             max_model_len=max(prefill_tokens + 2, len(prompt) + n_gen + 1)))
+    opts = ib.GenerateOptions(max_new_tokens=n_gen, ignore_eos=True)
+    engine.generate(prompt, ib.GenerateOptions(max_new_tokens=4, ignore_eos=True))  # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tokens = engine.generate(prompt, opts)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    rng = random.Random(args.seed)
+    long_prompt = [rng.randrange(vocab) for _ in range(prefill_tokens)]
+    one = ib.GenerateOptions(max_new_tokens=1, ignore_eos=True)
+    engine.generate(long_prompt, one)  # warm-up
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    engine.generate(long_prompt, one)
+    torch.cuda.synchronize()
+    dp = time.perf_counter() - t1
+    return {"workload": "single", "generated": len(tokens), "seconds": dt, "decode_tok_s": len(tokens) / dt,
+            "prefill_tokens": prefill_tokens, "prefill_tok_s": prefill_tokens / dp}
+
+
+def run_mixed(model, args) -> dict:
+    import torch
+
+    import infernum_b200 as ib
+
+    n_req = args.requests or 64
+    new_tokens = args.new_tokens or 128
+    max_prompt = args.prompt_len or 4096
+    vocab = model.spec.vocab_size
+    rng = random.Random(args.seed)
+    lens = [rng.randint(min(16, max_prompt), max_prompt) for _ in range(n_req)]
+    prompts = [[rng.randrange(vocab) for _ in range(n)] for n in lens]
+    total = sum(lens) + n_req * new_tokens
+    blocks = args.num_blocks or total // args.block_size + 2 * n_req
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=n_req, max_prefill_tokens=512,
+                                             block_size=args.block_size, num_blocks=blocks,
+                                             max_tokens_per_step=512 + n_req,
+                                             max_model_len=max_prompt + new_tokens + 1))
+    opts = [ib.GenerateOptions(max_new_tokens=new_tokens, ignore_eos=True,
+                               sampling=ib.SamplingParams(temperature=0.8, top_p=1.0, seed=args.seed + i))
+            for i in range(n_req)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate_batch(prompts, opts)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    st = engine.stats
+    return {"workload": "mixed", "requests": n_req, "prompt_tokens": sum(lens),
+            "generated": sum(len(o) for o in outs), "seconds": dt,
+            "total_tok_s": (sum(lens) + sum(len(o) for o in outs)) / dt,
+            "decode_tok_s": sum(len(o) for o in outs) / dt, "steps": st.steps,
+            "tokens_per_step": (st.prefill_tokens + st.decode_tokens) / max(st.steps, 1),
+            "preemptions": st.preemptions}
+
+
+def run_pressure(model, args) -> dict:
+    import torch
+
+    import infernum_b200 as ib
+
+    n_req = args.requests or 32
+    prompt_len = args.prompt_len or 2048
+    new_tokens = args.new_tokens or 512
+    vocab = model.spec.vocab_size
+    rng = random.Random(args.seed)
+    prompts = [[rng.randrange(vocab) for _ in range(prompt_len)] for _ in range(n_req)]
+    per_req = -(-(prompt_len + new_tokens) // args.block_size)
+    blocks = args.num_blocks or int(0.8 * n_req * per_req)  # deliberately too few
+    opts = ib.GenerateOptions(max_new_tokens=new_tokens, ignore_eos=True)
+    cfg = dict(max_batch_size=n_req, max_prefill_tokens=512, block_size=args.block_size,
+               max_tokens_per_step=512 + n_req, max_model_len=prompt_len + new_tokens + 1)
+    tight = ib.Engine(model, ib.BatchConfig(num_blocks=blocks, **cfg))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = tight.generate_batch(prompts, opts)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    preemptions = tight.stats.preemptions
+    del tight
+    torch.cuda.empty_cache()
+    # every request alone, with room: the yardstick
+    solo = ib.Engine(model, ib.BatchConfig(num_blocks=per_req + 2, **dict(cfg, max_batch_size=1)))
+    same, first_diff = 0, []
+    for p, o in zip(prompts, outs):
+        want = solo.generate(p, opts)
+        if want == o:
+            same += 1
+        else:
+            first_diff.append(next(i for i in range(len(o)) if o[i] != want[i]))
+    return {"workload": "pressure", "requests": n_req, "num_blocks": blocks,
+            "blocks_for_all": n_req * per_req, "preemptions": preemptions,
+            "generated": sum(len(o) for o in outs), "seconds": dt,
+            "decode_tok_s": sum(len(o) for o in outs) / dt, "identical_to_solo": same,
+            "first_difference_at": first_diff}
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    args = build_parser().parse_args(argv)
+    model = load(args)
+    result = {"single": run_single, "mixed": run_mixed, "pressure": run_pressure}[args.workload](model, args)
+    if args.json:
+        print(json.dumps({k: (round(v, 3) if isinstance(v, float) else v) for k, v in result.items()}))
+    elif args.workload == "single":
+        print(f"{result['generated']} tokens in {result['seconds']:.2f}s = {result['decode_tok_s']:.1f} tok/s")
+        print(f"prefill {result['prefill_tokens']} tokens = {result['prefill_tok_s']:.1f} tok/s")
+    else:
+        for k, v in result.items():
+            print(f"{k}: {v:.3f}" if isinstance(v, float) else f"{k}: {v}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
