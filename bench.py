@@ -149,11 +149,11 @@ def make_requests(runner, cache, batch, prompt_len, vocab, seed, chunk=2048):
 
 
 def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks=None, graph=True):
-    """Device-timed decode: K steps of a DecodeSession that feeds itself."""
+    """Device-timed decode: K steps of a DecodeRunner that feeds itself."""
     import torch
 
     from infernum_b200.cache import CacheManager
-    from infernum_b200.engine.decode import DecodeSession
+    from infernum_b200.engine.decode import DecodeRunner
     from infernum_b200.engine.step import ModelRunner
     from infernum_b200.ops import core
 
@@ -163,16 +163,17 @@ def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks
                          dtype=model.rt.dtype, device=model.rt.device)
     runner = ModelRunner(model, cache, max_rows=4096, max_entries=max(batch, 1))
     caches, first = make_requests(runner, cache, batch, prompt_len, model.spec.vocab_size, seed)
-    session = DecodeSession(runner, caches, first, max_steps=steps + warmup + 4, use_graph=graph)
+    session = DecodeRunner(runner, total + 8, use_graph=graph)
+    session.pin(caches, first, steps + max(warmup, 3) + 2)
     for _ in range(max(warmup, 3)):
-        session.step()
+        session.step_pinned()
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = core.LAUNCHES
     t0 = time.time()
     start.record()
     for _ in range(steps):
-        session.step()
+        session.step_pinned()
     end.record()
     torch.cuda.synchronize()
     t1 = time.time()
@@ -182,8 +183,8 @@ def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks
     result = {
         "ms_per_step": ms, "tokens_per_s": batch * 1000.0 / ms,
         "bytes_per_step": decode_bytes(model, cache, live),
-        "launches_per_step": session.launches_per_step,
-        "graph": session.graph is not None,
+        "launches_per_step": session.last.launches_per_step,
+        "graph": session.last.graph is not None,
         "clocks": clocks.summary(t0, t1) if clocks else None,
     }
     for rc in caches:

@@ -86,6 +86,11 @@ class CacheManager:
         self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
         self._requests: Dict[object, RequestCache] = {}
         self._state_tensors: List[torch.Tensor] = []
+        # One extra slot, and one extra page behind every group's pool (page id
+        # num_pages, never handed out), belong to no request: rows that only pad
+        # a batch to a fixed size write there.
+        self.pad_slot = self.max_requests
+        self.pad_page = self.num_pages
 
         group_of_spec: Dict[PagedCacheSpec, int] = {}
         for need in needs:
@@ -101,14 +106,14 @@ class CacheManager:
                     group_of_spec[need.paged] = g
                     self.groups.append(CacheGroup(need.paged, [], PagePool(self.num_pages)))
                 self.groups[g].positions.append(need.position)
-                lc.group, lc.page_size, lc.num_pages = g, self.page_size, self.num_pages
+                lc.group, lc.page_size, lc.num_pages = g, self.page_size, self.num_pages + 1
                 if device is not None:
-                    shape = (self.num_pages, need.paged.kv_heads, self.page_size, need.paged.head_dim)
+                    shape = (self.num_pages + 1, need.paged.kv_heads, self.page_size, need.paged.head_dim)
                     lc.k_pool = torch.zeros(shape, dtype=dtype, device=device)
                     lc.v_pool = torch.zeros(shape, dtype=dtype, device=device)
             if need.state is not None and need.cache_of is None:
                 if device is not None:
-                    lc.state = torch.zeros((self.max_requests, *need.state.shape),
+                    lc.state = torch.zeros((self.max_requests + 1, *need.state.shape),
                                            dtype=need.state.dtype, device=device)
                     self._state_tensors.append(lc.state)
             self.layer_caches.append(lc)
@@ -135,6 +140,10 @@ class CacheManager:
 
     def live_requests(self) -> List[RequestCache]:
         return list(self._requests.values())
+
+    def pad_pages(self) -> List[int]:
+        """Per group, the page that padding rows write to."""
+        return [self.pad_page] * len(self.groups)
 
     # ---- a request's life ---------------------------------------------------
     def admit(self, request_id) -> RequestCache:

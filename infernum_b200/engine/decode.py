@@ -1,21 +1,33 @@
-"""Decoding a fixed set of requests with inputs that live on the device.
+"""Decode steps from fixed device buffers, recorded once as CUDA graphs.
 
-While the same requests decode step after step, nothing about a step changes
-but the numbers: one token, one position and one cache length per request, and
-now and then a new page in a block table.  A ``DecodeSession`` keeps those in
-fixed device buffers, so the step - model, token selection, advance - is a
-fixed sequence of kernel launches that is recorded once as a CUDA graph and
-replayed.  The host still does the page bookkeeping (it knows every position
-without asking the device) and copies the block tables when one changed.
+A step in which every request brings exactly one token has the same sequence
+of kernel launches whatever the requests are; only numbers change: tokens,
+positions, cache lengths, slots and block tables.  A ``DecodeRunner`` keeps
+those in fixed device buffers per *batch bucket* (the batch size rounded up to
+1, 2, 4, 8, 16, 24, 32, 48, 64, ...), fills them from the host each step, pads
+the bucket with rows that belong to no request (they write to a page and a
+state slot reserved for padding), and replays the graph recorded for that
+bucket.  Requests may come and go between steps without a new recording; a
+graph is recorded per (bucket, cache-length class, sampling or not), the first
+time it is needed, after one eager step.
 
-The reference does the same for batch size one only: six stable device
-buffers and a captured graph (infernum-cuda/src/inner/cuda_graph_engine.rs:970-1133);
-larger batches rebuild and run eagerly every step (:1549-1598).
+Two ways to feed it:
+  * from the host (``Engine``): tokens, positions and lengths are copied from
+    pinned memory every step, changed block-table rows too;
+  * from the device (``pin``): a fixed set of requests whose tokens are the ones
+    the previous step selected and whose positions advance on the device; the
+    host only reserves pages ahead and uploads the tables once.  Nothing is read
+    back between steps.
+
+The reference records a graph for batch size one only, with six stable device
+buffers (infernum-cuda/src/inner/cuda_graph_engine.rs:970-1133); larger batches
+rebuild and run eagerly every step (:1549-1598).
 """
 
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -24,146 +36,234 @@ from ..ops import core
 from ..ops.attention_fast import SM_COUNT_FALLBACK, choose_splits
 from .step import ModelRunner, StepContext
 
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
 
-class DecodeSession:
-    def __init__(self, runner: ModelRunner, caches: Sequence[RequestCache], tokens: Sequence[int],
-                 max_steps: int, use_graph: bool = True, sampling_rows: Optional[Sequence[bool]] = None):
+
+def bucket_for(n: int) -> int:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return -(-n // 128) * 128
+
+
+@dataclass
+class _Slot:
+    """Buffers and graph of one (bucket, cache-length class, sampling, feed) key."""
+
+    size: int
+    ints: torch.Tensor  # device [4, size]: tokens, positions, kv_len, slot ids
+    host_ints: torch.Tensor  # pinned mirror
+    tables: torch.Tensor  # device [groups, size, MB]
+    host_tables: torch.Tensor  # pinned mirror
+    selected: torch.Tensor  # device [size] int32
+    ctx: StepContext
+    rows: List[Optional[Tuple[object, List[int]]]] = field(default_factory=list)  # who sits where
+    sampled: Optional[torch.Tensor] = None
+    params: Optional[torch.Tensor] = None
+    host_params: Optional[torch.Tensor] = None
+    recent: Optional[torch.Tensor] = None
+    host_recent: Optional[torch.Tensor] = None
+    mask: Optional[torch.Tensor] = None
+    host_mask: Optional[torch.Tensor] = None
+    graph: Optional[torch.cuda.CUDAGraph] = None
+    logits: Optional[torch.Tensor] = None
+    eager_steps: int = 0
+    launches_per_step: int = 0
+
+
+class DecodeRunner:
+    RECENT_WIDTH = 64
+
+    def __init__(self, runner: ModelRunner, max_model_len: int, use_graph: bool = True):
         self.runner = runner
         self.cache = runner.cache
         self.model = runner.model
         self.rt = runner.rt
-        self.caches = list(caches)
-        self.key = tuple(rc.request_id for rc in self.caches)
-        dev = self.rt.device
-        B = self.B = len(self.caches)
         self.use_graph = use_graph
-        self.steps_left = int(max_steps)
-        longest = max(rc.num_tokens for rc in self.caches) + max_steps + 1
-        self.MB = max(1, self.cache.pages_for(longest))
-        n_groups = len(self.cache.groups)
+        self.MB = max(1, self.cache.pages_for(max_model_len))
+        self.max_model_len = int(max_model_len)
+        self._slots: Dict[tuple, _Slot] = {}
+        self._pinned: Optional[Tuple[tuple, List[RequestCache]]] = None
+        self.last: Optional[_Slot] = None
 
-        def i32(values):
-            return torch.tensor(list(values), dtype=torch.int32, device=dev)
-
-        self.tokens = i32(tokens)
-        self.positions = i32(rc.num_tokens for rc in self.caches)
-        self.kv_len = i32(rc.num_tokens + 1 for rc in self.caches)
-        self.selected = torch.zeros(B, dtype=torch.int32, device=dev)
-        self.host_tokens = torch.zeros(B, dtype=torch.int32).pin_memory()
-        self.host_tables = torch.full((n_groups, B, self.MB), -1, dtype=torch.int32).pin_memory()
-        self.dev_tables = torch.full((n_groups, B, self.MB), -1, dtype=torch.int32, device=dev)
-        self._tables_dirty = True
-        self._known_pages = [[0] * n_groups for _ in range(B)]
-        self.sampling_rows = list(sampling_rows) if sampling_rows is not None else [False] * B
-        self.any_sampling = any(self.sampling_rows)
-        if self.any_sampling:
-            self.host_params = torch.zeros((B, core.SAMPLE_PARAM_FLOATS), dtype=torch.float32).pin_memory()
-            self.dev_params = torch.zeros((B, core.SAMPLE_PARAM_FLOATS), dtype=torch.float32, device=dev)
-            self.recent_width = 64
-            self.host_recent = torch.zeros((B, self.recent_width), dtype=torch.int32).pin_memory()
-            self.dev_recent = torch.zeros((B, self.recent_width), dtype=torch.int32, device=dev)
-            self.sample_mask = torch.tensor(self.sampling_rows, dtype=torch.bool, device=dev)
-            self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
-        arange = torch.arange(B + 1, dtype=torch.int32, device=dev)
+    # ---- buffers -------------------------------------------------------------------
+    def _slot(self, key: tuple) -> _Slot:
+        slot = self._slots.get(key)
+        if slot is not None:
+            return slot
+        size, kv_cap, sampling, _feed = key
+        dev = self.rt.device
+        G = len(self.cache.groups)
+        ints = torch.zeros((4, size), dtype=torch.int32, device=dev)
+        tables = torch.full((G, size, self.MB), -1, dtype=torch.int32, device=dev)
+        arange = torch.arange(size + 1, dtype=torch.int32, device=dev)
         kv_heads = max([g.spec.kv_heads for g in self.cache.groups] + [1])
         sm = self.rt.options.get("sm_count") or SM_COUNT_FALLBACK
-        splits = choose_splits(B, kv_heads, longest, sm)
-        self.ctx = StepContext(
-            n_rows=B, n_entries=B, token_ids=self.tokens, positions=self.positions,
-            row_entry=arange[:B], cu_rows=arange, q_start=self.positions, kv_len=self.kv_len,
-            slot_ids=i32(rc.slot for rc in self.caches), logit_rows=arange[:B],
-            block_tables=[self.dev_tables[g] for g in range(n_groups)],
-            host_cu_rows=list(range(B + 1)), host_kv_len=[], max_rows_per_entry=1,
-            max_kv_len=longest, all_decode=True)
-        self.ctx.attention_mode = (2, splits)
-        self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.logits: Optional[torch.Tensor] = None
-        self._eager_steps = 0
-        self.launches_per_step = 0
+        ctx = StepContext(
+            n_rows=size, n_entries=size, token_ids=ints[0], positions=ints[1], row_entry=arange[:size],
+            cu_rows=arange, q_start=ints[1], kv_len=ints[2], slot_ids=ints[3], logit_rows=arange[:size],
+            block_tables=[tables[g] for g in range(G)], host_cu_rows=list(range(size + 1)),
+            host_kv_len=[], max_rows_per_entry=1, max_kv_len=kv_cap, all_decode=True)
+        ctx.attention_mode = (2, choose_splits(size, kv_heads, kv_cap, sm))
+        slot = _Slot(size=size, ints=ints, host_ints=torch.zeros((4, size), dtype=torch.int32).pin_memory(),
+                     tables=tables,
+                     host_tables=torch.full((G, size, self.MB), -1, dtype=torch.int32).pin_memory(),
+                     selected=torch.zeros(size, dtype=torch.int32, device=dev), ctx=ctx,
+                     rows=[None] * size)
+        if sampling:
+            f = core.SAMPLE_PARAM_FLOATS
+            slot.sampled = torch.zeros(size, dtype=torch.int32, device=dev)
+            slot.params = torch.zeros((size, f), dtype=torch.float32, device=dev)
+            slot.host_params = torch.zeros((size, f), dtype=torch.float32).pin_memory()
+            slot.recent = torch.zeros((size, self.RECENT_WIDTH), dtype=torch.int32, device=dev)
+            slot.host_recent = torch.zeros((size, self.RECENT_WIDTH), dtype=torch.int32).pin_memory()
+            slot.mask = torch.zeros(size, dtype=torch.bool, device=dev)
+            slot.host_mask = torch.zeros(size, dtype=torch.bool).pin_memory()
+        self._slots[key] = slot
+        return slot
 
-    # ---- host bookkeeping ---------------------------------------------------------
-    def _reserve(self) -> None:
-        """Pages for one more token per request; raises OutOfPagesError with
-        nothing taken if the pool cannot give them."""
-        done = []
-        try:
-            for rc in self.caches:
-                need = rc.num_tokens + 1 - rc.reserved_tokens
-                if need > 0:
-                    self.cache.extend(rc, need)
-                    done.append(rc)
-        except Exception:
-            for rc in done:
-                self.cache.cancel_reservation(rc)
-            raise
-        for b, rc in enumerate(self.caches):
+    def _fill_tables(self, slot: _Slot, caches: Sequence[RequestCache]) -> bool:
+        """Brings the host mirror of the block tables up to date; True if it changed."""
+        changed = False
+        pads = self.cache.pad_pages()
+        windowed = [g.spec.window > 0 for g in self.cache.groups]
+        for r in range(slot.size):
+            rc = caches[r] if r < len(caches) else None
+            who = rc.request_id if rc is not None else None
+            prev = slot.rows[r]
+            if prev is None or prev[0] != who:
+                for g in range(len(self.cache.groups)):
+                    slot.host_tables[g, r].fill_(-1)
+                    if rc is None:
+                        slot.host_tables[g, r, 0] = pads[g]
+                prev = (who, [0] * len(self.cache.groups))
+                slot.rows[r] = prev
+                changed = True
+            if rc is None:
+                continue
             for g, table in enumerate(rc.tables):
-                if len(table) != self._known_pages[b][g] or self._tables_dirty:
-                    n = min(len(table), self.MB)
-                    self.host_tables[g, b, :n] = torch.tensor(table[:n], dtype=torch.int32)
-                    self._known_pages[b][g] = len(table)
-                    self._tables_dirty = True
-            # pages a window gave back
-            for g, grp in enumerate(self.cache.groups):
-                if grp.spec.window > 0:
-                    n = min(len(rc.tables[g]), self.MB)
-                    self.host_tables[g, b, :n] = torch.tensor(rc.tables[g][:n], dtype=torch.int32)
-                    self._tables_dirty = True
+                n = min(len(table), self.MB)
+                if windowed[g]:
+                    slot.host_tables[g, r, :n] = torch.tensor(table[:n], dtype=torch.int32)
+                    changed = True
+                elif n != prev[1][g]:
+                    lo = min(prev[1][g], n)
+                    slot.host_tables[g, r, lo:n] = torch.tensor(table[lo:n], dtype=torch.int32)
+                    prev[1][g] = n
+                    changed = True
+        return changed
 
-    def can_continue(self) -> bool:
-        return self.steps_left > 0 and all(
-            self.cache.pages_for(rc.num_tokens + 1) <= self.MB for rc in self.caches)
+    # ---- the recorded body -----------------------------------------------------------
+    def _body(self, slot: _Slot, device_feed: bool) -> None:
+        slot.logits = self.model.forward(slot.ctx, self.cache.layer_caches)
+        core.argmax(slot.logits, slot.selected)
+        if slot.sampled is not None:
+            core.sample(slot.logits, slot.params, slot.recent, slot.sampled)
+            slot.selected.copy_(torch.where(slot.mask, slot.sampled, slot.selected))
+        if device_feed:
+            core.decode_advance(slot.ctx.token_ids, slot.selected, slot.ctx.positions, slot.ctx.kv_len)
 
-    # ---- the step --------------------------------------------------------------------
-    def _body(self) -> None:
-        self.logits = self.model.forward(self.ctx, self.cache.layer_caches)
-        core.argmax(self.logits, self.selected)
-        if self.any_sampling:
-            core.sample(self.logits, self.dev_params, self.dev_recent, self.sampled)
-            self.selected.copy_(torch.where(self.sample_mask, self.sampled, self.selected))
-        core.decode_advance(self.tokens, None if self._feed_host else self.selected,
-                            self.positions, self.kv_len)
-
-    def step(self, host_tokens: Optional[Sequence[int]] = None, sample_params=None) -> torch.Tensor:
-        """One decode step.  ``host_tokens``: the tokens to feed, copied from
-        pinned memory (None: the device feeds itself the tokens it selected).
-        Returns the selected token ids, int32 [B] on the device."""
-        self._feed_host = host_tokens is not None
-        self._reserve()
-        if self._tables_dirty:
-            self.dev_tables.copy_(self.host_tables, non_blocking=True)
-            self._tables_dirty = False
-        if host_tokens is not None:
-            self.host_tokens.copy_(torch.tensor(list(host_tokens), dtype=torch.int32))
-            self.tokens.copy_(self.host_tokens, non_blocking=True)
-        if self.any_sampling and sample_params is not None:
-            params, recent = sample_params
-            self.host_params.copy_(params)
-            self.host_recent.zero_()
-            self.host_recent[:, : recent.shape[1]] = recent[:, : self.recent_width]
-            self.dev_params.copy_(self.host_params, non_blocking=True)
-            self.dev_recent.copy_(self.host_recent, non_blocking=True)
-        if self.graph is not None and self._graph_feed_host == self._feed_host:
-            self.graph.replay()
-        elif self.use_graph and self._eager_steps >= 1:
-            self._capture()
-            self.graph.replay()
+    def _run(self, slot: _Slot, device_feed: bool) -> None:
+        if slot.graph is not None:
+            slot.graph.replay()
+        elif self.use_graph and slot.eager_steps >= 1:
+            torch.cuda.synchronize(self.rt.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._body(slot, device_feed)
+            slot.graph = graph
+            graph.replay()
         else:
             before = core.LAUNCHES
-            self._body()
-            self.launches_per_step = core.LAUNCHES - before
-            self._eager_steps += 1
-        for rc in self.caches:
-            self.cache.commit(rc, 1)
-        self.steps_left -= 1
-        self.runner.steps_run += 1
-        self.runner.rows_run += self.B
-        return self.selected
+            self._body(slot, device_feed)
+            slot.launches_per_step = core.LAUNCHES - before
+            slot.eager_steps += 1
 
-    def _capture(self) -> None:
+    def _key(self, caches: Sequence[RequestCache], sampling: bool, feed: str, ahead: int = 1) -> tuple:
+        longest = max(rc.num_tokens for rc in caches) + ahead
+        kv_cap = 256
+        while kv_cap < longest:
+            kv_cap *= 2
+        return (bucket_for(len(caches)), kv_cap, bool(sampling), feed)
+
+    def can_take(self, caches: Sequence[RequestCache]) -> bool:
+        return all(self.cache.pages_for(rc.num_tokens + 1) <= self.MB for rc in caches)
+
+    # ---- fed from the host ---------------------------------------------------------------
+    def step(self, caches: Sequence[RequestCache], tokens: Sequence[int],
+             sample: Optional[tuple] = None) -> torch.Tensor:
+        """One decode step of ``caches`` (pages for one more token must be held)
+        with the given input tokens.  ``sample``: (params, recent, mask) host
+        tensors from ``pack_choices`` when some row samples.  Returns the
+        selected token ids, int32 [len(caches)] on the device."""
+        B = len(caches)
+        slot = self._slot(self._key(caches, sample is not None, "host"))
+        self.last = slot
+        pad = slot.size - B
+        hi = slot.host_ints
+        hi[0, :B] = torch.tensor(list(tokens), dtype=torch.int32)
+        hi[1, :B] = torch.tensor([rc.num_tokens for rc in caches], dtype=torch.int32)
+        hi[3, :B] = torch.tensor([rc.slot for rc in caches], dtype=torch.int32)
+        if pad:
+            hi[0, B:] = 0
+            hi[1, B:] = 0
+            hi[3, B:] = self.cache.pad_slot
+        hi[2] = hi[1] + 1
+        slot.ints.copy_(hi, non_blocking=True)
+        if self._fill_tables(slot, caches):
+            slot.tables.copy_(slot.host_tables, non_blocking=True)
+        if sample is not None:
+            params, recent, mask = sample
+            slot.host_params.zero_()
+            slot.host_params[:, :3] = 1.0
+            slot.host_params[:B] = params
+            slot.host_recent.zero_()
+            slot.host_recent[:B, : recent.shape[1]] = recent[:, : self.RECENT_WIDTH]
+            slot.host_mask.zero_()
+            slot.host_mask[:B] = mask
+            slot.params.copy_(slot.host_params, non_blocking=True)
+            slot.recent.copy_(slot.host_recent, non_blocking=True)
+            slot.mask.copy_(slot.host_mask, non_blocking=True)
+        self._run(slot, device_feed=False)
+        for rc in caches:
+            self.cache.commit(rc, 1)
+        self.runner.steps_run += 1
+        self.runner.rows_run += B
+        return slot.selected[:B]
+
+    # ---- fed from the device ---------------------------------------------------------------
+    def pin(self, caches: Sequence[RequestCache], tokens: Sequence[int], steps: int) -> None:
+        """Fixes a set of requests for ``steps`` device-fed steps: reserves their
+        pages ahead, uploads tokens, positions and tables once."""
+        caches = list(caches)
+        for rc in caches:
+            need = rc.num_tokens + steps - rc.reserved_tokens
+            if need > 0:
+                self.cache.extend(rc, need)
+        key = self._key(caches, False, "device", ahead=steps)
+        slot = self._slot(key)
+        B = len(caches)
+        hi = slot.host_ints
+        hi.zero_()
+        hi[0, :B] = torch.tensor(list(tokens), dtype=torch.int32)
+        hi[1, :B] = torch.tensor([rc.num_tokens for rc in caches], dtype=torch.int32)
+        hi[3, :B] = torch.tensor([rc.slot for rc in caches], dtype=torch.int32)
+        hi[3, B:] = self.cache.pad_slot
+        hi[2] = hi[1] + 1
+        slot.ints.copy_(hi, non_blocking=True)
+        self._fill_tables(slot, caches)
+        slot.tables.copy_(slot.host_tables, non_blocking=True)
         torch.cuda.synchronize(self.rt.device)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            self._body()
-        self.graph = graph
-        self._graph_feed_host = self._feed_host
+        self._pinned = (key, caches)
+        self.last = slot
+
+    def step_pinned(self) -> torch.Tensor:
+        """One step of the pinned requests; nothing crosses the bus."""
+        key, caches = self._pinned
+        slot = self._slots[key]
+        self._run(slot, device_feed=True)
+        for rc in caches:
+            self.cache.commit(rc, 1)
+        self.runner.steps_run += 1
+        self.runner.rows_run += len(caches)
+        return slot.selected[: len(caches)]

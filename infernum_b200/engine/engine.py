@@ -21,7 +21,7 @@ from ..cache.manager import CacheManager
 from ..errors import InfernumError
 from ..sampling.params import GenerateOptions
 from ..sampling.sampler import Sampler, pack_choices, recent_window
-from .decode import DecodeSession
+from .decode import DecodeRunner
 from .scheduler import BatchConfig, FinishReason, Scheduler, Sequence_, StepPlan
 from .step import ModelRunner, StepEntry
 
@@ -85,8 +85,7 @@ class Engine:
         self.sampler = Sampler(rt.device)
         self.stats = EngineStats()
         self._handles: Dict[int, RequestHandle] = {}
-        self._session: Optional[DecodeSession] = None
-        self._last_decode_key = None
+        self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if cfg.cuda_graphs else None
         self.h2d_bytes = 0  # bytes of step inputs copied to the device so far
         self.d2h_bytes = 0  # bytes of step results read back so far
 
@@ -125,13 +124,15 @@ class Engine:
                 sp = p.seq.options.sampling
                 choices.append(None if sp is None else
                                (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
-            session = self._decode_session(plan, choices)
-            if session is not None:
-                sample_params = pack_choices(choices, session.recent_width)[:2] \
-                    if session.any_sampling else None
-                chosen = session.step([p.tokens[0] for p in plan.portions], sample_params)
-                self.h2d_bytes += 4 * len(plan.portions)
-                logits = session.logits
+            caches = [p.seq.cache for p in plan.portions]
+            decode_only = self.decoder is not None and all(
+                p.count == 1 and p.wants_logits for p in plan.portions) and self.decoder.can_take(caches)
+            if decode_only:
+                sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) \
+                    if any(c is not None for c in choices) else None
+                chosen = self.decoder.step(caches, [p.tokens[0] for p in plan.portions], sample)
+                self.h2d_bytes += 16 * len(plan.portions)
+                logits = self.decoder.last.logits
             else:
                 entries = [StepEntry(p.seq.cache, p.tokens, [p.count - 1] if p.wants_logits else [])
                            for p in plan.portions]
@@ -170,24 +171,6 @@ class Engine:
                 del self._handles[handle.id]
         self.stats.step_seconds += time.perf_counter() - t0
         return events
-
-    def _decode_session(self, plan: StepPlan, choices) -> Optional[DecodeSession]:
-        """The session to run this step with, when the step only decodes and the
-        same requests decoded in the step before; else None."""
-        if not self.config.cuda_graphs or any(p.count != 1 or not p.wants_logits for p in plan.portions):
-            self._session = None
-            self._last_decode_key = None
-            return None
-        key = tuple(p.seq.cache.request_id for p in plan.portions)
-        if self._session is not None and (self._session.key != key or not self._session.can_continue()):
-            self._session = None
-        if self._session is None and self._last_decode_key == key:
-            longest = max(p.seq.options.max_new_tokens - len(p.seq.generated_ids) for p in plan.portions)
-            self._session = DecodeSession(
-                self.runner, [p.seq.cache for p in plan.portions], [p.tokens[0] for p in plan.portions],
-                max_steps=longest + 1, use_graph=True, sampling_rows=[c is not None for c in choices])
-        self._last_decode_key = key
-        return self._session
 
     def run_until_done(self, handles: Optional[Sequence[RequestHandle]] = None) -> None:
         while self.has_work() and (handles is None or any(not h.finished for h in handles)):

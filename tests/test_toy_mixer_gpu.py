@@ -86,7 +86,8 @@ def test_toy_mixer_with_state_steps_like_a_whole_run(dtype, tmp_path):
     def run(cuts_a, cuts_b):
         cache = CacheManager(needs, page_size=4, num_pages=24, max_requests=3,
                              dtype=model.rt.dtype, device=DEV)
-        assert cache.layer_caches[0].state.shape == (3, 32) and cache.layer_caches[1].state is None
+        # one row per request slot, and one more that rows padding a batch write to
+        assert cache.layer_caches[0].state.shape == (3 + 1, 32) and cache.layer_caches[1].state is None
         runner = ModelRunner(model, cache)
         # a request that lived in the slot before leaves state behind: it must be zeroed
         old = cache.admit("old")
