@@ -156,3 +156,30 @@ def test_command_line_generate(folders):
                            "--dtype", "float32"], capture_output=True, text=True, timeout=600)
     assert out2.returncode == 0, out2.stderr[-3000:]
     assert "Sampling: temperature=0.9, top_p=0.8, seed=7, repetition_penalty=1.3 (window=64)" in out2.stdout
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_come_and_go_under_recorded_decode_graphs(folders, dtype):
+    """Requests of different lengths leave the batch one by one and a late one
+    joins: the decode graphs are recorded per batch bucket, not per set of
+    requests, rows that only pad a bucket do no harm, and every request gets
+    the tokens it gets alone."""
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype=dtype)
+    cfg = ib.BatchConfig(max_batch_size=8, block_size=8, num_blocks=96, max_prefill_tokens=64)
+    engine = ib.Engine(model, cfg)
+    prompts = [random_tokens(n, 320, 30 + n) for n in (3, 11, 7, 20, 5)]
+    news = [4, 30, 9, 17, 24]
+    opts = [ib.GenerateOptions(max_new_tokens=n) for n in news]
+    handles = [engine.submit(p, o) for p, o in zip(prompts[:4], opts[:4])]
+    for _ in range(6):
+        engine.step()
+    handles.append(engine.submit(prompts[4], opts[4]))  # joins while the others decode
+    engine.run_until_done(handles)
+    recorded = [k for k, s in engine.decoder._slots.items() if s.graph is not None]
+    assert recorded and len(recorded) <= 4  # buckets 1, 2, 4, 8 at most: not one per composition
+    solo = ib.Engine(model, cfg)
+    for p, o, h in zip(prompts, opts, handles):
+        assert len(h.tokens) == o.max_new_tokens
+        assert_same_up_to_ties(folders["B"], p, h.tokens, solo.generate(p, o), dtype)
+    assert engine.cache.free_pages() == [96] and engine.cache.num_free_slots == 8
