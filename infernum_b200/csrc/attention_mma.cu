@@ -675,7 +675,9 @@ IB_EXPORT long long ib_attention_mma_scratch_bytes(int n_rows, int nh, int split
 // mode bits: 1 = launch tile mode, 2 = launch split mode.  With both, an entry
 // whose rows times min(group, 8) is at most 8 goes to split mode and the rest
 // to tile mode; with one bit every entry is taken by that mode, except that
-// split mode can never take an entry with more than 8 packed rows.
+// split mode can never take an entry with more than 8 packed rows.  Bit 4 with
+// bit 2: the tile-mode entries were computed by another kernel; only the small
+// entries are taken here.
 IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                void* out, int out_stride, const int* cu_rows, const int* q_start,
                                const int* block_tables, int max_blocks, int n_entries, int n_rows,
@@ -725,10 +727,13 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     p.part_ml = nullptr;
     p.cluster_merge = 0;
     // which entries each mode takes
-    if ((mode & 3) == 3) p.small_rows = 8;
+    const bool tiles_done_elsewhere = (mode & 4) != 0;  // another kernel took the tile-mode entries
+    if (tiles_done_elsewhere) mode = 2;
+    if ((mode & 3) == 3 || tiles_done_elsewhere) p.small_rows = 8;
     else if (mode & 2) p.small_rows = 1 << 30;   // everything is "small"
     else p.small_rows = -1;                      // nothing is "small"
-    if ((mode & 2) && !(mode & 1) && max_rows_per_entry * p.gs_split > 8) return IB_ERR_BAD_ARG;
+    if ((mode & 2) && !(mode & 1) && !tiles_done_elsewhere && max_rows_per_entry * p.gs_split > 8)
+        return IB_ERR_BAD_ARG;
     if (n_entries > 65535 || nkv * p.n_hsub > 65535) return IB_ERR_TOO_LARGE;
 
     static bool attr_done = false;

@@ -1,0 +1,497 @@
+// Prompt attention over the paged cache on the tcgen05 tensor cores (bf16),
+// one head size per build (-DIB_HD=64 or 128).
+//
+// A CTA owns 128 packed rows - query rows of one request times the query heads
+// that share one key/value head - and walks the keys in tiles of 64:
+//
+//   producer warp   TMA: the query tile once (a 3-D box: dims x heads x rows,
+//                   which lands in packed-row order), then per tile the pages
+//                   of K and of V through the request's block table (2-D
+//                   boxes of page_size x 64, 128-byte swizzle)
+//   MMA warp        S = Q K^T into tensor memory (8 MMAs of 128 x 64 x 16),
+//                   then O += P V (4 MMAs of 128 x HD x 16, V as an N-major
+//                   operand straight from its [key][dim] rows)
+//   4 softmax warps one thread per packed row = one TMEM lane: read the
+//                   scores with tcgen05.ld, mask, running maximum and sum in
+//                   32-bit, write P as bf16 into shared memory in the
+//                   swizzled layout the MMA reads, and rescale the output
+//                   accumulator in tensor memory when a maximum moved
+//
+// K's buffer is free once S has been computed and V's once O has been
+// updated, so the next tile's pages load while the current tile is processed;
+// two CTAs share an SM and fill each other's gaps.  Every wait is bounded.
+//
+// Same mathematics as attention_plain.cu; what it restates of the reference is
+// cited there.  The reference has no tensor-core attention kernel.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#ifndef IB_HD
+#define IB_HD 128
+#endif
+
+using namespace ib;
+
+namespace {
+
+constexpr int HD = IB_HD;
+static_assert(HD == 64 || HD == 128, "this kernel is built for head sizes 64 and 128");
+constexpr int BM = 128;                 // packed rows per CTA
+constexpr int BN = 64;                  // keys per tile
+constexpr int KB = HD / 64;             // 64-wide blocks of the head dimension
+constexpr int NUM_THREADS = 192;        // 4 softmax warps, producer, MMA
+constexpr unsigned WAIT_LIMIT = 1u << 20;
+constexpr int Q_BYTES = BM * HD * 2;
+constexpr int K_BYTES = BN * HD * 2;
+constexpr int V_BYTES = BN * HD * 2;
+constexpr int P_BYTES = BM * BN * 2;
+constexpr int SMEM_BYTES = Q_BYTES + K_BYTES + V_BYTES + P_BYTES + 1024;
+constexpr unsigned TMEM_COLS = 256;     // scores in columns [0, 64), output in [64, 64 + HD)
+constexpr unsigned O_COL = 64;
+
+struct Params {
+    bf16* out;
+    const int* cu_rows;
+    const int* q_start;
+    const int* block_tables;
+    unsigned* err;
+    int out_stride, max_blocks, nh, nkv, page_size, num_pages;
+    int small_rows;     // entries with rows * min(group, 8) <= small_rows belong to split mode
+    float scale_log2;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool elect_one() {
+    unsigned pred = 0;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, void* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned addr, unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_st16(unsigned addr, const unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// K-major operand tile with 128-byte rows and the 128-byte swizzle: groups of 8
+// rows are 1024 bytes apart.  (Addresses and offsets in units of 16 bytes;
+// version 1; layout type 2 = SWIZZLE_128B.)
+__device__ __forceinline__ uint64_t desc_k_major(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// N-major operand (V as [key][dim] rows of 128 bytes, swizzled): along K, groups
+// of 8 keys are 1024 bytes apart (stride byte offset); along N, the next block
+// of 64 dims starts `block_bytes` further on (leading byte offset).
+__device__ __forceinline__ uint64_t desc_n_major(const void* tile, unsigned block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) >> 4) & 0x3FFF);
+    d |= (uint64_t)((block_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// float32 accumulator, bf16 operands, A K-major; B K-major or N-major (bit 16).
+__host__ __device__ constexpr unsigned make_idesc(int n, bool b_n_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_n_major ? (1u << 16) : 0u) |
+           ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;
+    unsigned char* k_s = q_s + Q_BYTES;
+    unsigned char* v_s = k_s + K_BYTES;
+    unsigned char* p_s = v_s + V_BYTES;
+    __shared__ __align__(8) unsigned long long q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_done;
+    __shared__ unsigned tmem_slot;
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y, g = blockIdx.z;
+    const int G = p.nh / p.nkv;
+    const int rq = BM / G;  // query rows per CTA
+    const int row0 = p.cu_rows[e];
+    const int rows_e = p.cu_rows[e + 1] - row0;
+    const int pos0 = p.q_start[e];
+    const int gs_split = G < 8 ? G : 8;
+    if (rows_e * gs_split <= p.small_rows) return;  // split mode takes this entry
+    // the last rows see the most keys: their CTAs go first
+    const int r_begin = ((int)gridDim.x - 1 - (int)blockIdx.x) * rq;
+    if (r_begin >= rows_e) return;
+    const int r_count = min(rq, rows_e - r_begin);
+    const int kv_hi = pos0 + r_begin + r_count;
+    const int n_tiles = (kv_hi + BN - 1) / BN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        mbar_init(&k_full, 1);
+        mbar_init(&k_empty, 1);
+        mbar_init(&v_full, 1);
+        mbar_init(&v_empty, 1);
+        mbar_init(&s_full, 1);
+        mbar_init(&p_full, 128);
+        mbar_init(&o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = tmem_slot;
+    pdl_wait();  // queries, keys and values come from the kernels before this one
+
+    if (warp == 4) {
+        // ---- producer -------------------------------------------------------------
+        if (elect_one()) {
+            const int* table = p.block_tables + (size_t)e * p.max_blocks;
+            mbar_expect_tx(&q_full, Q_BYTES);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_3d(q_s + kb * (BM * 128), &map_q, &q_full, kb * 64, g * G, row0 + r_begin);
+            const int pages_per_tile = BN / p.page_size;
+            bool ok = true;
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                for (int which = 0; which < 2 && ok; ++which) {
+                    void* full = which == 0 ? (void*)&k_full : (void*)&v_full;
+                    void* empty = which == 0 ? (void*)&k_empty : (void*)&v_empty;
+                    unsigned char* dst = which == 0 ? k_s : v_s;
+                    const CUtensorMap* map = which == 0 ? &map_k : &map_v;
+                    if (t > 0 && !mbar_wait(empty, (t - 1) & 1)) {
+                        atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full, K_BYTES);
+                    for (int pg = 0; pg < pages_per_tile; ++pg) {
+                        const int j = t * BN + pg * p.page_size;
+                        int page = j < kv_hi ? table[j / p.page_size] : 0;
+                        if (page < 0 || page >= p.num_pages) {
+                            atomicOr(p.err, IB_FLAG_BAD_PAGE);
+                            page = 0;
+                        }
+                        const int y = (page * p.nkv + g) * p.page_size;
+#pragma unroll
+                        for (int kb = 0; kb < KB; ++kb)
+                            tma_load_2d(dst + kb * (BN * 128) + pg * p.page_size * 128, map, full, kb * 64, y);
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issuer -------------------------------------------------------------
+        if (elect_one()) {
+            constexpr unsigned idesc_s = make_idesc(BN, false);
+            constexpr unsigned idesc_o = make_idesc(HD, true);
+            bool ok = mbar_wait(&q_full, 0);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                // S = Q K^T.  The score columns are free: the softmax warps read
+                // tile t-1's scores before they signalled p_full, which was waited for.
+                if (!mbar_wait(&k_full, t & 1)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+                    const uint64_t a = desc_k_major(q_s + kb * (BM * 128));
+                    const uint64_t b = desc_k_major(k_s + kb * (BN * 128));
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_bf16(tmem, a + 2 * kk, b + 2 * kk, idesc_s, (kb > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&k_empty);
+                umma_commit(&s_full);
+                // O += P V once the softmax warps have written P (and rescaled O)
+                if (!mbar_wait(&p_full, t & 1) || !mbar_wait(&v_full, t & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t a = desc_k_major(p_s);
+                const uint64_t b = desc_n_major(v_s, BN * 128);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    umma_bf16(tmem + O_COL, a + 2 * kk, b + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_o,
+                              (t > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&v_empty);
+                umma_commit(&o_done);
+            }
+            if (!ok) {
+                atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+                // let the softmax warps run out of their waits quickly
+            }
+        }
+    } else {
+        // ---- softmax: thread m owns packed row m = TMEM lane m ---------------------
+        const int m = threadIdx.x;  // 0..127
+        const int r = m / G, h = m % G;
+        const bool valid = r < r_count;
+        const int my_pos = valid ? pos0 + r_begin + r : -1;
+        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            if (ok && !mbar_wait(&s_full, t & 1)) ok = false;
+            tc_fence_after();
+            float s[BN];
+#pragma unroll
+            for (int c = 0; c < BN; c += 16) {
+                unsigned v[16];
+                tmem_ld16(lane_addr + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) s[c + j] = __uint_as_float(v[j]);
+            }
+            const int tile_start = t * BN;
+            float m_new = m_run;
+            if (tile_start + BN - 1 > pos0 + r_begin || !valid) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    s[c] = (tile_start + c <= my_pos) ? s[c] * p.scale_log2 : -INFINITY;
+                    m_new = fmaxf(m_new, s[c]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    s[c] *= p.scale_log2;
+                    m_new = fmaxf(m_new, s[c]);
+                }
+            }
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = fast_exp2(m_run - m_use);
+            m_run = m_new;
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < BN; ++c) {
+                s[c] = fast_exp2(s[c] - m_use);
+                sum += s[c];
+            }
+            l_run = l_run * corr + sum;
+            // the output accumulator holds tiles 0..t-1: rescale it if any row of
+            // this warp moved its maximum (tile t-1's update must have completed)
+            if (t > 0) {
+                if (ok && !mbar_wait(&o_done, (t - 1) & 1)) ok = false;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+                    for (int c = 0; c < HD; c += 16) {
+                        unsigned v[16];
+                        tmem_ld16(lane_addr + O_COL + c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+                        tmem_st16(lane_addr + O_COL + c, v);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // P (bf16) into the K-major swizzled tile [128 rows][64 keys]: row m,
+            // 16-byte chunk ch sits at chunk position ch ^ (m % 8) of its 128-byte row
+#pragma unroll
+            for (int ch = 0; ch < BN / 8; ++ch) {
+                uint4 pk;
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(s[ch * 8 + 2 * j], s[ch * 8 + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(p_s + m * 128 + ((ch ^ (m & 7)) << 4)) = pk;
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(&p_full);
+        }
+        // ---- epilogue: O / l -------------------------------------------------------
+        if (n_tiles > 0) {
+            if (ok && !mbar_wait(&o_done, (n_tiles - 1) & 1)) ok = false;
+            tc_fence_after();
+        }
+        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        bf16* dst = valid ? p.out + (size_t)(row0 + r_begin + r) * p.out_stride + (size_t)(g * G + h) * HD : nullptr;
+#pragma unroll
+        for (int c = 0; c < HD; c += 16) {
+            unsigned v[16];
+            tmem_ld16(lane_addr + O_COL + c, v);
+            tmem_ld_wait();
+            if (valid && ok) {
+                uint4 lo, hi;
+                __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    l2[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]) * inv, __uint_as_float(v[2 * j + 1]) * inv);
+                    h2[j] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * j]) * inv,
+                                                  __uint_as_float(v[8 + 2 * j + 1]) * inv);
+                }
+                *reinterpret_cast<uint4*>(dst + c) = lo;
+                *reinterpret_cast<uint4*>(dst + c + 8) = hi;
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+}  // namespace
+
+IB_EXPORT int ib_attention_tc_head_dim() { return HD; }
+
+// Tile-mode attention for every entry with more rows than split mode takes.
+// Needs: bf16, head size 64 or 128, (heads / kv_heads) a divisor of 128,
+// page_size a multiple of 8 that divides 64, no window, 16-byte aligned q rows.
+IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, void* out,
+                              int out_stride, const int* cu_rows, const int* q_start, const int* block_tables,
+                              int max_blocks, int n_entries, int n_rows, int max_rows_per_entry, int nh, int nkv,
+                              int page_size, int num_pages, float scale, int small_rows, unsigned* err,
+                              void* stream) {
+    if (n_entries <= 0 || n_rows <= 0) return IB_OK;
+    if (!q || !k_pool || !v_pool || !out || !cu_rows || !q_start || !block_tables || !err) return IB_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv) return IB_ERR_BAD_ARG;
+    const int G = nh / nkv;
+    if (BM % G || page_size % 8 || BN % page_size || (q_stride % 8) || (out_stride % 8) ||
+        ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
+        return IB_ERR_UNSUPPORTED;
+    if (n_entries > 65535 || nkv > 65535) return IB_ERR_TOO_LARGE;
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return IB_ERR_UNSUPPORTED;
+    const int rq = BM / G;
+    CUtensorMap mq, mk, mv;
+    {
+        // queries as [row][head][dim]; a box of 64 dims x G heads x rq rows lands in
+        // packed-row order (row-major over (row, head))
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nh, (cuuint64_t)n_rows};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_stride * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)rq};
+        cuuint32_t es[3] = {1, 1, 1};
+        if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return IB_ERR_BAD_ARG;
+    }
+    for (int which = 0; which < 2; ++which) {
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)num_pages * nkv * page_size};
+        cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(which ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                const_cast<void*>(which ? v_pool : k_pool), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return IB_ERR_BAD_ARG;
+    }
+    Params p;
+    p.out = (bf16*)out;
+    p.cu_rows = cu_rows;
+    p.q_start = q_start;
+    p.block_tables = block_tables;
+    p.err = err;
+    p.out_stride = out_stride;
+    p.max_blocks = max_blocks;
+    p.nh = nh;
+    p.nkv = nkv;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.small_rows = small_rows;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e1 = cudaFuncSetAttribute(attention_tcgen05_kernel,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e1 != cudaSuccess) return (int)e1;
+        attr_done = true;
+    }
+    dim3 grid((max_rows_per_entry + rq - 1) / rq, n_entries, nkv);
+    cudaError_t le = launch_kernel(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), (size_t)SMEM_BYTES,
+                                   (cudaStream_t)stream, mq, mk, mv, p);
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

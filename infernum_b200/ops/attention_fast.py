@@ -22,6 +22,7 @@ from . import core
 
 _c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 _libs: Dict[int, ctypes.CDLL] = {}
+_tc_libs: Dict[int, ctypes.CDLL] = {}
 SM_COUNT_FALLBACK = 148
 
 
@@ -45,6 +46,31 @@ def lib_for(head_dim: int) -> ctypes.CDLL:
             raise KernelError(f"attention module for head size {head_dim} was built for another size")
         _libs[head_dim] = lib
     return lib
+
+
+def tc_lib_for(head_dim: int) -> ctypes.CDLL:
+    """The tcgen05 prompt-attention module for a head size (64 or 128)."""
+    lib = _tc_libs.get(head_dim)
+    if lib is None:
+        lib = load_module(f"attn_tc_hd{head_dim}", ["attention_tcgen05.cu"], [f"-DIB_HD={head_dim}"])
+        lib.ib_attention_tc.argtypes = [
+            _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
+            _c_void_p]
+        lib.ib_attention_tc.restype = _c_int
+        _tc_libs[head_dim] = lib
+    return lib
+
+
+def tc_eligible(q, k_pool, out, n_heads: int, window: int) -> bool:
+    """Whether the tcgen05 prompt kernel takes this layer: head size 64 or 128,
+    the head group a divisor of 128, pages of 8, 16, 32 or 64 tokens, no window,
+    16-byte aligned rows."""
+    _, nkv, page_size, hd = k_pool.shape
+    G = n_heads // nkv
+    return (hd in (64, 128) and window <= 0 and 128 % G == 0 and page_size % 8 == 0
+            and 64 % page_size == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
 def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count: int) -> int:
@@ -91,6 +117,20 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
         if mode == 2:
             sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
             splits = choose_splits(ctx.n_entries, nkv * n_hsub, ctx.max_kv_len, sm)
+    if (mode & 1) and rt.options.get("prompt_attention", "tcgen05") == "tcgen05" \
+            and tc_eligible(q, k_pool, out, n_heads, window):
+        # prompt portions on the tcgen05 kernel; what is left (decoded tokens and
+        # very short portions in the same step) goes to split mode below
+        code = tc_lib_for(hd).ib_attention_tc(
+            q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+            out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
+            tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
+            page_size, num_pages, float(scale), 8 if (mode & 2) else -1, rt.err.data_ptr(),
+            core.stream_ptr(q))
+        core.check(code, "attention_tcgen05")
+        if not (mode & 2):
+            return True
+        mode = 2 | 4  # split mode for the small entries only; the others are done
     lib = lib_for(hd)
     scratch_ptr, scratch_bytes = None, 0
     if splits > 8:
@@ -104,7 +144,7 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
         q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
         out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
         tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
-        page_size, num_pages, int(window), float(scale), mode, splits, scratch_ptr, scratch_bytes,
-        rt.err.data_ptr(), core.stream_ptr(q))
+        page_size, num_pages, int(window), float(scale), mode, splits,
+        scratch_ptr, scratch_bytes, rt.err.data_ptr(), core.stream_ptr(q))
     core.check(code, "attention_mma")
     return True

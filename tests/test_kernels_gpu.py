@@ -435,3 +435,55 @@ def test_gemm_tcgen05_with_swiglu_epilogue(T, I, K):
     out2 = torch.empty(T, I, dtype=torch.bfloat16, device=DEV)
     c.silu_mul(gu, out2, block=64)
     assert rel_err(out2, want) < 2e-2
+
+
+TC_CASES = [
+    # nh, nkv, hd, ps, lengths, rows
+    (8, 2, 128, 16, [257, 64], [257, 64]),           # whole prompts
+    (8, 2, 128, 16, [300, 77, 513, 90], [1, 40, 200, 2]),   # prompt portions beside decoded tokens
+    (4, 4, 64, 8, [130, 65], [130, 33]),             # G = 1, head size 64, pages of 8
+    (16, 2, 64, 32, [100], [100]),                   # G = 8
+    (32, 1, 128, 16, [70, 200], [70, 9]),            # G = 32
+    (8, 2, 128, 64, [1000], [1000]),                 # pages of 64, many tiles
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=[f"nh{c[0]}kv{c[1]}hd{c[2]}ps{c[3]}r{max(c[5])}" for c in TC_CASES])
+def test_attention_tcgen05_against_plain(case):
+    from infernum_b200.ops import attention_fast
+    from infernum_b200.parts.base import Runtime
+    nh, nkv, hd, ps, lens, rows = case
+    c = core()
+    q, kp, vp, tables, ctx, refs = paged_case(lens, rows, nh, nkv, hd, ps, torch.bfloat16, 11)
+    # queries sit in rows as wide as the fused qkv rows of the engine
+    wide = torch.zeros(q.shape[0], (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device=DEV)
+    wide[:, : nh * hd] = q
+    out = torch.full((q.shape[0], nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert attention_fast.tc_eligible(wide, kp, out, nh, 0)
+    rt = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV))
+    assert attention_fast.run(wide, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt)
+    assert rt.err.item() == 0
+    assert torch.isfinite(out).all()
+    assert rel_err(out, plain_result(refs)) < 1e-2
+    # and against the mma.sync kernel on the same inputs
+    rt2 = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV),
+                  options={"prompt_attention": "mma"})
+    out2 = torch.empty_like(out)
+    assert attention_fast.run(wide, kp, vp, out2, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt2)
+    assert rel_err(out, out2.double()) < 1e-2
+
+
+def test_attention_tcgen05_far_key_and_edges():
+    """One key carries the answer, at tile and page edges of a long prompt."""
+    from infernum_b200.ops import attention_fast
+    from infernum_b200.parts.base import Runtime
+    c = core()
+    nh, nkv, hd, ps = 8, 2, 128, 16
+    for L, key in ((700, 0), (700, 63), (700, 64), (700, 127), (513, 511), (300, -1), (65, 64)):
+        q, kp, vp, tables, ctx, refs = paged_case([L], [L], nh, nkv, hd, ps, torch.bfloat16, L + key + 5,
+                                                  scale_key=key)
+        out = torch.full((L, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        rt = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV))
+        assert attention_fast.run(q, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt)
+        assert rt.err.item() == 0
+        assert rel_err(out, plain_result(refs)) < 1e-2, (L, key)
