@@ -17,9 +17,10 @@
 //                   swizzled layout the MMA reads, and rescale the output
 //                   accumulator in tensor memory when a maximum moved
 //
-// K's buffer is free once S has been computed and V's once O has been
-// updated, so the next tile's pages load while the current tile is processed;
-// two CTAs share an SM and fill each other's gaps.  Every wait is bounded.
+// Scores and K are double-buffered: while the softmax warps work on tile t the
+// tensor cores already compute the scores of tile t+1, and K of tile t+2 loads.
+// V's buffer is free once O has been updated.  Two CTAs share an SM and fill
+// each other's gaps.  Every wait is bounded.
 //
 // Same mathematics as attention_plain.cu; what it restates of the reference is
 // cited there.  The reference has no tensor-core attention kernel.
@@ -46,9 +47,9 @@ constexpr int Q_BYTES = BM * HD * 2;
 constexpr int K_BYTES = BN * HD * 2;
 constexpr int V_BYTES = BN * HD * 2;
 constexpr int P_BYTES = BM * BN * 2;
-constexpr int SMEM_BYTES = Q_BYTES + K_BYTES + V_BYTES + P_BYTES + 1024;
-constexpr unsigned TMEM_COLS = 256;     // scores in columns [0, 64), output in [64, 64 + HD)
-constexpr unsigned O_COL = 64;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * K_BYTES + V_BYTES + P_BYTES + 1024;  // K is double-buffered
+constexpr unsigned TMEM_COLS = 256;     // two score tiles in columns [0, 64) and [64, 128), output from 128
+constexpr unsigned O_COL = 128;
 
 struct Params {
     bf16* out;
@@ -170,9 +171,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
     unsigned char* k_s = q_s + Q_BYTES;
-    unsigned char* v_s = k_s + K_BYTES;
+    unsigned char* v_s = k_s + 2 * K_BYTES;
     unsigned char* p_s = v_s + V_BYTES;
-    __shared__ __align__(8) unsigned long long q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_done;
+    __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full,
+        o_done;
     __shared__ unsigned tmem_slot;
 
     pdl_trigger();
@@ -194,11 +196,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
-        mbar_init(&k_full, 1);
-        mbar_init(&k_empty, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+        }
         mbar_init(&v_full, 1);
         mbar_init(&v_empty, 1);
-        mbar_init(&s_full, 1);
         mbar_init(&p_full, 128);
         mbar_init(&o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -215,63 +219,92 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     pdl_wait();  // queries, keys and values come from the kernels before this one
 
     if (warp == 4) {
-        // ---- producer -------------------------------------------------------------
-        if (elect_one()) {
-            const int* table = p.block_tables + (size_t)e * p.max_blocks;
+        // ---- producer: the whole warp ------------------------------------------------
+        // Block-table entries are fetched 32 at a time (one per lane) and handed
+        // round with shuffles, so that no TMA copy waits for a dependent load; the
+        // pages of a tile are issued by as many lanes in parallel.
+        const int* table = p.block_tables + (size_t)e * p.max_blocks;
+        const int ppt = BN / p.page_size;                       // pages per tile
+        const int total_pages = (kv_hi + p.page_size - 1) / p.page_size;
+        if (lane == 0) {
             mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb)
                 tma_load_3d(q_s + kb * (BM * 128), &map_q, &q_full, kb * 64, g * G, row0 + r_begin);
-            const int pages_per_tile = BN / p.page_size;
-            bool ok = true;
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                for (int which = 0; which < 2 && ok; ++which) {
-                    void* full = which == 0 ? (void*)&k_full : (void*)&v_full;
-                    void* empty = which == 0 ? (void*)&k_empty : (void*)&v_empty;
-                    unsigned char* dst = which == 0 ? k_s : v_s;
-                    const CUtensorMap* map = which == 0 ? &map_k : &map_v;
-                    if (t > 0 && !mbar_wait(empty, (t - 1) & 1)) {
-                        atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
-                        ok = false;
-                        break;
-                    }
-                    mbar_expect_tx(full, K_BYTES);
-                    for (int pg = 0; pg < pages_per_tile; ++pg) {
-                        const int j = t * BN + pg * p.page_size;
-                        int page = j < kv_hi ? table[j / p.page_size] : 0;
-                        if (page < 0 || page >= p.num_pages) {
-                            atomicOr(p.err, IB_FLAG_BAD_PAGE);
-                            page = 0;
-                        }
-                        const int y = (page * p.nkv + g) * p.page_size;
+        }
+        struct Window { int base, page; };
+        auto refill = [&](Window& w, int base) {
+            w.base = base;
+            const int pi = base + lane;
+            int page = pi < total_pages ? table[pi] : 0;
+            if (page < 0 || page >= p.num_pages) {
+                atomicOr(p.err, IB_FLAG_BAD_PAGE);
+                page = 0;
+            }
+            w.page = page;
+        };
+        Window wk, wv;
+        refill(wk, 0);
+        wv = wk;
+        auto load = [&](unsigned char* dst, const CUtensorMap* map, void* full, int t, Window& w) {
+            const int pi0 = t * ppt;
+            if (pi0 + ppt > w.base + 32) refill(w, pi0);
+            if (lane == 0) mbar_expect_tx(full, K_BYTES);
+            __syncwarp();
+            const int page = __shfl_sync(0xffffffffu, w.page, (pi0 - w.base + lane) & 31);
+            if (lane < ppt) {
+                const int y = (page * p.nkv + g) * p.page_size;
 #pragma unroll
-                        for (int kb = 0; kb < KB; ++kb)
-                            tma_load_2d(dst + kb * (BN * 128) + pg * p.page_size * 128, map, full, kb * 64, y);
-                    }
-                }
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(dst + kb * (BN * 128) + lane * p.page_size * 128, map, full, kb * 64, y);
+            }
+        };
+        // K of tile t goes to buffer t % 2 (free once the scores of tile t - 2 are
+        // computed), V of tile t to the single V buffer (free once tile t - 1's
+        // output update is done).  K runs one tile ahead of V.
+        bool ok = true;
+        for (int t = 0; t < n_tiles + 1 && ok; ++t) {
+            if (t < n_tiles) {
+                const int b = t & 1;
+                if (t >= 2 && !mbar_wait(&k_empty[b], ((t - 2) >> 1) & 1)) { ok = false; break; }
+                load(k_s + b * K_BYTES, &map_k, &k_full[b], t, wk);
+            }
+            if (t >= 1) {
+                const int tv = t - 1;
+                if (tv >= 1 && !mbar_wait(&v_empty, (tv - 1) & 1)) { ok = false; break; }
+                load(v_s, &map_v, &v_full, tv, wv);
             }
         }
+        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
     } else if (warp == 5) {
         // ---- MMA issuer -------------------------------------------------------------
         if (elect_one()) {
             constexpr unsigned idesc_s = make_idesc(BN, false);
             constexpr unsigned idesc_o = make_idesc(HD, true);
             bool ok = mbar_wait(&q_full, 0);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                // S = Q K^T.  The score columns are free: the softmax warps read
-                // tile t-1's scores before they signalled p_full, which was waited for.
-                if (!mbar_wait(&k_full, t & 1)) { ok = false; break; }
+            // scores of tile t into score buffer t % 2
+            auto issue_scores = [&](int t) -> bool {
+                const int b = t & 1;
+                if (!mbar_wait(&k_full[b], (t >> 1) & 1)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb) {
                     const uint64_t a = desc_k_major(q_s + kb * (BM * 128));
-                    const uint64_t b = desc_k_major(k_s + kb * (BN * 128));
+                    const uint64_t bd = desc_k_major(k_s + b * K_BYTES + kb * (BN * 128));
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma_bf16(tmem, a + 2 * kk, b + 2 * kk, idesc_s, (kb > 0 || kk > 0) ? 1u : 0u);
+                        umma_bf16(tmem + b * BN, a + 2 * kk, bd + 2 * kk, idesc_s, (kb > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(&k_empty);
-                umma_commit(&s_full);
+                umma_commit(&k_empty[b]);
+                umma_commit(&s_full[b]);
+                return true;
+            };
+            if (ok) ok = issue_scores(0);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                // The scores of tile t + 1 are computed while the softmax warps work on
+                // tile t.  Their buffer held tile t - 1, which the softmax warps read
+                // before they signalled p_full(t - 1), waited for in the last round.
+                if (t + 1 < n_tiles && !issue_scores(t + 1)) { ok = false; break; }
                 // O += P V once the softmax warps have written P (and rescaled O)
                 if (!mbar_wait(&p_full, t & 1) || !mbar_wait(&v_full, t & 1)) { ok = false; break; }
                 tc_fence_after();
@@ -299,13 +332,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int t = 0; t < n_tiles; ++t) {
-            if (ok && !mbar_wait(&s_full, t & 1)) ok = false;
+            if (ok && !mbar_wait(&s_full[t & 1], (t >> 1) & 1)) ok = false;
             tc_fence_after();
             float s[BN];
 #pragma unroll
             for (int c = 0; c < BN; c += 16) {
                 unsigned v[16];
-                tmem_ld16(lane_addr + c, v);
+                tmem_ld16(lane_addr + (t & 1) * BN + c, v);
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) s[c + j] = __uint_as_float(v[j]);
