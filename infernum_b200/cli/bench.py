@@ -74,6 +74,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-warmup", action="store_true",
+                    help="mixed: time the first pass too (it records the decode graphs)")
     ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
     return ap
 
@@ -148,6 +150,9 @@ def run_mixed(model, args) -> dict:
     opts = [ib.GenerateOptions(max_new_tokens=new_tokens, ignore_eos=True,
                                sampling=ib.SamplingParams(temperature=0.8, top_p=1.0, seed=args.seed + i))
             for i in range(n_req)]
+    if not args.no_warmup:
+        engine.generate_batch(prompts, opts)  # records the decode graphs of every batch bucket met
+        engine.stats = type(engine.stats)()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = engine.generate_batch(prompts, opts)
