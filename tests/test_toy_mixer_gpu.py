@@ -123,3 +123,138 @@ def test_toy_mixer_with_state_steps_like_a_whole_run(dtype, tmp_path):
         scale = whole[k].abs().max()
         assert (whole[k] - cut[k]).abs().max() / scale < tol
     assert (whole["a"][:17] - whole["b"]).abs().max() > 1e-3  # the two requests are not mixed up
+
+
+def define_toy_parts():
+    """A position encoding and a routed feed-forward defined here, registered
+    through the package's registries."""
+    from infernum_b200.parts import (FeedForward, PositionEncoding, WeightSpec, register_feed_forward,
+                                     register_position_encoding)
+
+    @register_position_encoding("toy_scaled")
+    class ScaledPositions(PositionEncoding):
+        """q and k are scaled by (1 + rate * position): not a rotation, so the
+        attention part must take its general route (apply, then store k and v)."""
+
+        def __init__(self, params, rt):
+            super().__init__(params, rt)
+            self.rate = params["rate"]
+
+        def apply(self, q, k, positions):
+            f = (1.0 + self.rate * positions.float()).to(q.dtype)
+            q.mul_(f[:, None, None])
+            if k is not None:
+                k.mul_(f[:, None, None])
+
+    @register_feed_forward("toy_routed")
+    class RoutedFFN(FeedForward):
+        """Each token goes to the expert with the largest router logit (computed
+        in 32-bit); an expert is one matrix."""
+
+        def __init__(self, params, rt):
+            super().__init__(params, rt)
+            self.h, self.n, self.prefix = params["hidden_size"], params["experts"], params["prefix"]
+
+        def weight_specs(self):
+            specs = {self.prefix + "router.weight": WeightSpec((self.n, self.h), std=1.0)}
+            for i in range(self.n):
+                specs[self.prefix + f"experts.{i}.weight"] = WeightSpec((self.h, self.h), std=0.1)
+            return specs
+
+        def bind(self, weights):
+            self.router = weights[self.prefix + "router.weight"].float()
+            self.experts = [weights[self.prefix + f"experts.{i}.weight"] for i in range(self.n)]
+
+        def forward(self, x, ctx):
+            choice = (x.float() @ self.router.T).argmax(dim=-1)
+            out = torch.zeros_like(x)
+            for i, w in enumerate(self.experts):
+                rows = (choice == i).nonzero().flatten()
+                if rows.numel():
+                    out[rows] = (x[rows].float() @ w.float().T).to(x.dtype)
+            return out
+
+
+def toy_parts_spec(H=48, V=60):
+    from infernum_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleItem
+    layers = []
+    for i in range(2):
+        p = f"layers.{i}."
+        norm = lambda n: PartSpec("rmsnorm", {"hidden_size": H, "eps": 1e-5, "weight": p + n})  # noqa: E731
+        layers.append(LayerSpec("prenorm", name=p, parts={
+            "norm1": norm("n1"),
+            "mixer": PartSpec("attention", {"hidden_size": H, "num_heads": 3, "num_kv_heads": 3, "head_dim": 16,
+                                            "prefix": p + "attn.",
+                                            "position": {"kind": "toy_scaled", "params": {"rate": 0.02}}}),
+            "norm2": norm("n2"),
+            "ffn": PartSpec("toy_routed", {"hidden_size": H, "experts": 3, "prefix": p + "moe."}) if i == 1
+            else PartSpec("swiglu", {"hidden_size": H, "intermediate_size": 96, "prefix": p + "mlp."})}))
+    return ModelSpec(
+        hidden_size=H, vocab_size=V,
+        embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "weight": "emb"}),
+        layers=tuple(layers), schedule=(ScheduleItem(0), ScheduleItem(1)),
+        final_norm=PartSpec("rmsnorm", {"hidden_size": H, "eps": 1e-5, "weight": "fn"}),
+        lm_head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "weight": "head"}), max_position=128)
+
+
+def test_toy_position_encoding_and_routed_feed_forward():
+    """Different feed-forwards in different layers, a position encoding the
+    attention part has no fused route for: whole prompts equal portions, and
+    the first layer equals a by-hand float64 computation."""
+    import plain_llama as pl
+    from infernum_b200.cache import CacheManager
+    from infernum_b200.engine.step import ModelRunner, StepEntry
+    from infernum_b200.models.model import Model
+    from infernum_b200.ops import core
+    from infernum_b200.parts.base import Runtime
+    from infernum_b200.weights.random_init import random_tensors
+    define_toy_parts()
+    rt = Runtime(DEV, torch.float32, err=core.new_error_word(DEV))
+    model = Model(toy_parts_spec(), rt)
+    W = random_tensors(model.weight_specs(), 9, DEV, torch.float32)
+    for k in W:
+        if "attn" in k:
+            W[k] = W[k] * 8
+    model.bind(W)
+    tokens = [int(t) for t in (torch.arange(37) * 11) % 60]
+
+    def run(cuts):
+        cache = CacheManager(model.cache_needs(), page_size=4, num_pages=16, max_requests=1,
+                             dtype=torch.float32, device=DEV)
+        runner = ModelRunner(model, cache)
+        rc = cache.admit("r")
+        rows, pos = [], 0
+        for n in cuts:
+            rows.append(runner.step([StepEntry(rc, tokens[pos: pos + n], list(range(n)))]))
+            pos += n
+        runner.check_errors()
+        return torch.cat(rows).cpu()
+
+    whole, cut = run([37]), run([5, 1, 9, 2, 1, 19])
+    assert torch.isfinite(whole).all()
+    assert (whole - cut).abs().max() / whole.abs().max() < 1e-5
+    # layer 0's attention by hand: scaled q and k instead of rotated ones
+    Wd = {k: v.double().cpu() for k, v in W.items()}
+    T = len(tokens)
+    h = Wd["emb"][tokens]
+    x = pl.rms_norm(h, Wd["layers.0.n1"], 1e-5)
+    f = (1.0 + 0.02 * torch.arange(T, dtype=torch.float32)).double()[:, None, None]
+    q = (x @ Wd["layers.0.attn.q_proj.weight"].T).view(T, 3, 16) * f
+    k = (x @ Wd["layers.0.attn.k_proj.weight"].T).view(T, 3, 16) * f
+    v = (x @ Wd["layers.0.attn.v_proj.weight"].T).view(T, 3, 16)
+    h = h + pl.attention(q, k, v).reshape(T, 48) @ Wd["layers.0.attn.o_proj.weight"].T
+    h = h + pl.swiglu(pl.rms_norm(h, Wd["layers.0.n2"], 1e-5), Wd["layers.0.mlp.gate_proj.weight"],
+                      Wd["layers.0.mlp.up_proj.weight"], Wd["layers.0.mlp.down_proj.weight"])
+    # layer 1: attention the same way, then the routed feed-forward
+    x = pl.rms_norm(h, Wd["layers.1.n1"], 1e-5)
+    q = (x @ Wd["layers.1.attn.q_proj.weight"].T).view(T, 3, 16) * f
+    k = (x @ Wd["layers.1.attn.k_proj.weight"].T).view(T, 3, 16) * f
+    v = (x @ Wd["layers.1.attn.v_proj.weight"].T).view(T, 3, 16)
+    h = h + pl.attention(q, k, v).reshape(T, 48) @ Wd["layers.1.attn.o_proj.weight"].T
+    m = pl.rms_norm(h, Wd["layers.1.n2"], 1e-5)
+    choice = (m @ Wd["layers.1.moe.router.weight"].T).argmax(dim=-1)
+    moe = torch.stack([m[t] @ Wd[f"layers.1.moe.experts.{int(choice[t])}.weight"].T for t in range(T)])
+    h = h + moe
+    want = pl.rms_norm(h, Wd["fn"], 1e-5) @ Wd["head"].T
+    assert (whole.double() - want).abs().max() / want.abs().max() < 5e-5
+    assert len(set(choice.tolist())) > 1  # more than one expert was used
