@@ -16,7 +16,8 @@ line is printed:
              fraction of the measured bf16 matmul peak its flops reach
   roofline   bytes a decode step must read (every weight once, the cache of
              the live requests) / its time, against the measured copy bandwidth
-  points     decode tokens/s at batch 1 and at batch 64
+  points     decode tokens/s at batch 1 and at batch 64 (1,024-token prompts), and
+             at batch 8 near the end of an 8,192-token context
 
 Weights (15 GB) and cache are far larger than the 126 MB L2, so every timed
 step streams its inputs from HBM; no L2 flush is needed between steps.
@@ -332,6 +333,11 @@ def main() -> int:
                 points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
                 points[f"decode_b{b}_hbm_frac"] = round(
                     r["bytes_per_step"] / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+            # the same batch of 8 near the end of the 8,192-token context the configuration names
+            r = time_decode(model, 8, 8192 - 128, 32, warmup, args.page_size, args.seed + 9)
+            points["decode_b8_ctx8k"] = round(r["tokens_per_s"], 1)
+            points["decode_b8_ctx8k_hbm_frac"] = round(
+                r["bytes_per_step"] / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
             prefill = time_prefill(model, cfg, layers, 2048, args.page_size, peaks)
     finally:
         clocks.stop()
