@@ -222,9 +222,13 @@ class Scheduler:
                 self.waiting.popleft()
                 continue
             first = min(seq.remaining, cfg.max_prefill_tokens, budget)
-            fit = self._fit(None, first)
-            if fit < first and (self.running or fit <= 0):
-                break  # the head request's first portion does not fit: wait, skip nobody
+            # A request that was preempted comes back only when all it has to
+            # recompute fits: let back in for one portion it would run out of pages
+            # again at once and be preempted again.
+            need = seq.remaining if seq.preemptions else first
+            fit = self._fit(None, need)
+            if fit < need and (self.running or fit <= 0):
+                break  # the head request does not fit yet: wait, skip nobody
             self.waiting.popleft()
             seq.cache = self.cache.admit(seq.id)
             seq.phase = Phase.PREFILL

@@ -204,3 +204,29 @@ def test_many_requests_random_lengths_all_finish():
     for s, (p, n) in zip(seqs, reqs):
         assert s.generated_ids == solo_tokens(p, n)
     assert cache.free_pages() == [40]
+
+
+def test_a_preempted_request_waits_until_its_whole_recomputation_fits():
+    sched, cache = make(num_blocks=10, block_size=4, budget=64, chunk=4, max_batch=2)
+    a = sched.add_request([1] * 12, GenerateOptions(max_new_tokens=40))
+    b = sched.add_request([2] * 12, GenerateOptions(max_new_tokens=40))
+    log = []
+    while not b.preemptions:
+        run_step(sched, cache, log)
+    # b now has its prompt and what it generated to recompute; a keeps growing.  While
+    # fewer pages are free than b's tokens need, b stays in the queue even though a
+    # first portion of 4 tokens would fit.
+    readmitted_at = None
+    for _ in range(200):
+        free_before = cache.free_pages()[0]
+        need = cache.pages_for(b.num_tokens)
+        plan = run_step(sched, cache, log)
+        if b in plan.admitted:
+            readmitted_at = (free_before, need)
+            break
+        if not sched.has_work():
+            break
+    assert readmitted_at is not None and readmitted_at[0] >= readmitted_at[1]
+    drain(sched, cache)
+    assert len(a.generated_ids) == 40 and len(b.generated_ids) == 40
+    assert b.preemptions <= 2
