@@ -207,7 +207,7 @@ def test_many_requests_random_lengths_all_finish():
 
 
 def test_a_preempted_request_waits_until_its_whole_recomputation_fits():
-    sched, cache = make(num_blocks=10, block_size=4, budget=64, chunk=4, max_batch=2)
+    sched, cache = make(num_blocks=16, block_size=4, budget=64, chunk=4, max_batch=2)
     a = sched.add_request([1] * 12, GenerateOptions(max_new_tokens=40))
     b = sched.add_request([2] * 12, GenerateOptions(max_new_tokens=40))
     log = []
@@ -218,6 +218,7 @@ def test_a_preempted_request_waits_until_its_whole_recomputation_fits():
     # first portion of 4 tokens would fit.
     readmitted_at = None
     for _ in range(200):
+        sched._reap()  # what the round itself does first: finished requests give their pages back
         free_before = cache.free_pages()[0]
         need = cache.pages_for(b.num_tokens)
         plan = run_step(sched, cache, log)
