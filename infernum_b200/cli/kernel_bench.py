@@ -104,6 +104,9 @@ def main(argv=None) -> int:
     ap.add_argument("--reps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--library", action="store_true", help="gemm: time the library product instead")
+    ap.add_argument("--bn", type=int, default=0, help="gemm --pair: force the tile's weight rows")
+    ap.add_argument("--swiglu", action="store_true", help="gemm --pair: SiLU(gate) * up in the epilogue")
+    ap.add_argument("--pair", action="store_true", help="gemm: the kernel on pairs of SMs (many tokens)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a graph")
     args = ap.parse_args(argv)
 
@@ -148,9 +151,14 @@ def main(argv=None) -> int:
         copies = max(2, int(300e6 / (N * K * 2)) + 1)
         ws = [torch.randn(N, K, device=dev).to(torch.bfloat16) for _ in range(copies)]
         x = torch.randn(T, K, device=dev).to(torch.bfloat16)
-        o = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+        o = torch.empty(T, N // 2 if args.swiglu else N, dtype=torch.bfloat16, device=dev)
+        gemm_tc.POLICY["sm_count"] = rt.options["sm_count"]
         if args.library:
             fns = [lambda w=w: torch.mm(x, w.t(), out=o) for w in ws]
+        elif args.pair:
+            fns = [lambda w=w: gemm_tc.gemm_pair(x, w, o, err=rt.err, swiglu=args.swiglu,
+                                                 tiling=(args.bn, 1 << 20, args.bn) if args.bn else None)
+                   for w in ws]
         else:
             fns = [lambda w=w: gemm_tc.gemm_tc(x, w, o, splits=args.splits or None) for w in ws]
         us = _time(fns, args.reps, args.warmup, not args.no_graph)

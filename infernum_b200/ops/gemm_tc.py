@@ -13,8 +13,9 @@ and are added in a fixed order through distributed shared memory.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
-from typing import Dict, Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -23,12 +24,25 @@ from . import core
 
 _c_int, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_void_p, ctypes.c_longlong
 _lib: Optional[ctypes.CDLL] = None
+_pair_lib: Optional[ctypes.CDLL] = None
 _workspaces: Dict[torch.device, dict] = {}
 
 BM, BK = 128, 64
+# What a tile of gemm_pair costs beside its width, in weight rows: its token half is
+# fetched and its prologue and epilogue run whatever the width.
+PAIR_TILE_OVERHEAD = 66
 
 # Which products the kernel takes: "all", "none", or a largest token count.
-POLICY = {"mode": os.environ.get("INFERNUM_GEMM", "auto"), "max_tokens": 64, "sm_count": 148}
+POLICY = {"mode": os.environ.get("INFERNUM_GEMM", "auto"), "max_tokens": 64, "pair_max_padding": 1.13,
+          "sm_count": 148}
+
+
+def pair_suits(T: int) -> bool:
+    """The kernel on pairs of SMs works on 256 tokens at a time; it is taken when
+    rounding ``T`` up to that wastes little (measured on the 8B gate/up product:
+    ahead of the library at 256, 512, 768, 1024 and 2048 tokens, behind it at 320
+    and 520)."""
+    return -(-T // 256) * 256 <= POLICY["pair_max_padding"] * T
 
 
 def lib() -> ctypes.CDLL:
@@ -40,8 +54,23 @@ def lib() -> ctypes.CDLL:
         l.ib_gemm_tc.restype = _c_int
         l.ib_gemm_tc_token_tile.argtypes = [_c_int]
         l.ib_gemm_tc_token_tile.restype = _c_int
+        if torch.cuda.is_available():
+            POLICY["sm_count"] = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         _lib = l
     return _lib
+
+
+def pair_lib() -> ctypes.CDLL:
+    """The kernel for many tokens, on pairs of SMs (``gemm_tcgen05_2cta.cu``)."""
+    global _pair_lib
+    if _pair_lib is None:
+        l = load_module("gemm_pair", ["gemm_tcgen05_2cta.cu"])
+        l.ib_gemm_pair.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
+        l.ib_gemm_pair.restype = _c_int
+        lib()  # the SM count
+        _pair_lib = l
+    return _pair_lib
 
 
 def _error_word(device) -> torch.Tensor:
@@ -95,30 +124,98 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
     core.check(code, "gemm_tc")
 
 
+@functools.lru_cache(maxsize=256)
+def choose_pair_tiling(T: int, N: int, sm_count: int, swiglu: bool = False) -> Tuple[int, int, int]:
+    """How ``gemm_pair`` cuts the weight rows: ``(bn_a, cols_a, bn_b)`` = ``cols_a``
+    columns of tiles ``bn_a`` rows wide, then the rest in columns ``bn_b`` wide.
+    The pairs of SMs take the tiles in turn, so the time is that of the pair with
+    the most work; a tile costs its width plus a constant (its token half is
+    fetched and its first and last steps run whatever the width).  Mostly this
+    ends in full-width tiles for the full rounds and a narrower last round."""
+    pairs = max(sm_count // 2, 1)
+    t_tiles = -(-T // 256)
+    step = 128 if swiglu else 16
+    widths = list(range(256, 127, -step))  # narrower tiles take as long as 128 rows
+    best, best_cost = (256, -(-N // 256), 256), None
+    for bn_a in (256,) if not swiglu else (256, 128):
+        all_a = -(-N // bn_a)
+        for cols_a in range(all_a, -1, -1):
+            rest = N - cols_a * bn_a
+            for bn_b in (widths if rest > 0 else [bn_a]):
+                tiles_a = cols_a * t_tiles
+                tiles_b = -(-rest // bn_b) * t_tiles if rest > 0 else 0
+                total = tiles_a + tiles_b
+                cost = 0
+                # the pairs that matter: the first, and those around the region's and the list's end
+                for pr in {0, (tiles_a - 1) % pairs, tiles_a % pairs, (total - 1) % pairs, pairs - 1}:
+                    if pr >= total:
+                        continue
+                    n_all = -(-(total - pr) // pairs)
+                    n_a = -(-(tiles_a - pr) // pairs) if pr < tiles_a else 0
+                    cost = max(cost, n_a * (bn_a + PAIR_TILE_OVERHEAD) + (n_all - n_a) * (bn_b + PAIR_TILE_OVERHEAD))
+                if best_cost is None or cost < best_cost:
+                    best, best_cost = (bn_a, cols_a, bn_b), cost
+    return best
+
+
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+              err: Optional[torch.Tensor] = None, swiglu: bool = False,
+              tiling: Optional[Tuple[int, int, int]] = None) -> None:
+    """The product for many tokens: tiles of 256 tokens x up to 256 weight rows,
+    each computed by two SMs as one (tcgen05 ``cta_group::2``); bf16 out.
+    ``swiglu`` as in ``gemm_tc``, for any number of tokens."""
+    core.require_cuda(x, w, out)
+    T, K = x.shape
+    N = w.shape[0]
+    bn_a, cols_a, bn_b = tiling or choose_pair_tiling(T, N, POLICY["sm_count"], swiglu)
+    code = pair_lib().ib_gemm_pair(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                                   out.stride(0), T, N, K, 1 if swiglu else 0, bn_a, cols_a, bn_b,
+                                   POLICY["sm_count"],
+                                   (err if err is not None else _error_word(x.device)).data_ptr(),
+                                   core.stream_ptr(x))
+    core.check(code, "gemm_pair")
+
+
 def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Takes a product or leaves it to the library.  ``auto``: up to
+    ``max_tokens`` tokens, where this kernel streams the weights faster; ``all``:
+    every product, the ones of many tokens on pairs of SMs."""
     mode = POLICY["mode"]
     if mode in ("none", "cublas", "library"):
         return False
-    if mode == "auto" and x.shape[0] > POLICY["max_tokens"]:
+    T = x.shape[0]
+    if mode == "auto" and T > POLICY["max_tokens"]:
         return False
     if not eligible(x, w, out):
         return False
-    gemm_tc(x, w, out)
+    if (pair_suits(T) and out.dtype == torch.bfloat16 and out.stride(0) % 8 == 0
+            and out.data_ptr() % 16 == 0):
+        gemm_pair(x, w, out)
+    else:
+        gemm_tc(x, w, out)
     return True
 
 
 def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor) -> bool:
     """The gate/up product with SiLU(gate) * up applied in its epilogue, when
-    the policy and the operands allow; ``out`` is [T, I]."""
+    the policy and the operands allow; ``out`` is [T, I].  Up to 64 tokens go to
+    the kernel that streams the weights once (decode), prompts to the kernel on
+    pairs of SMs when their length suits its tiles (``pair_suits``)."""
     mode = POLICY["mode"]
-    if mode in ("none", "cublas", "library") or x.shape[0] > min(POLICY["max_tokens"], 64):
+    if mode in ("none", "cublas", "library"):
         return False
     if w_interleaved.shape[0] % 128 or out.dtype != torch.bfloat16:
         return False
-    if not eligible(x, w_interleaved, out):
+    if not eligible(x, w_interleaved, out) or out.stride(0) % 8 or out.data_ptr() % 16:
         return False
-    gemm_tc(x, w_interleaved, out, splits=1, swiglu=True)
-    return True
+    T = x.shape[0]
+    if T <= min(POLICY["max_tokens"], 64):
+        gemm_tc(x, w_interleaved, out, splits=1, swiglu=True)
+        return True
+    if pair_suits(T):
+        gemm_pair(x, w_interleaved, out, swiglu=True)
+        return True
+    return False
 
 
 def error_flags(device) -> int:

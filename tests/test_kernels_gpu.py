@@ -437,6 +437,74 @@ def test_gemm_tcgen05_with_swiglu_epilogue(T, I, K):
     assert rel_err(out2, want) < 2e-2
 
 
+
+# --------------------------------------------------------------------------
+# the matrix product on pairs of SMs (prompts)
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("T, N, K", [
+    (256, 256, 64), (300, 392, 200), (129, 640, 1000), (65, 128, 72), (1000, 1024, 520), (2048, 4096, 256),
+    (515, 6000, 136),
+])
+@pytest.mark.parametrize("tiling", [None, (32, 1 << 20, 32), (112, 1, 176), (256, 2, 240), (256, 0, 144)])
+def test_gemm_pair(T, N, K, tiling):
+    """Every way of cutting the weight rows gives the product; widths that are no
+    divisor of N, token counts that are no multiple of the tile, a short K."""
+    from infernum_b200.ops import gemm_tc
+    g = torch.Generator().manual_seed(T * 1000 + N)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_pair(x.to(DEV), w.to(DEV), out, tiling=tiling)
+    assert gemm_tc.error_flags(DEV) == 0
+    assert rel_err(out, x.double() @ w.double().T) < 5e-3
+    # rounding apart, it is the product of the kernel for few tokens
+    few = torch.empty(min(T, 64), N, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_tc(x[:few.shape[0]].contiguous().to(DEV), w.to(DEV), few, splits=1)
+    assert rel_err(out[:few.shape[0]], few.double().cpu()) < 5e-3
+
+
+@pytest.mark.parametrize("T, I, K", [(256, 128, 64), (300, 192, 200), (700, 1024, 1024), (64, 320, 520)])
+@pytest.mark.parametrize("tiling", [None, (128, 1 << 20, 128), (256, 1, 128), (128, 3, 256)])
+def test_gemm_pair_with_swiglu_epilogue(T, I, K, tiling):
+    from infernum_b200.ops import gemm_tc
+    g = torch.Generator().manual_seed(I + T)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    wu = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([wg.view(I // 64, 64, K), wu.view(I // 64, 64, K)], dim=1).reshape(2 * I, K)
+    out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_pair(x.to(DEV), w.contiguous().to(DEV), out, swiglu=True, tiling=tiling)
+    assert gemm_tc.error_flags(DEV) == 0
+    gate, up = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = gate / (1 + torch.exp(-gate)) * up
+    assert rel_err(out, want) < 6e-3
+
+
+def test_gemm_pair_refuses_widths_it_cannot_run():
+    from infernum_b200.errors import KernelError
+    from infernum_b200.ops import gemm_tc
+    x = torch.zeros(256, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(256, 64, dtype=torch.bfloat16, device=DEV)
+    out = torch.empty(256, 256, dtype=torch.bfloat16, device=DEV)
+    for tiling in [(264, 1, 256), (256, 1, 24), (250, 1, 256)]:
+        with pytest.raises(KernelError):
+            gemm_tc.gemm_pair(x, w, out, tiling=tiling)
+    with pytest.raises(KernelError):  # the activation wants whole blocks of 64 gates and 64 ups
+        gemm_tc.gemm_pair(x, w, out[:, :128], swiglu=True, tiling=(192, 1, 128))
+
+
+def test_pair_tiling_covers_the_weight_rows():
+    """The chosen cut is one the kernel accepts and never costs more, by the
+    chooser's own measure, than full-width tiles."""
+    from infernum_b200.ops import gemm_tc
+    for T in (200, 256, 512, 1000, 2048, 5000):
+        for N, sw in ((4096, False), (6144, False), (28672, True), (1000, False), (128256, False), (384, True)):
+            bn_a, cols_a, bn_b = gemm_tc.choose_pair_tiling(T, N, 148, sw)
+            step = 128 if sw else 16
+            assert bn_a % step == 0 and bn_b % step == 0 and 32 <= bn_a <= 256 and 32 <= bn_b <= 256
+            assert 0 <= cols_a <= -(-N // bn_a)
+
+
 TC_CASES = [
     # nh, nkv, hd, ps, lengths, rows
     (8, 2, 128, 16, [257, 64], [257, 64]),           # whole prompts
