@@ -178,21 +178,22 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
 
 def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     """Takes a product or leaves it to the library.  ``auto``: up to
-    ``max_tokens`` tokens, where this kernel streams the weights faster; ``all``:
-    every product, the ones of many tokens on pairs of SMs."""
+    ``max_tokens`` tokens go to the kernel that streams the weights once, prompts
+    whose length suits its tiles to the kernel on pairs of SMs (inside a model
+    step it is ahead of the library, whose kernels do not start under the tail of
+    their predecessor), the rest to the library; ``all``: every product."""
     mode = POLICY["mode"]
-    if mode in ("none", "cublas", "library"):
+    if mode in ("none", "cublas", "library") or not eligible(x, w, out):
         return False
     T = x.shape[0]
-    if mode == "auto" and T > POLICY["max_tokens"]:
-        return False
-    if not eligible(x, w, out):
-        return False
-    if (pair_suits(T) and out.dtype == torch.bfloat16 and out.stride(0) % 8 == 0
-            and out.data_ptr() % 16 == 0):
-        gemm_pair(x, w, out)
-    else:
-        gemm_tc(x, w, out)
+    if T > POLICY["max_tokens"]:
+        if (pair_suits(T) and out.dtype == torch.bfloat16 and out.stride(0) % 8 == 0
+                and out.data_ptr() % 16 == 0):
+            gemm_pair(x, w, out)
+            return True
+        if mode != "all":
+            return False
+    gemm_tc(x, w, out)
     return True
 
 
