@@ -107,6 +107,7 @@ def main(argv=None) -> int:
     ap.add_argument("--bn", type=int, default=0, help="gemm --pair: force the tile's weight rows")
     ap.add_argument("--swiglu", action="store_true", help="gemm --pair: SiLU(gate) * up in the epilogue")
     ap.add_argument("--pair", action="store_true", help="gemm: the kernel on pairs of SMs (many tokens)")
+    ap.add_argument("--no-tma", action="store_true", help="attention-decode: fetch keys and values with cp.async")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a graph")
     args = ap.parse_args(argv)
 
@@ -120,6 +121,8 @@ def main(argv=None) -> int:
     rt = Runtime(dev, torch.bfloat16, err=core.new_error_word(dev),
                  options={"sm_count": torch.cuda.get_device_properties(0).multi_processor_count})
     nh, nkv, hd = args.heads, args.kv_heads, args.head_dim
+    if args.no_tma:
+        rt.options["split_copy"] = "cp.async"
     out = {"kernel": args.kernel}
 
     if args.kernel in ("attention-decode", "attention-prefill"):

@@ -14,9 +14,11 @@
 //     Up to 8 slices of one request are the CTAs of one thread-block cluster
 //     and are merged through distributed shared memory; more slices are merged
 //     by a second small kernel through scratch memory.
-// Keys and values are fetched page by page through the request's block table
-// with 16-byte cp.async copies into padded shared-memory rows, two tiles in
-// flight.  Scores, the running maximum, the running sum and the output
+// Keys and values are fetched page by page through the request's block table:
+// in split mode by TMA, one bulk copy per page into swizzled shared memory,
+// issued by a fifth warp (head sizes that are multiples of 64, pages of a power
+// of two of at least 8 tokens); otherwise with 16-byte cp.async copies into
+// padded shared-memory rows.  Two tiles are in flight while a third is used.  Scores, the running maximum, the running sum and the output
 // accumulator are 32-bit; exponentials are 2^x (ex2.approx, 32-bit) of scores
 // pre-multiplied by log2(e).  Key tiles start at absolute multiples of 64, so the order of the
 // additions for a query does not depend on how its prompt was cut.
@@ -27,6 +29,8 @@
 // no tensor-core attention (its bf16 prefill loops cuBLAS per head over a
 // materialised score matrix: infernum-cuda/src/inner/cuda/ops/fused_attention.rs:265-473).
 #include "common.cuh"
+
+#include <cuda.h>
 
 #ifndef IB_HD
 #define IB_HD 128
@@ -386,6 +390,108 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
     }
 }
 
+// The end of split mode: the 4 warps of a CTA, each of which saw different keys,
+// are merged through shared memory (every thread of the block takes part, also
+// those of a warp that computed nothing), and then the slices of the request:
+// within a cluster through distributed shared memory, else through scratch.
+__device__ __forceinline__ void split_merge(const Params& p, unsigned char* smem_raw, const float (&o)[HD / 16][4],
+                                            const float (&m_run)[2], const float (&l_run)[2], int g, int hsub,
+                                            int row0, int rows_e) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int G = p.nh / p.nkv;
+    const int gs = p.gs_split;
+    // ---- merge the 4 warps (each saw different keys) -----------------------------
+    __syncthreads();
+    float* so = reinterpret_cast<float*>(smem_raw);   // [4][8][HD]
+    float* sml = so + 4 * 8 * HD;                     // [4][8][2]
+    float* fin = sml + 4 * 8 * 2;                     // [8][HD]   this CTA's result (cluster merge)
+    float* finml = fin + 8 * HD;                      // [8][2]
+    if (warp < 4) {
+#pragma unroll
+        for (int mt = 0; mt < HD / 16; ++mt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int n = tig * 2 + (i & 1);
+                const int d = mt * 16 + gid + 8 * (i >> 1);
+                so[((size_t)warp * 8 + n) * HD + d] = o[mt][i];
+            }
+        }
+    }
+    if (warp < 4 && gid == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            sml[(warp * 8 + tig * 2 + h) * 2] = m_run[h];
+            sml[(warp * 8 + tig * 2 + h) * 2 + 1] = l_run[h];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 8 * HD; idx += (int)blockDim.x) {
+        const int n = idx / HD, d = idx % HD;
+        const int r = n / gs, hh = hsub * gs + n % gs;
+        if (r >= rows_e || hh >= G) continue;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, sml[(w * 8 + n) * 2]);
+        float acc = 0.f, l = 0.f;
+        if (mx > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = fast_exp2(sml[(w * 8 + n) * 2] - mx);
+                acc += f * so[((size_t)w * 8 + n) * HD + d];
+                l += f * sml[(w * 8 + n) * 2 + 1];
+            }
+        }
+        const int grow = row0 + r, head = g * G + hh;
+        if (p.splits == 1) {
+            p.out[(size_t)grow * p.out_stride + (size_t)head * HD + d] =
+                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else if (p.cluster_merge) {
+            fin[n * HD + d] = acc;
+            if (d == 0) {
+                finml[n * 2] = mx;
+                finml[n * 2 + 1] = l;
+            }
+        } else {
+            const size_t base = ((size_t)blockIdx.x * p.n_rows + grow) * p.nh + head;
+            p.part_o[base * HD + d] = acc;
+            if (d == 0) {
+                p.part_ml[base * 2] = mx;
+                p.part_ml[base * 2 + 1] = l;
+            }
+        }
+    }
+    if (p.splits > 1 && p.cluster_merge) {
+        // The slices of this request are the CTAs of my cluster.  Each has its
+        // result in its own shared memory; after a cluster barrier each CTA merges
+        // a share of the (column, dim) elements over all slices, in slice order,
+        // reading the peers' shared memory directly.
+        cluster_sync_all();
+        const int total = 8 * HD;
+        const int share = (total + p.splits - 1) / p.splits;
+        const int begin = (int)blockIdx.x * share, end = min(total, begin + share);
+        for (int idx = begin + threadIdx.x; idx < end; idx += (int)blockDim.x) {
+            const int n = idx / HD, d = idx % HD;
+            const int r = n / gs, hh = hsub * gs + n % gs;
+            if (r >= rows_e || hh >= G) continue;
+            float mx = -INFINITY;
+            for (int sidx = 0; sidx < p.splits; ++sidx)
+                mx = fmaxf(mx, ld_peer_smem(finml + n * 2, (unsigned)sidx));
+            float acc = 0.f, l = 0.f;
+            if (mx > -INFINITY) {
+                for (int sidx = 0; sidx < p.splits; ++sidx) {
+                    const float f = fast_exp2(ld_peer_smem(finml + n * 2, (unsigned)sidx) - mx);
+                    acc += f * ld_peer_smem(fin + n * HD + d, (unsigned)sidx);
+                    l += f * ld_peer_smem(finml + n * 2 + 1, (unsigned)sidx);
+                }
+            }
+            p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(g * G + hh) * HD + d] =
+                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        }
+        cluster_sync_all();  // nobody leaves while a peer may still read its result
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Split mode.  Packed query columns n in [0, 8): n = r * gs + hh (query row r of
 // the entry, head hh of the kv head's group, gs = min(group, 8)).
@@ -550,94 +656,267 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
     }
 
-    // ---- merge the 4 warps (each saw different keys) -----------------------------
+    split_merge(p, smem_raw, o, m_run, l_run, g, hsub, row0, rows_e);
+}
+
+#if IB_HD % 64 == 0
+// ---------------------------------------------------------------------------
+// Split mode with keys and values fetched by TMA: the same mathematics, but a
+// fifth warp brings whole pages into 128-byte-swizzled shared memory with one
+// bulk copy each, so that the four computing warps spend no instructions on
+// addresses and copies and need no block-wide barrier per tile (each stage has
+// a "full" and an "empty" mbarrier; every wait is bounded).  For head sizes
+// that are multiples of 64 and pages of 8, 16, 32, 64, 128, ... tokens.
+//
+// A stage holds a K tile and a V tile, each as HD / 64 blocks of 64 rows x
+// 128 bytes: element (row, dim) of a tile lies at block dim / 64, row `row`,
+// 16-byte chunk ((dim % 64) / 8) ^ (row % 8).
+//
+// Whole pages are copied, so rows outside the request's keys hold whatever the
+// page held: their scores are masked, and the warp that owns them clears their
+// V rows in shared memory first (0 x anything must be 0).  Pages outside the
+// key range are not looked up (a window may have given them back); page 0 is
+// fetched in their place.
+// ---------------------------------------------------------------------------
+constexpr int TMA_KB = HD / 64;
+constexpr int TMA_BLOCK_BYTES = BN * 128;                   // 64 rows x 128 bytes
+constexpr int TMA_TILE_BYTES = TMA_KB * TMA_BLOCK_BYTES;
+constexpr int TMA_STAGE_BYTES = 2 * TMA_TILE_BYTES;         // K and V
+constexpr int TMA_STAGES = 3;
+constexpr int TMA_SMEM_BYTES = TMA_STAGES * TMA_STAGE_BYTES + 1024;
+constexpr int TMA_THREADS = 160;
+constexpr unsigned WAIT_LIMIT = 1u << 20;
+static_assert(4 * 8 * HD * 4 + 4 * 8 * 2 * 4 + 8 * HD * 4 + 8 * 2 * 4 <= TMA_STAGES * TMA_STAGE_BYTES,
+              "the merge buffers reuse the stages");
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// Element (row, dim) of a swizzled tile; dim a multiple of 8.
+__device__ __forceinline__ const bf16* swz(const bf16* tile, int row, int dim) {
+    return tile + (dim >> 6) * (TMA_BLOCK_BYTES / 2) + row * 64 + ((((dim & 63) >> 3) ^ (row & 7)) << 3);
+}
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_k,
+                           const __grid_constant__ CUtensorMap map_v) {
+    extern __shared__ __align__(16) unsigned char smem_dyn[];
+    __shared__ __align__(8) unsigned long long full_bar[TMA_STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[TMA_STAGES];
+    pdl_trigger();
+    unsigned char* smem_raw = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    auto k_stage = [&](int st) { return reinterpret_cast<bf16*>(smem_raw + (size_t)st * TMA_STAGE_BYTES); };
+    auto v_stage = [&](int st) {
+        return reinterpret_cast<bf16*>(smem_raw + (size_t)st * TMA_STAGE_BYTES + TMA_TILE_BYTES);
+    };
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int st = 0; st < TMA_STAGES; ++st) {
+            mbar_init(&full_bar[st], 1);
+            mbar_init(&empty_bar[st], 4);   // the four computing warps
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
     __syncthreads();
-    float* so = reinterpret_cast<float*>(smem_raw);   // [4][8][HD]
-    float* sml = so + 4 * 8 * HD;                     // [4][8][2]
-    float* fin = sml + 4 * 8 * 2;                     // [8][HD]   this CTA's result (cluster merge)
-    float* finml = fin + 8 * HD;                      // [8][2]
+    pdl_wait();  // queries, keys, values and tables come from the kernels before this one
+
+    const int e = blockIdx.y;
+    const int g = blockIdx.z / p.n_hsub_split;
+    const int hsub = blockIdx.z % p.n_hsub_split;
+    const int G = p.nh / p.nkv;
+    const int gs = p.gs_split;
+    const int row0 = p.cu_rows[e];
+    const int rows_e = p.cu_rows[e + 1] - row0;
+    const int pos0 = p.q_start[e];
+    if (rows_e * gs > p.small_rows) return;  // tile mode takes this entry (the whole block leaves)
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+
+    const int kv_hi = pos0 + rows_e;
+    const int kv_min = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int kv_lo = (kv_min / BN) * BN;
+    const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
+    const int per = (n_tiles + p.splits - 1) / p.splits;
+    const int t_begin = blockIdx.x * per;
+    const int t_end = min(n_tiles, t_begin + per);
+
+    float o[HD / 16][4];  // O^T: rows = head dims, my columns tig*2, tig*2 + 1
 #pragma unroll
-    for (int mt = 0; mt < HD / 16; ++mt) {
+    for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    if (warp == 4) {
+        // ---- producer ---------------------------------------------------------------
+        // Lane i fetches the i-th page of a tile (one lane when a page holds the
+        // whole tile).  The block-table entry of the next tile is read while this
+        // tile's copies are issued, so no copy waits for a dependent load.
+        const int* table = p.block_tables + (size_t)e * p.max_blocks;
+        const int box_rows = p.page_size < BN ? p.page_size : BN;
+        const int ppt = BN / box_rows;
+        const int first_page = kv_min >> p.page_shift, last_page = (kv_hi - 1) >> p.page_shift;
+        auto lookup = [&](int t) -> int {
+            const int pi = (kv_lo + t * BN + lane * box_rows) >> p.page_shift;
+            return (lane < ppt && t < t_end && pi >= first_page && pi <= last_page && pi < p.max_blocks)
+                       ? table[pi] : 0;
+        };
+        int page_next = lookup(t_begin);
+        bool ok = true;
+        for (int t = t_begin; t < t_end; ++t) {
+            const int i = t - t_begin, st = i % TMA_STAGES;
+            int page = page_next;
+            page_next = lookup(t + 1);
+            if (i >= TMA_STAGES && !mbar_wait(&empty_bar[st], ((i / TMA_STAGES) - 1) & 1)) { ok = false; break; }
+            if (lane == 0) mbar_expect_tx(&full_bar[st], TMA_STAGE_BYTES);
+            __syncwarp();
+            if (lane < ppt) {
+                if (page < 0 || page >= p.num_pages) {
+                    atomicOr(p.err, IB_FLAG_BAD_PAGE);
+                    page = 0;
+                }
+                const int key0 = kv_lo + t * BN + lane * box_rows;
+                const int y = (page * p.nkv + g) * p.page_size + (key0 & (p.page_size - 1));
+                unsigned char* kd = reinterpret_cast<unsigned char*>(k_stage(st)) + lane * box_rows * 128;
+                unsigned char* vd = reinterpret_cast<unsigned char*>(v_stage(st)) + lane * box_rows * 128;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int n = tig * 2 + (i & 1);
-            const int d = mt * 16 + gid + 8 * (i >> 1);
-            so[((size_t)warp * 8 + n) * HD + d] = o[mt][i];
-        }
-    }
-    if (gid == 0) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            sml[(warp * 8 + tig * 2 + h) * 2] = m_run[h];
-            sml[(warp * 8 + tig * 2 + h) * 2 + 1] = l_run[h];
-        }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < 8 * HD; idx += NTHREADS) {
-        const int n = idx / HD, d = idx % HD;
-        const int r = n / gs, hh = hsub * gs + n % gs;
-        if (r >= rows_e || hh >= G) continue;
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, sml[(w * 8 + n) * 2]);
-        float acc = 0.f, l = 0.f;
-        if (mx > -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float f = fast_exp2(sml[(w * 8 + n) * 2] - mx);
-                acc += f * so[((size_t)w * 8 + n) * HD + d];
-                l += f * sml[(w * 8 + n) * 2 + 1];
-            }
-        }
-        const int grow = row0 + r, head = g * G + hh;
-        if (p.splits == 1) {
-            p.out[(size_t)grow * p.out_stride + (size_t)head * HD + d] =
-                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-        } else if (p.cluster_merge) {
-            fin[n * HD + d] = acc;
-            if (d == 0) {
-                finml[n * 2] = mx;
-                finml[n * 2 + 1] = l;
-            }
-        } else {
-            const size_t base = ((size_t)blockIdx.x * p.n_rows + grow) * p.nh + head;
-            p.part_o[base * HD + d] = acc;
-            if (d == 0) {
-                p.part_ml[base * 2] = mx;
-                p.part_ml[base * 2 + 1] = l;
-            }
-        }
-    }
-    if (p.splits > 1 && p.cluster_merge) {
-        // The slices of this request are the CTAs of my cluster.  Each has its
-        // result in its own shared memory; after a cluster barrier each CTA merges
-        // a share of the (column, dim) elements over all slices, in slice order,
-        // reading the peers' shared memory directly.
-        cluster_sync_all();
-        const int total = 8 * HD;
-        const int share = (total + p.splits - 1) / p.splits;
-        const int begin = (int)blockIdx.x * share, end = min(total, begin + share);
-        for (int idx = begin + threadIdx.x; idx < end; idx += NTHREADS) {
-            const int n = idx / HD, d = idx % HD;
-            const int r = n / gs, hh = hsub * gs + n % gs;
-            if (r >= rows_e || hh >= G) continue;
-            float mx = -INFINITY;
-            for (int sidx = 0; sidx < p.splits; ++sidx)
-                mx = fmaxf(mx, ld_peer_smem(finml + n * 2, (unsigned)sidx));
-            float acc = 0.f, l = 0.f;
-            if (mx > -INFINITY) {
-                for (int sidx = 0; sidx < p.splits; ++sidx) {
-                    const float f = fast_exp2(ld_peer_smem(finml + n * 2, (unsigned)sidx) - mx);
-                    acc += f * ld_peer_smem(fin + n * HD + d, (unsigned)sidx);
-                    l += f * ld_peer_smem(finml + n * 2 + 1, (unsigned)sidx);
+                for (int kb = 0; kb < TMA_KB; ++kb) {
+                    tma_load_2d(kd + kb * TMA_BLOCK_BYTES, &map_k, &full_bar[st], kb * 64, y);
+                    tma_load_2d(vd + kb * TMA_BLOCK_BYTES, &map_v, &full_bar[st], kb * 64, y);
                 }
             }
-            p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(g * G + hh) * HD + d] =
-                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         }
-        cluster_sync_all();  // nobody leaves while a peer may still read its result
+        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+    } else {
+        // ---- the four computing warps -----------------------------------------------------
+        unsigned qf[HD / 16][2];
+        {
+            const int r = gid / gs, hh = hsub * gs + gid % gs;
+            const bool okq = r < rows_e && hh < G;
+            const bf16* qp =
+                p.q + (size_t)(row0 + (okq ? r : 0)) * p.q_stride + (size_t)(g * G + (okq ? hh : 0)) * HD;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                qf[ks][0] = okq ? *reinterpret_cast<const unsigned*>(qp + ks * 16 + tig * 2) : 0u;
+                qf[ks][1] = okq ? *reinterpret_cast<const unsigned*>(qp + ks * 16 + 8 + tig * 2) : 0u;
+            }
+        }
+        int col_pos[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int n = tig * 2 + h;
+            const int r = n / gs, hh = hsub * gs + n % gs;
+            col_pos[h] = (r < rows_e && hh < G) ? pos0 + r : -1;
+        }
+        const int key_base = warp * 16;
+        bool ok = true;
+        for (int t = t_begin; t < t_end; ++t) {
+            const int i = t - t_begin, st = i % TMA_STAGES;
+            if (!mbar_wait(&full_bar[st], (i / TMA_STAGES) & 1)) { ok = false; break; }
+            const int tile_start = kv_lo + t * BN;
+            const bf16* ks_ = k_stage(st);
+            bf16* vs_ = v_stage(st);
+            if (tile_start < kv_min || tile_start + BN > kv_hi) {
+                // clear the V rows of my keys that are not the request's
+                for (int c = lane; c < 16 * CH; c += 32) {
+                    const int row = key_base + c / CH, key = tile_start + row;
+                    if (key < kv_min || key >= kv_hi)
+                        *reinterpret_cast<uint4*>(const_cast<bf16*>(swz(vs_, row, (c % CH) * 8))) =
+                            make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+            }
+
+            // S^T for my 16 keys
+            float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                unsigned a[4];
+                const int key = key_base + (lane & 7) + 8 * ((lane >> 3) & 1);
+                const int dim = ks * 16 + 8 * (lane >> 4);
+                ldmatrix_x4(a[0], a[1], a[2], a[3], swz(ks_, key, dim));
+                mma_bf16(sc, a, qf[ks][0], qf[ks][1]);
+            }
+            float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int h = q & 1;
+                const int key = tile_start + key_base + gid + 8 * (q >> 1);
+                const bool in = key <= col_pos[h] && (p.window <= 0 || key > col_pos[h] - p.window);
+                sc[q] = in ? sc[q] * p.scale_log2 : -INFINITY;
+                m_new[h] = fmaxf(m_new[h], sc[q]);
+            }
+            float corr[2], m_use[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 4));
+                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 8));
+                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 16));
+                m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];
+                corr[h] = fast_exp2(m_run[h] - m_use[h]);
+                m_run[h] = m_new[h];
+                l_run[h] *= corr[h];
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                sc[q] = fast_exp2(sc[q] - m_use[q & 1]);
+                l_run[q & 1] += sc[q];
+            }
+#pragma unroll
+            for (int q = 0; q < HD / 16; ++q) {
+                o[q][0] *= corr[0];
+                o[q][1] *= corr[1];
+                o[q][2] *= corr[0];
+                o[q][3] *= corr[1];
+            }
+            const unsigned b0 = movmatrix_trans(pack_bf16(sc[0], sc[1]));
+            const unsigned b1 = movmatrix_trans(pack_bf16(sc[2], sc[3]));
+#pragma unroll
+            for (int mt = 0; mt < HD / 16; ++mt) {
+                unsigned a[4];
+                const int mi = lane >> 3;
+                const int key = key_base + (lane & 7) + 8 * (mi >> 1);
+                const int dim = mt * 16 + 8 * (mi & 1);
+                ldmatrix_x4_trans(a[0], a[1], a[2], a[3], swz(vs_, key, dim));
+                mma_bf16(o[mt], a, b0, b1);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[st]);   // my warp is done with this stage
+        }
+        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
+        }
     }
+    split_merge(p, smem_raw, o, m_run, l_run, g, hsub, row0, rows_e);
 }
+#endif  // IB_HD % 64 == 0
 
 // Merges the slices of split mode: one block per (row, head).
 __global__ void attention_combine_kernel(const Params p) {
@@ -662,6 +941,39 @@ __global__ void attention_combine_kernel(const Params p) {
     }
 }
 
+#if IB_HD % 64 == 0
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// A pool [pages][kv heads][page_size][HD] as rows of HD values; a box is 64 values
+// of up to 64 consecutive rows (one page, or the tile's part of a larger page).
+bool make_pool_map(CUtensorMap* map, const void* pool, long long rows, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+#endif
+
 }  // namespace
 
 IB_EXPORT int ib_attention_mma_head_dim() { return HD; }
@@ -677,7 +989,9 @@ IB_EXPORT long long ib_attention_mma_scratch_bytes(int n_rows, int nh, int split
 // to tile mode; with one bit every entry is taken by that mode, except that
 // split mode can never take an entry with more than 8 packed rows.  Bit 4 with
 // bit 2: the tile-mode entries were computed by another kernel; only the small
-// entries are taken here.
+// entries are taken here.  Bit 8: split mode fetches keys and values with cp.async
+// also where it could use TMA (head size a multiple of 64, pages of a power of
+// two of at least 8 tokens).
 IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                void* out, int out_stride, const int* cu_rows, const int* q_start,
                                const int* block_tables, int max_blocks, int n_entries, int n_rows,
@@ -727,6 +1041,9 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     p.part_ml = nullptr;
     p.cluster_merge = 0;
     // which entries each mode takes
+    const bool no_tma = (mode & 8) != 0;
+    (void)no_tma;
+    mode &= 7;
     const bool tiles_done_elsewhere = (mode & 4) != 0;  // another kernel took the tile-mode entries
     if (tiles_done_elsewhere) mode = 2;
     if ((mode & 3) == 3 || tiles_done_elsewhere) p.small_rows = 8;
@@ -765,7 +1082,52 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
         }
         dim3 grid(splits, n_entries, nkv * p.n_hsub_split);
         p.cluster_merge = (splits > 1 && splits <= 8) ? 1 : 0;
-        if (p.cluster_merge) {
+        bool use_tma = false;
+#if IB_HD % 64 == 0
+        CUtensorMap map_k, map_v;
+        const long long pool_rows = (long long)num_pages * nkv * page_size;
+        if (!no_tma && p.page_shift >= 3 && pool_rows < 0x7fffffffLL) {
+            const int box_rows = page_size < BN ? page_size : BN;
+            use_tma = make_pool_map(&map_k, k_pool, pool_rows, box_rows) &&
+                      make_pool_map(&map_v, v_pool, pool_rows, box_rows);
+        }
+        if (use_tma) {
+            static bool tma_attr_done = false;
+            if (!tma_attr_done) {
+                cudaError_t e3 = cudaFuncSetAttribute(attention_split_tma_kernel,
+                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, TMA_SMEM_BYTES);
+                if (e3 != cudaSuccess) return (int)e3;
+                tma_attr_done = true;
+            }
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(TMA_THREADS);
+            cfg.dynamicSmemBytes = TMA_SMEM_BYTES;
+            cfg.stream = s;
+            cudaLaunchAttribute attr[2];
+            int n_attr = 0;
+            if (p.cluster_merge) {
+                attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+                attr[n_attr].val.clusterDim.x = splits;
+                attr[n_attr].val.clusterDim.y = 1;
+                attr[n_attr].val.clusterDim.z = 1;
+                ++n_attr;
+            }
+            if (pdl_flag()) {
+                attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+                ++n_attr;
+            }
+            cfg.attrs = attr;
+            cfg.numAttrs = n_attr;
+            cudaError_t le = cudaLaunchKernelEx(&cfg, attention_split_tma_kernel, p, map_k, map_v);
+            if (le != cudaSuccess) return (int)le;
+            IB_LAUNCH_CHECK();
+        }
+#endif
+        if (use_tma) {
+            // launched above
+        } else if (p.cluster_merge) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = grid;
             cfg.blockDim = dim3(NTHREADS);
@@ -783,14 +1145,15 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
             cudaError_t le = cudaLaunchKernelEx(&cfg, attention_split_kernel, p);
             if (le != cudaSuccess) return (int)le;
             IB_LAUNCH_CHECK();
-            return IB_OK;
+        } else {
+            cudaError_t le =
+                launch_kernel(attention_split_kernel, grid, dim3(NTHREADS), SPLIT_SMEM_BYTES, s, p);
+            if (le != cudaSuccess) return (int)le;
+            IB_LAUNCH_CHECK();
         }
-        cudaError_t le = launch_kernel(attention_split_kernel, grid, dim3(NTHREADS), SPLIT_SMEM_BYTES, s, p);
-        if (le != cudaSuccess) return (int)le;
-        IB_LAUNCH_CHECK();
-        if (splits > 1) {
+        if (splits > 1 && !p.cluster_merge) {
             dim3 cgrid(n_rows, nh);
-            le = launch_kernel(attention_combine_kernel, cgrid, dim3(HD >= 128 ? 128 : 64), 0, s, p);
+            cudaError_t le = launch_kernel(attention_combine_kernel, cgrid, dim3(HD >= 128 ? 128 : 64), 0, s, p);
             if (le != cudaSuccess) return (int)le;
             IB_LAUNCH_CHECK();
         }

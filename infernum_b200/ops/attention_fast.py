@@ -131,6 +131,8 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
         if not (mode & 2):
             return True
         mode = 2 | 4  # split mode for the small entries only; the others are done
+    if rt.options.get("split_copy", "tma") != "tma":
+        mode |= 8  # keys and values by cp.async also where TMA could fetch them
     lib = lib_for(hd)
     scratch_ptr, scratch_bytes = None, 0
     if splits > 8:

@@ -377,6 +377,57 @@ def test_attention_mma_edges_of_tiles_and_pages():
             assert rel_err(out, plain_result(refs)) < 1e-2, (L, n)
 
 
+@pytest.mark.parametrize("hd, ps, window", [
+    (64, 8, 0), (128, 8, 0), (128, 16, 0), (128, 32, 0), (64, 64, 0), (128, 128, 0), (128, 256, 0),
+    (128, 16, 40), (64, 32, 100), (128, 8, 64), (64, 128, 130),
+])
+@pytest.mark.parametrize("splits", [1, 3, 12])
+def test_attention_split_by_tma_and_by_cp_async(hd, ps, window, splits):
+    """Split mode fetches whole pages by TMA where it can.  What a page holds
+    beyond the request's last key, and pages that a window has given back, must
+    not reach the result: they are poisoned here with NaN.  Both ways of
+    fetching give the plain result."""
+    from infernum_b200.ops import attention_fast
+    from infernum_b200.parts.base import Runtime
+    c = core()
+    nh, nkv = 8, 2
+    lens = [1, 63, 64, 65, 200, 517]
+    q, kp, vp, tables, ctx, refs = paged_case(lens, [1] * len(lens), nh, nkv, hd, ps, torch.bfloat16,
+                                              hd + ps + window, scale_key=0 if window == 0 else -1)
+    tables_h = tables.cpu()
+    used = set()
+    for e, L in enumerate(lens):
+        n_pages = -(-L // ps)
+        kv_min = max(0, L - window) if window else 0
+        for i in range(n_pages):
+            page = int(tables_h[e, i])
+            used.add(page)
+            hi = min(L, (i + 1) * ps) - i * ps
+            kp[page, :, hi:] = float("nan")
+            vp[page, :, hi:] = float("nan")
+            if (i + 1) * ps <= kv_min:  # the window has passed this page: given back
+                kp[page] = float("nan")
+                vp[page] = float("nan")
+                tables_h[e, i] = -1
+    for page in range(kp.shape[0]):
+        if page not in used:
+            kp[page] = float("nan")
+            vp[page] = float("nan")
+    tables = tables_h.to(DEV)
+    want = plain_result(refs, window)
+    outs = []
+    for copy in ("tma", "cp.async"):
+        ctx.attention_mode = (2, splits)
+        rt = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV), options={"split_copy": copy})
+        out = torch.full((len(lens), nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        assert attention_fast.run(q, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), window, rt)
+        assert rt.err.item() == 0, copy
+        assert torch.isfinite(out).all(), copy
+        assert rel_err(out, want) < 1e-2, copy
+        outs.append(out)
+    assert rel_err(outs[0], outs[1].double()) < 4e-3
+
+
 # --------------------------------------------------------------------------
 # the tcgen05 matrix product
 # --------------------------------------------------------------------------
