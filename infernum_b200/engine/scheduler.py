@@ -70,6 +70,11 @@ class BatchConfig:
     max_tokens_per_step: int = 2048
     max_model_len: Optional[int] = None  # default: the model's max_position_embeddings
     cuda_graphs: bool = True  # replay a recorded graph while the same requests decode
+    # The kernels for prompts work on tiles of so many rows.  A step with prompt
+    # portions whose row count lies a little above a multiple of it (by at most
+    # 1/16) is cut back to that multiple; the rows cut come with the next step.
+    # 0: leave steps as they are.
+    token_multiple: int = 256
 
 
 @dataclass
@@ -182,7 +187,23 @@ class Scheduler:
                 self._reap()
                 break
             self._preempt(victim, plan)
+        self._trim_to_multiple(plan)
         return plan
+
+    def _trim_to_multiple(self, plan: StepPlan) -> None:
+        m = self.config.token_multiple
+        total = plan.num_tokens
+        if m <= 0 or total <= m:
+            return
+        extra = total % m
+        if extra == 0 or extra * 16 > total:
+            return
+        # the last prompt portion that stays a portion of at least two tokens
+        for p in reversed(plan.portions):
+            if p.count >= extra + 2:
+                p.count -= extra           # its pages stay reserved for the next step
+                p.wants_logits = False     # it no longer reaches the request's last token
+                return
 
     def _fill(self, plan: StepPlan) -> None:
         cfg = self.config

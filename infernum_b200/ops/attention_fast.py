@@ -134,6 +134,12 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
         if not (mode & 2):
             return True
         mode = 2 | 4  # split mode for the small entries only; the others are done
+        if forced is None:
+            # they are sliced as in a step of decoded tokens alone: a single CTA per
+            # request and kv head would walk a long context tile by tile
+            n_small = sum(1 for r in rows if r <= small_limit)
+            sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
+            splits = min(8, choose_splits(n_small, nkv * n_hsub, ctx.max_kv_len, sm))
     if rt.options.get("split_copy", "tma") != "tma":
         mode |= 8  # keys and values by cp.async also where TMA could fetch them
     lib = lib_for(hd)

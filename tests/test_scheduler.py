@@ -48,7 +48,7 @@ def drain(sched, cache, limit=10000):
 
 
 def solo_tokens(prompt, n_new):
-    sched, cache = make(num_blocks=256)
+    sched, cache = make(num_blocks=max(256, (len(prompt) + n_new) // 4 + 2), max_len=max(256, len(prompt) + n_new))
     s = sched.add_request(prompt, GenerateOptions(max_new_tokens=n_new))
     drain(sched, cache)
     return s.generated_ids
@@ -231,3 +231,46 @@ def test_a_preempted_request_waits_until_its_whole_recomputation_fits():
     drain(sched, cache)
     assert len(a.generated_ids) == 40 and len(b.generated_ids) == 40
     assert b.preemptions <= 2
+
+
+def test_steps_a_little_above_a_multiple_of_the_tile_are_cut_back():
+    """520 rows (a portion of 512 beside 8 decoded tokens) become 512; the 8 rows
+    cut come with the next step, and every prompt is still covered exactly once."""
+    cfg = BatchConfig(max_batch_size=16, max_prefill_tokens=512, block_size=16, num_blocks=1024,
+                      max_tokens_per_step=2048, token_multiple=256)
+    need = SimpleNamespace(position=0, paged=PagedCacheSpec(1, 8, 0), state=None, cache_of=None)
+    cache = CacheManager([need], page_size=16, num_pages=1024, max_requests=16)
+    sched = Scheduler(cfg, cache, 4096)
+    opts = GenerateOptions(max_new_tokens=40, ignore_eos=True)
+    short = [sched.add_request([5 + i] * 3, opts) for i in range(8)]
+    run_step(sched, cache)  # the eight short prompts: 24 rows, left alone
+    assert all(s.phase == Phase.DECODE for s in short)
+    long = sched.add_request(list(range(3, 1403)), opts)
+    plan = run_step(sched, cache)
+    assert plan.num_tokens == 512  # 8 decoded tokens + 504 of the prompt, not 520
+    assert sum(p.count for p in plan.portions if p.seq is long) == 504
+    plan = run_step(sched, cache)
+    assert plan.num_tokens == 512 and long.num_computed == 1008
+    plan = run_step(sched, cache)  # 392 left + 8 = 400: far from a multiple, left alone
+    assert plan.num_tokens == 400 and long.phase == Phase.DECODE
+    drain(sched, cache)
+    assert long.generated_ids == solo_tokens(list(range(3, 1403)), 40)
+    cache.check_invariants()
+
+
+def test_a_cut_portion_that_would_have_ended_its_prompt_asks_for_no_logits():
+    cfg = BatchConfig(max_batch_size=4, max_prefill_tokens=600, block_size=16, num_blocks=256,
+                      max_tokens_per_step=2048, token_multiple=256)
+    need = SimpleNamespace(position=0, paged=PagedCacheSpec(1, 8, 0), state=None, cache_of=None)
+    cache = CacheManager([need], page_size=16, num_pages=256, max_requests=4)
+    sched = Scheduler(cfg, cache, 4096)
+    seq = sched.add_request(list(range(3, 523)), GenerateOptions(max_new_tokens=2, ignore_eos=True))  # 520 tokens
+    plan = run_step(sched, cache)
+    assert plan.num_tokens == 512 and not plan.portions[0].wants_logits and not seq.generated_ids
+    plan = run_step(sched, cache)
+    assert plan.num_tokens == 8 and plan.portions[0].wants_logits and len(seq.generated_ids) == 1
+    off = Scheduler(BatchConfig(max_batch_size=4, max_prefill_tokens=600, block_size=16, num_blocks=256,
+                                token_multiple=0),
+                    CacheManager([need], page_size=16, num_pages=256, max_requests=4), 4096)
+    off.add_request(list(range(3, 523)), GenerateOptions(max_new_tokens=2, ignore_eos=True))
+    assert off.schedule().num_tokens == 520
