@@ -59,9 +59,9 @@ def build_dir() -> str:
     for cand in candidates:
         try:
             os.makedirs(cand, exist_ok=True)
-            probe = os.path.join(cand, f".probe_{os.getpid()}")
-            with open(probe, "w"):
-                pass
+            # a name of its own for every caller: modules are built from several threads
+            fd, probe = tempfile.mkstemp(prefix=".probe_", dir=cand)
+            os.close(fd)
             os.remove(probe)
             return cand
         except OSError:
