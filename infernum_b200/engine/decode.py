@@ -33,6 +33,7 @@ import torch
 
 from ..cache.manager import RequestCache
 from ..ops import core
+from ..errors import CacheError
 from ..ops.attention_fast import SM_COUNT_FALLBACK, choose_splits
 from .step import ModelRunner, StepContext
 
@@ -58,6 +59,11 @@ class _Slot:
     selected: torch.Tensor  # device [size] int32
     ctx: StepContext
     rows: List[Optional[Tuple[object, List[int]]]] = field(default_factory=list)  # who sits where
+    host_np: object = None  # host_ints' memory as a numpy array (cheap to fill from lists)
+    uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
+    prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
+    result: Optional[torch.Tensor] = None  # device [size + 1]: the selected tokens, then the error word
+    host_result: Optional[torch.Tensor] = None  # pinned mirror
     sampled: Optional[torch.Tensor] = None
     params: Optional[torch.Tensor] = None
     host_params: Optional[torch.Tensor] = None
@@ -110,6 +116,9 @@ class DecodeRunner:
                      host_tables=torch.full((G, size, self.MB), -1, dtype=torch.int32).pin_memory(),
                      selected=torch.zeros(size, dtype=torch.int32, device=dev), ctx=ctx,
                      rows=[None] * size)
+        slot.host_np = slot.host_ints.numpy()
+        slot.result = torch.zeros(size + 1, dtype=torch.int32, device=dev)
+        slot.host_result = torch.zeros(size + 1, dtype=torch.int32).pin_memory()
         if sampling:
             f = core.SAMPLE_PARAM_FLOATS
             slot.sampled = torch.zeros(size, dtype=torch.int32, device=dev)
@@ -162,6 +171,9 @@ class DecodeRunner:
             slot.selected.copy_(torch.where(slot.mask, slot.sampled, slot.selected))
         if device_feed:
             core.decode_advance(slot.ctx.token_ids, slot.selected, slot.ctx.positions, slot.ctx.kv_len)
+        else:
+            # what the host reads after the step, in one piece
+            torch.cat((slot.selected, self.rt.err), out=slot.result)
 
     def _run(self, slot: _Slot, device_feed: bool) -> None:
         if slot.graph is not None:
@@ -196,22 +208,40 @@ class DecodeRunner:
         with the given input tokens.  ``sample``: (params, recent, mask) host
         tensors from ``pack_choices`` when some row samples.  Returns the
         selected token ids, int32 [len(caches)] on the device."""
+        return self.launch(self.prepare(caches, sample is not None), caches, tokens, sample)
+
+    def prepare(self, caches: Sequence[RequestCache], sampling: bool) -> _Slot:
+        """The part of a step that does not need the input tokens: picks the
+        buffers, fills positions, slots and block tables.  It may run while the
+        step before is still on the GPU (its uploads are waited for first)."""
         B = len(caches)
-        slot = self._slot(self._key(caches, sample is not None, "host"))
-        self.last = slot
+        slot = self._slot(self._key(caches, sampling, "host"))
+        if slot.uploaded is not None:
+            slot.uploaded.synchronize()  # the pinned mirrors are free to be written again
         pad = slot.size - B
-        hi = slot.host_ints
-        hi[0, :B] = torch.tensor(list(tokens), dtype=torch.int32)
-        hi[1, :B] = torch.tensor([rc.num_tokens for rc in caches], dtype=torch.int32)
-        hi[3, :B] = torch.tensor([rc.slot for rc in caches], dtype=torch.int32)
+        hn = slot.host_np
+        hn[1, :B] = [rc.num_tokens for rc in caches]
+        hn[3, :B] = [rc.slot for rc in caches]
         if pad:
-            hi[0, B:] = 0
-            hi[1, B:] = 0
-            hi[3, B:] = self.cache.pad_slot
-        hi[2] = hi[1] + 1
-        slot.ints.copy_(hi, non_blocking=True)
+            hn[0, B:] = 0
+            hn[1, B:] = 0
+            hn[3, B:] = self.cache.pad_slot
+        hn[2] = hn[1] + 1
         if self._fill_tables(slot, caches):
             slot.tables.copy_(slot.host_tables, non_blocking=True)
+        slot.prepared_for = tuple(rc.request_id for rc in caches)
+        return slot
+
+    def launch(self, slot: _Slot, caches: Sequence[RequestCache], tokens: Sequence[int],
+               sample: Optional[tuple] = None) -> torch.Tensor:
+        """Uploads the tokens (and sampling rows) and runs the prepared step."""
+        B = len(caches)
+        if slot.prepared_for != tuple(rc.request_id for rc in caches):
+            raise CacheError("decode step launched for other requests than it was prepared for")
+        slot.prepared_for = None
+        self.last = slot
+        slot.host_np[0, :B] = tokens
+        slot.ints.copy_(slot.host_ints, non_blocking=True)
         if sample is not None:
             params, recent, mask = sample
             slot.host_params.zero_()
@@ -224,12 +254,24 @@ class DecodeRunner:
             slot.params.copy_(slot.host_params, non_blocking=True)
             slot.recent.copy_(slot.host_recent, non_blocking=True)
             slot.mask.copy_(slot.host_mask, non_blocking=True)
+        if slot.uploaded is None:
+            slot.uploaded = torch.cuda.Event()
+        slot.uploaded.record()
         self._run(slot, device_feed=False)
         for rc in caches:
             self.cache.commit(rc, 1)
         self.runner.steps_run += 1
         self.runner.rows_run += B
         return slot.selected[:B]
+
+    def read_result(self, n: int) -> Tuple[List[int], int]:
+        """The tokens selected by the last host-fed step and the error word, read
+        through pinned memory (this waits for the step)."""
+        slot = self.last
+        slot.host_result.copy_(slot.result, non_blocking=True)
+        torch.cuda.current_stream(self.rt.device).synchronize()
+        host = slot.host_result.tolist()
+        return host[:n], host[slot.size]
 
     # ---- fed from the device ---------------------------------------------------------------
     def pin(self, caches: Sequence[RequestCache], tokens: Sequence[int], steps: int) -> None:

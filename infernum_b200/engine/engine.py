@@ -67,6 +67,8 @@ class EngineStats:
     preemptions: int = 0
     generated_tokens: int = 0
     step_seconds: float = 0.0
+    ahead_used: int = 0    # decode steps that ran from a plan made while the step before them ran
+    ahead_voided: int = 0  # such plans dropped because a request ended or arrived meanwhile
 
 
 class Engine:
@@ -86,6 +88,8 @@ class Engine:
         self.stats = EngineStats()
         self._handles: Dict[int, RequestHandle] = {}
         self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if cfg.cuda_graphs else None
+        # the next decode step, planned and prepared while the one before it ran
+        self._ahead: Optional[Tuple[StepPlan, object]] = None
         self.h2d_bytes = 0  # bytes of step inputs copied to the device so far
         self.d2h_bytes = 0  # bytes of step results read back so far
 
@@ -114,7 +118,19 @@ class Engine:
     def step(self) -> List[Tuple[RequestHandle, GenerationEvent]]:
         """One scheduling round and one model step; returns the new events."""
         t0 = time.perf_counter()
-        plan = self.scheduler.schedule()
+        prepared = None
+        if self._ahead is not None:
+            plan, prepared = self._ahead
+            self._ahead = None
+            if self.scheduler.ahead_still_holds(plan):
+                self.stats.ahead_used += 1
+            else:
+                self.stats.ahead_voided += 1
+                plan, prepared = None, None
+        else:
+            plan = None
+        if plan is None:
+            plan = self.scheduler.schedule()
         self.stats.preemptions = self.scheduler.num_preemptions
         events: List[Tuple[RequestHandle, GenerationEvent]] = []
         if plan.portions:
@@ -130,7 +146,10 @@ class Engine:
             if decode_only:
                 sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) \
                     if any(c is not None for c in choices) else None
-                chosen = self.decoder.step(caches, [p.tokens[0] for p in plan.portions], sample)
+                if prepared is None or prepared.prepared_for != tuple(rc.request_id for rc in caches):
+                    prepared = self.decoder.prepare(caches, sample is not None)
+                chosen = self.decoder.launch(prepared, caches,
+                                             [p.seq.token_at(p.start) for p in plan.portions], sample)
                 self.h2d_bytes += 16 * len(plan.portions)
                 logits = self.decoder.last.logits
             else:
@@ -140,12 +159,25 @@ class Engine:
                 self.h2d_bytes += self.runner.last_upload_bytes
                 chosen = self.sampler.select(logits, choices) if logits is not None and wanting else None
             self.scheduler.commit(plan)
+            if decode_only:
+                # While this step runs: plan the next one and fill in all of it but the
+                # tokens, so that little is left to do between the two steps.
+                ahead = self.scheduler.plan_decode_ahead()
+                if ahead is not None:
+                    nxt = [p.seq.cache for p in ahead.portions]
+                    samples = any(p.seq.options.sampling is not None for p in ahead.portions)
+                    self._ahead = (ahead, self.decoder.prepare(nxt, samples)
+                                   if self.decoder.can_take(nxt) else None)
             if chosen is not None:
-                host = torch.cat([chosen, self.runner.rt.err]).cpu().tolist()
-                self.d2h_bytes += 4 * len(host)
-                if host[-1]:
+                if decode_only:
+                    picked, flags = self.decoder.read_result(len(wanting))
+                else:
+                    host = torch.cat([chosen, self.runner.rt.err]).cpu().tolist()
+                    picked, flags = host[:-1], host[-1]
+                self.d2h_bytes += 4 * (len(picked) + 1)
+                if flags:
                     self.runner.check_errors()
-                for p, tok in zip(wanting, host[:-1]):
+                for p, tok in zip(wanting, picked):
                     handle = self._handles[p.seq.id]
                     emitted = self.scheduler.append_token(p.seq, tok)
                     if emitted is not None:

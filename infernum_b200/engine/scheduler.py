@@ -99,6 +99,18 @@ class Sequence_:
     def num_tokens(self) -> int:
         return len(self.prompt_ids) + len(self.generated_ids)
 
+    def token_at(self, i: int) -> int:
+        n = len(self.prompt_ids)
+        return self.prompt_ids[i] if i < n else self.generated_ids[i - n]
+
+    def token_range(self, start: int, stop: int) -> List[int]:
+        n = len(self.prompt_ids)
+        if stop <= n:
+            return self.prompt_ids[start:stop]
+        if start >= n:
+            return self.generated_ids[start - n: stop - n]
+        return self.prompt_ids[start:] + self.generated_ids[: stop - n]
+
     @property
     def remaining(self) -> int:
         return self.num_tokens - self.num_computed
@@ -117,7 +129,7 @@ class Portion:
 
     @property
     def tokens(self) -> List[int]:
-        return self.seq.tokens[self.start: self.start + self.count]
+        return self.seq.token_range(self.start, self.start + self.count)
 
 
 @dataclass
@@ -189,6 +201,50 @@ class Scheduler:
             self._preempt(victim, plan)
         self._trim_to_multiple(plan)
         return plan
+
+    def plan_decode_ahead(self) -> Optional[StepPlan]:
+        """The next step, planned before the tokens of the step in flight are known,
+        for the common case in which it is certain but for those tokens: nobody
+        waits, every running request decodes and stays below its length limit
+        whatever token it gets, and one more token fits each without taking
+        pages from anyone.  Returns None otherwise.  The plan holds no token
+        values (a portion reads them when asked); it is void if a request ends
+        (end-of-sequence, cancel) or arrives before it is used - the caller
+        checks that with ``ahead_still_holds`` - and the pages it reserved then
+        simply stay with their requests."""
+        if self.waiting:
+            return None
+        live = [s for s in self.running if not s.finished]
+        if not live or len(live) > self.config.max_tokens_per_step:
+            return None
+        for seq in live:
+            # its token of the step in flight is not appended yet: it will have
+            # len(generated_ids) + 1 tokens and must still be short of the limit
+            if seq.phase != Phase.DECODE or seq.cache is None \
+                    or len(seq.generated_ids) + 1 >= seq.options.max_new_tokens \
+                    or seq.num_computed + 1 >= self.max_model_len:
+                return None
+        live.sort(key=lambda s: s.admitted_at)
+        plan = StepPlan()
+        for seq in live:
+            need = self._to_reserve(seq, 1)
+            if need:
+                if not self.cache.can_extend(seq.cache, need):
+                    return None  # what was reserved so far stays with its requests
+                self.cache.extend(seq.cache, need)
+            plan.portions.append(Portion(seq, seq.num_computed, 1, True))
+        return plan
+
+    def ahead_still_holds(self, plan: StepPlan) -> bool:
+        """Whether a plan of ``plan_decode_ahead`` can run now that the tokens of
+        the step before it are appended."""
+        if self.waiting:
+            return False
+        live = [s for s in self.running if not s.finished]
+        return len(live) == len(plan.portions) and all(
+            not p.seq.finished and p.seq.cache is not None and p.seq.phase == Phase.DECODE
+            and p.start == p.seq.num_computed and p.seq.num_tokens == p.start + 1
+            for p in plan.portions)
 
     def _trim_to_multiple(self, plan: StepPlan) -> None:
         m = self.config.token_multiple

@@ -183,3 +183,40 @@ def test_requests_come_and_go_under_recorded_decode_graphs(folders, dtype):
         assert len(h.tokens) == o.max_new_tokens
         assert_same_up_to_ties(folders["B"], p, h.tokens, solo.generate(p, o), dtype)
     assert engine.cache.free_pages() == [96] and engine.cache.num_free_slots == 8
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_planned_ahead_survive_ends_and_arrivals(folders, dtype):
+    """While a decode step runs, the engine plans and prepares the next one.  A
+    request that ends on an end-of-sequence token, one that is cancelled and one
+    that arrives each void such a plan; the tokens of the others do not change."""
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype=dtype)
+    cfg = ib.BatchConfig(max_batch_size=4, block_size=8, num_blocks=96, max_prefill_tokens=64)
+    solo = ib.Engine(model, cfg)
+    prompts = [random_tokens(n, 320, 70 + n) for n in (5, 9, 14, 6)]
+    sampled = ib.SamplingParams(temperature=0.9, top_p=0.95, seed=3, repetition_penalty=1.3)
+    alone = [solo.generate(prompts[0], ib.GenerateOptions(max_new_tokens=30)),
+             solo.generate(prompts[1], ib.GenerateOptions(max_new_tokens=30, sampling=sampled)),
+             solo.generate(prompts[2], ib.GenerateOptions(max_new_tokens=30)),
+             solo.generate(prompts[3], ib.GenerateOptions(max_new_tokens=12))]
+    stop = alone[0][10]  # request 0 ends where this token first shows
+    engine = ib.Engine(model, cfg)
+    h0 = engine.submit(prompts[0], ib.GenerateOptions(max_new_tokens=30, eos_token_id=stop))
+    h1 = engine.submit(prompts[1], ib.GenerateOptions(max_new_tokens=30, sampling=sampled))
+    h2 = engine.submit(prompts[2], ib.GenerateOptions(max_new_tokens=30))
+    for _ in range(5):
+        engine.step()
+    h3 = engine.submit(prompts[3], ib.GenerateOptions(max_new_tokens=12))  # arrives
+    while len(h2.tokens) < 20:
+        engine.step()
+    engine.cancel(h2)
+    engine.run_until_done([h0, h1, h3])
+    assert engine.stats.ahead_used > 10 and engine.stats.ahead_voided >= 2
+    assert h3.finish_reason == ib.FinishReason.LENGTH and len(h3.tokens) == 12 and len(h1.tokens) == 30
+    if dtype == "float32":  # token for token; in bfloat16 the solo engine may round a near-tie otherwise
+        assert h0.tokens == alone[0][: alone[0].index(stop)] and h0.finish_reason == ib.FinishReason.STOP
+        assert h1.tokens == alone[1] and h3.tokens == alone[3]
+        assert h2.tokens == alone[2][: len(h2.tokens)]
+    engine.step()
+    assert engine.cache.free_pages() == [96] and engine.cache.num_free_slots == 4

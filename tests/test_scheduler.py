@@ -274,3 +274,50 @@ def test_a_cut_portion_that_would_have_ended_its_prompt_asks_for_no_logits():
                     CacheManager([need], page_size=16, num_pages=256, max_requests=4), 4096)
     off.add_request(list(range(3, 523)), GenerateOptions(max_new_tokens=2, ignore_eos=True))
     assert off.schedule().num_tokens == 520
+
+
+def test_the_next_decode_step_can_be_planned_before_its_tokens_are_known():
+    sched, cache = make(num_blocks=64, block_size=4, max_batch=4, chunk=8, budget=16)
+    opts = GenerateOptions(max_new_tokens=6, ignore_eos=True)
+    a = sched.add_request([5, 6, 7], opts)
+    b = sched.add_request([8, 9], opts)
+    run_step(sched, cache)  # prompts; both decode from here on
+    # a decode step in flight: scheduled and committed, its tokens not yet appended
+    plan = sched.schedule()
+    sched.commit(plan, commit_cache=True)
+    ahead = sched.plan_decode_ahead()
+    assert ahead is not None and [p.seq for p in ahead.portions] == [a, b]
+    assert [(p.start, p.count, p.wants_logits) for p in ahead.portions] == \
+        [(a.num_computed, 1, True), (b.num_computed, 1, True)]
+    for p in plan.portions:
+        sched.append_token(p.seq, fake_token(p.seq))
+    assert sched.ahead_still_holds(ahead)
+    assert [p.tokens for p in ahead.portions] == [[a.generated_ids[-1]], [b.generated_ids[-1]]]
+    cache.check_invariants()
+    # a request that arrives, or one that ends, voids the plan
+    sched.add_request([1, 2, 3], opts)
+    assert not sched.ahead_still_holds(ahead)
+    drain(sched, cache)
+    assert a.generated_ids == solo_tokens([5, 6, 7], 6)
+
+
+def test_no_plan_ahead_when_a_request_is_about_to_reach_its_limit_or_pages_are_short():
+    sched, cache = make(num_blocks=64, block_size=4)
+    a = sched.add_request([5, 6, 7], GenerateOptions(max_new_tokens=2, ignore_eos=True))
+    run_step(sched, cache)
+    plan = sched.schedule()
+    sched.commit(plan, commit_cache=True)
+    assert sched.plan_decode_ahead() is None  # the token in flight is its last
+    for p in plan.portions:
+        sched.append_token(p.seq, fake_token(p.seq))
+    assert a.finished
+    # pages: two requests that fill the pool exactly cannot both grow
+    sched, cache = make(num_blocks=4, block_size=4)
+    opts = GenerateOptions(max_new_tokens=8, ignore_eos=True)
+    sched.add_request([1] * 7, opts)
+    sched.add_request([2] * 7, opts)
+    run_step(sched, cache)           # 7 tokens each: two pages each, the pool is full
+    plan = sched.schedule()          # token 8 fits the pages held
+    sched.commit(plan, commit_cache=True)
+    assert sched.plan_decode_ahead() is None  # token 9 would need a fifth page
+    cache.check_invariants()
