@@ -809,7 +809,7 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
                 }
             }
         }
-        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+        if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_SPLIT_PRODUCER));
     } else {
         // ---- the four computing warps -----------------------------------------------------
         unsigned qf[HD / 16][2];
@@ -906,7 +906,7 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[st]);   // my warp is done with this stage
         }
-        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+        if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_SPLIT_COMPUTE));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);

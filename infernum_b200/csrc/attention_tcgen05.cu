@@ -47,7 +47,13 @@ constexpr int Q_BYTES = BM * HD * 2;
 constexpr int K_BYTES = BN * HD * 2;
 constexpr int V_BYTES = BN * HD * 2;
 constexpr int P_BYTES = BM * BN * 2;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * K_BYTES + V_BYTES + P_BYTES + 1024;  // K is double-buffered
+constexpr int TILE_BYTES = Q_BYTES + 2 * K_BYTES + V_BYTES + 2 * P_BYTES;  // K and P are double-buffered
+constexpr int BAR_BYTES = 128;  // the mbarriers and the TMEM address, behind the tiles
+// Two CTAs must fit an SM (228 KB, 1 KB of it taken per CTA): the kernel has no
+// static shared memory, so its dynamic window starts on a 1 KB boundary and the
+// tiles need no padding in front; what is left of the budget is slack for it.
+constexpr int SMEM_BYTES = (HD == 128) ? (233472 / 2 - 1024) : (TILE_BYTES + BAR_BYTES + 1024);
+static_assert(TILE_BYTES + BAR_BYTES <= SMEM_BYTES, "tiles and barriers exceed the shared memory asked for");
 constexpr unsigned TMEM_COLS = 256;     // two score tiles in columns [0, 64) and [64, 128), output from 128
 constexpr unsigned O_COL = 128;
 
@@ -126,6 +132,27 @@ __device__ __forceinline__ void tmem_st16(unsigned addr, const unsigned (&r)[16]
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+// Sixty-four consecutive columns of this thread's lane and the wait for them, as
+// one statement: the values may be used as soon as it returns, and the four
+// loads are in flight together.
+__device__ __forceinline__ void tmem_ld64_wait(unsigned addr, float (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%64];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%65];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47}, [%66];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%67];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+          "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
+          "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
+          "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31]),
+          "=f"(r[32]), "=f"(r[33]), "=f"(r[34]), "=f"(r[35]), "=f"(r[36]), "=f"(r[37]), "=f"(r[38]), "=f"(r[39]),
+          "=f"(r[40]), "=f"(r[41]), "=f"(r[42]), "=f"(r[43]), "=f"(r[44]), "=f"(r[45]), "=f"(r[46]), "=f"(r[47]),
+          "=f"(r[48]), "=f"(r[49]), "=f"(r[50]), "=f"(r[51]), "=f"(r[52]), "=f"(r[53]), "=f"(r[54]), "=f"(r[55]),
+          "=f"(r[56]), "=f"(r[57]), "=f"(r[58]), "=f"(r[59]), "=f"(r[60]), "=f"(r[61]), "=f"(r[62]), "=f"(r[63])
+        : "r"(addr), "r"(addr + 16), "r"(addr + 32), "r"(addr + 48)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -169,13 +196,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const __grid_constant__ CUtensorMap map_v, const Params p) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    if (smem + TILE_BYTES + BAR_BYTES > smem_dyn + SMEM_BYTES) {
+        // the window does not start where the budget assumes: refuse rather than overrun
+        if (threadIdx.x == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_LAYOUT));
+        return;
+    }
     unsigned char* q_s = smem;
     unsigned char* k_s = q_s + Q_BYTES;
     unsigned char* v_s = k_s + 2 * K_BYTES;
     unsigned char* p_s = v_s + V_BYTES;
-    __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full,
-        o_done;
-    __shared__ unsigned tmem_slot;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 2 * P_BYTES);
+    // o_done[b]: the output update of a tile t with t % 2 == b is complete (two
+    // barriers, because the softmax warps wait for tile t - 2 when tile t - 1 may
+    // be complete as well: one barrier's parity could not tell those apart)
+    unsigned long long& q_full = bars[0];
+    unsigned long long* k_full = bars + 1;
+    unsigned long long* k_empty = bars + 3;
+    unsigned long long& v_full = bars[5];
+    unsigned long long& v_empty = bars[6];
+    unsigned long long* s_full = bars + 7;
+    // p_full[b]: P of a tile t with t % 2 == b is written.  Two barriers, as for
+    // o_done: with two P buffers the softmax warps may finish tile t + 1 before the
+    // MMA thread has looked at tile t.
+    unsigned long long* p_full = bars + 9;
+    unsigned long long* o_done = bars + 11;
+    unsigned& tmem_slot = *reinterpret_cast<unsigned*>(bars + 13);
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -203,8 +248,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         mbar_init(&v_full, 1);
         mbar_init(&v_empty, 1);
-        mbar_init(&p_full, 128);
-        mbar_init(&o_done, 1);
+        mbar_init(&p_full[0], 128);
+        mbar_init(&p_full[1], 128);
+        mbar_init(&o_done[0], 1);
+        mbar_init(&o_done[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 5) {
@@ -275,7 +322,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 load(v_s, &map_v, &v_full, tv, wv);
             }
         }
-        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+        if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_PRODUCER));
     } else if (warp == 5) {
         // ---- MMA issuer -------------------------------------------------------------
         if (elect_one()) {
@@ -306,19 +353,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // before they signalled p_full(t - 1), waited for in the last round.
                 if (t + 1 < n_tiles && !issue_scores(t + 1)) { ok = false; break; }
                 // O += P V once the softmax warps have written P (and rescaled O)
-                if (!mbar_wait(&p_full, t & 1) || !mbar_wait(&v_full, t & 1)) { ok = false; break; }
+                if (!mbar_wait(&p_full[t & 1], (t >> 1) & 1) || !mbar_wait(&v_full, t & 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t a = desc_k_major(p_s);
+                const uint64_t a = desc_k_major(p_s + (t & 1) * P_BYTES);
                 const uint64_t b = desc_n_major(v_s, BN * 128);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
                     umma_bf16(tmem + O_COL, a + 2 * kk, b + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_o,
                               (t > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&v_empty);
-                umma_commit(&o_done);
+                umma_commit(&o_done[t & 1]);
             }
             if (!ok) {
-                atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+                atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_MMA));
                 // let the softmax warps run out of their waits quickly
             }
         }
@@ -334,46 +381,47 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int t = 0; t < n_tiles; ++t) {
             if (ok && !mbar_wait(&s_full[t & 1], (t >> 1) & 1)) ok = false;
             tc_fence_after();
+            static_assert(BN == 64, "the score tile is read 64 columns at a time");
             float s[BN];
-#pragma unroll
-            for (int c = 0; c < BN; c += 16) {
-                unsigned v[16];
-                tmem_ld16(lane_addr + (t & 1) * BN + c, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) s[c + j] = __uint_as_float(v[j]);
-            }
+            tmem_ld64_wait(lane_addr + (t & 1) * BN, s);
+            // The running maximum is kept in raw scores (the scale is positive); the
+            // scale and the maximum enter the exponent in one multiply-add.
             const int tile_start = t * BN;
             float m_new = m_run;
             if (tile_start + BN - 1 > pos0 + r_begin || !valid) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
-                    s[c] = (tile_start + c <= my_pos) ? s[c] * p.scale_log2 : -INFINITY;
+                    s[c] = (tile_start + c <= my_pos) ? s[c] : -INFINITY;
                     m_new = fmaxf(m_new, s[c]);
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
-                    s[c] *= p.scale_log2;
-                    m_new = fmaxf(m_new, s[c]);
-                }
+                for (int c = 0; c < BN; c += 2) m_new = fmaxf(m_new, fmaxf(s[c], s[c + 1]));
             }
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = fast_exp2(m_run - m_use);
-            m_run = m_new;
-            float sum = 0.f;
+            // The exponents refer to m_run, which follows the true maximum only when
+            // that has risen by more than 2^8 in the exponent: softmax does not depend
+            // on the reference, P stays below 256 (fine in bfloat16, the sum is 32-bit),
+            // and the output accumulator is rescaled seldom instead of at most tiles.
+            const bool move = m_new > -INFINITY && (m_run == -INFINITY || (m_new - m_run) * p.scale_log2 > 8.f);
+            const float m_ref = move ? m_new : m_run;
+            const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
+            const float corr = move ? fast_exp2(fmaf(m_run, p.scale_log2, -m_scaled)) : 1.f;
+            m_run = m_ref;
+            float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                s[c] = fast_exp2(s[c] - m_use);
-                sum += s[c];
+            for (int c = 0; c < BN; c += 2) {
+                s[c] = fast_exp2(fmaf(s[c], p.scale_log2, -m_scaled));
+                s[c + 1] = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_scaled));
+                sum0 += s[c];
+                sum1 += s[c + 1];
             }
-            l_run = l_run * corr + sum;
+            l_run = l_run * corr + (sum0 + sum1);
             // the output accumulator holds tiles 0..t-1: rescale it if any row of
-            // this warp moved its maximum (tile t-1's update must have completed)
-            if (t > 0) {
-                if (ok && !mbar_wait(&o_done, (t - 1) & 1)) ok = false;
+            // this warp moved its reference (tile t-1's update must have completed)
+            if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+                if (ok && !mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) ok = false;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
+                {
 #pragma unroll
                     for (int c = 0; c < HD; c += 16) {
                         unsigned v[16];
@@ -387,25 +435,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
             // P (bf16) into the K-major swizzled tile [128 rows][64 keys]: row m,
-            // 16-byte chunk ch sits at chunk position ch ^ (m % 8) of its 128-byte row
+            // 16-byte chunk ch sits at chunk position ch ^ (m % 8) of its 128-byte row.
+            // Two P buffers: this one was last read by the output update of tile t - 2.
+            if (t >= 2 && ok && !mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1)) ok = false;
+            unsigned char* p_t = p_s + (t & 1) * P_BYTES;
 #pragma unroll
             for (int ch = 0; ch < BN / 8; ++ch) {
                 uint4 pk;
                 __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(s[ch * 8 + 2 * j], s[ch * 8 + 2 * j + 1]);
-                *reinterpret_cast<uint4*>(p_s + m * 128 + ((ch ^ (m & 7)) << 4)) = pk;
+                *reinterpret_cast<uint4*>(p_t + m * 128 + ((ch ^ (m & 7)) << 4)) = pk;
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
-            mbar_arrive(&p_full);
+            mbar_arrive(&p_full[t & 1]);
         }
         // ---- epilogue: O / l -------------------------------------------------------
         if (n_tiles > 0) {
-            if (ok && !mbar_wait(&o_done, (n_tiles - 1) & 1)) ok = false;
+            if (ok && !mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) ok = false;
             tc_fence_after();
         }
-        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+        if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_SOFTMAX));
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         bf16* dst = valid ? p.out + (size_t)(row0 + r_begin + r) * p.out_stride + (size_t)(g * G + h) * HD : nullptr;
 #pragma unroll

@@ -21,6 +21,20 @@
 #define IB_FLAG_BAD_TOKEN 1u      // token id outside the vocabulary
 #define IB_FLAG_BAD_PAGE 2u       // block-table entry outside the pool
 #define IB_FLAG_WAIT_TIMEOUT 4u   // a bounded wait on a barrier gave up
+// Which wait gave up: bit 8 + site is set beside IB_FLAG_WAIT_TIMEOUT.
+#define IB_SITE_GEMM_PRODUCER 0      // gemm_tcgen05: TMA producer
+#define IB_SITE_GEMM_MMA 1           // gemm_tcgen05: MMA issuer
+#define IB_SITE_GEMM_EPILOGUE 2      // gemm_tcgen05: epilogue
+#define IB_SITE_PAIR_PRODUCER 3      // gemm_tcgen05_2cta: TMA producer
+#define IB_SITE_PAIR_MMA 4           // gemm_tcgen05_2cta: MMA issuer
+#define IB_SITE_PAIR_EPILOGUE 5      // gemm_tcgen05_2cta: epilogue
+#define IB_SITE_ATTN_TC_PRODUCER 6   // attention_tcgen05: TMA producer
+#define IB_SITE_ATTN_TC_MMA 7        // attention_tcgen05: MMA issuer
+#define IB_SITE_ATTN_TC_SOFTMAX 8    // attention_tcgen05: softmax warps
+#define IB_SITE_ATTN_TC_LAYOUT 9     // attention_tcgen05: shared memory window not where the budget assumes
+#define IB_SITE_SPLIT_PRODUCER 10    // attention_mma split mode: TMA producer
+#define IB_SITE_SPLIT_COMPUTE 11     // attention_mma split mode: computing warps
+#define IB_TIMEOUT_AT(site) (IB_FLAG_WAIT_TIMEOUT | (1u << (8 + (site))))
 
 #define IB_EXPORT extern "C" __attribute__((visibility("default")))
 

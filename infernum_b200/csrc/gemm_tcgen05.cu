@@ -261,7 +261,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                 const int s = i % STAGES;
                 const unsigned round = i / STAGES;
                 if (!mbar_wait(&empty_bar[s], (round - 1) & 1)) {
-                    atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+                    atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_GEMM_PRODUCER));
                     gave_up = 1;
                     break;
                 }
@@ -282,7 +282,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                 const int s = i % STAGES;
                 const unsigned round = i / STAGES;
                 if (!mbar_wait(&full_bar[s], round & 1)) {
-                    atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+                    atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_GEMM_MMA));
                     gave_up = 1;
                     ok = false;
                     break;
@@ -309,7 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         pdl_wait();  // nothing is stored before the kernels ahead of this one are done
         bool ok = mbar_wait(&accum_bar, 0);
         if (!ok && lane == 0) {
-            atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+            atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_GEMM_EPILOGUE));
             gave_up = 1;
         }
         tc_fence_after();

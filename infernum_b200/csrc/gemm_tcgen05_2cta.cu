@@ -273,7 +273,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     tma_load_2d_pair(xs + X_BYTES, mw, &full_bar[s], i * BK, n0);
                 }
             }
-            if (!ok) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+            if (!ok) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_PAIR_PRODUCER));
         }
     } else if (warp == 1) {
         // ---- MMA issuer (leader CTA only) -----------------------------------------------
@@ -300,7 +300,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
                 if (ok) umma_commit_pair(&acc_full[buf]);
             }
-            if (!ok) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+            if (!ok) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_PAIR_MMA));
         }
     } else {
         // ---- epilogue: my 128 tokens x the tile's weight rows, half of them per warp ------------
@@ -362,7 +362,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
         }
-        if (!ok && lane == 0) atomicOr(p.err, IB_FLAG_WAIT_TIMEOUT);
+        if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_PAIR_EPILOGUE));
     }
     tc_fence_before();
     cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still use it

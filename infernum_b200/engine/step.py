@@ -186,8 +186,4 @@ class ModelRunner:
         flags = int(self.rt.err.item())
         if flags:
             self.rt.err.zero_()
-            what = [name for bit, name in ((core.FLAG_BAD_TOKEN, "token id outside the vocabulary"),
-                                           (core.FLAG_BAD_PAGE, "block-table entry outside the pool"),
-                                           (core.FLAG_WAIT_TIMEOUT, "a device-side wait ran out"))
-                    if flags & bit]
-            raise KernelError("a kernel reported: " + "; ".join(what))
+            raise KernelError("a kernel reported: " + core.describe_flags(flags))

@@ -25,6 +25,21 @@ _c_ll = ctypes.c_longlong
 FLAG_BAD_TOKEN = 1
 FLAG_BAD_PAGE = 2
 FLAG_WAIT_TIMEOUT = 4
+# beside FLAG_WAIT_TIMEOUT, bit 8 + i says which wait gave up (common.cuh: IB_SITE_*)
+TIMEOUT_SITES = ["product for few tokens: producer", "product for few tokens: MMA issuer",
+                 "product for few tokens: epilogue", "product on SM pairs: producer",
+                 "product on SM pairs: MMA issuer", "product on SM pairs: epilogue",
+                 "prompt attention: producer", "prompt attention: MMA issuer", "prompt attention: softmax",
+                 "prompt attention: shared memory window misplaced", "decode attention: producer",
+                 "decode attention: computing warps"]
+
+
+def describe_flags(flags: int) -> str:
+    what = [name for bit, name in ((FLAG_BAD_TOKEN, "token id outside the vocabulary"),
+                                   (FLAG_BAD_PAGE, "block-table entry outside the pool"),
+                                   (FLAG_WAIT_TIMEOUT, "a device-side wait ran out")) if flags & bit]
+    sites = [name for i, name in enumerate(TIMEOUT_SITES) if flags & (1 << (8 + i))]
+    return "; ".join(what) + (" (" + ", ".join(sites) + ")" if sites else "")
 
 _ERR_NAMES = {-1: "bad argument", -2: "unsupported configuration", -3: "size beyond the kernel's maximum"}
 
