@@ -742,7 +742,12 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
-    pdl_wait();  // queries, keys, values and tables come from the kernels before this one
+    // What the kernel before this one wrote - the queries, and the keys and values
+    // of this step's tokens - is waited for where it is first needed: the computing
+    // warps wait before they read the queries, the producer before the first tile
+    // that holds a token of this step.  Older keys and values, the block tables
+    // and the step's positions were complete before this chain of kernels began,
+    // so the first tiles are under way while the predecessor finishes.
 
     const int e = blockIdx.y;
     const int g = blockIdx.z / p.n_hsub_split;
@@ -786,10 +791,16 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
         };
         int page_next = lookup(t_begin);
         bool ok = true;
+        const int t_wait = (pos0 - kv_lo) / BN;  // the first tile with a token of this step
+        bool waited = false;
         for (int t = t_begin; t < t_end; ++t) {
             const int i = t - t_begin, st = i % TMA_STAGES;
             int page = page_next;
             page_next = lookup(t + 1);
+            if (!waited && t >= t_wait) {
+                pdl_wait();
+                waited = true;
+            }
             if (i >= TMA_STAGES && !mbar_wait(&empty_bar[st], ((i / TMA_STAGES) - 1) & 1)) { ok = false; break; }
             if (lane == 0) mbar_expect_tx(&full_bar[st], TMA_STAGE_BYTES);
             __syncwarp();
@@ -810,8 +821,10 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
             }
         }
         if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_SPLIT_PRODUCER));
+        if (!waited) pdl_wait();  // this warp helps to write the result, which a predecessor may still read
     } else {
         // ---- the four computing warps -----------------------------------------------------
+        pdl_wait();
         unsigned qf[HD / 16][2];
         {
             const int r = gid / gs, hh = hsub * gs + gid % gs;

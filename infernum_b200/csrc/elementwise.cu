@@ -354,7 +354,10 @@ __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
                                         int page_size, int num_pages, int write_kv,
                                         unsigned* __restrict__ err) {
     pdl_trigger();
-    pdl_wait();
+    // Positions, block tables and frequencies were complete before this chain of
+    // kernels began: the page look-up and the sines and cosines of this thread's
+    // first item are done while the product before this kernel still runs, and
+    // only then is its result waited for.
     const int row = blockIdx.x;
     const int rot_items = rd >> 4;             // per head: items of 8 pairs
     const int pass_items = (hd - rd) >> 3;     // per head: items of 8 unrotated elements
@@ -378,7 +381,20 @@ __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
     const long long head_step = (long long)page_size * hd;
     const int half = rd >> 1;
 
-    for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < items; it += gridDim.y * blockDim.x) {
+    const int first_it = blockIdx.y * blockDim.x + threadIdx.x;
+    float sn[8], cs[8];
+    auto angles = [&](int it) {
+        if (it < items_qk && it % per_head < rot_items) {
+            const int j = (it % per_head) << 3;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sincosf((float)pos * inv_freq[j + k], &sn[k], &cs[k]);
+        }
+    };
+    angles(first_it);
+    pdl_wait();
+
+    for (int it = first_it; it < items; it += gridDim.y * blockDim.x) {
+        if (it != first_it) angles(it);
         if (it < items_qk) {
             const int head = it / per_head, p = it % per_head;
             bf16* x = base + (size_t)head * hd;
@@ -393,9 +409,7 @@ __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const float2 xa = __bfloat1622float2(a2[k]), xb = __bfloat1622float2(b2[k]);
-                    float s0, c0, s1, c1;
-                    sincosf((float)pos * inv_freq[j + 2 * k], &s0, &c0);
-                    sincosf((float)pos * inv_freq[j + 2 * k + 1], &s1, &c1);
+                    const float s0 = sn[2 * k], c0 = cs[2 * k], s1 = sn[2 * k + 1], c1 = cs[2 * k + 1];
                     a2[k] = __floats2bfloat162_rn(xa.x * c0 - xb.x * s0, xa.y * c1 - xb.y * s1);
                     b2[k] = __floats2bfloat162_rn(xa.x * s0 + xb.x * c0, xa.y * s1 + xb.y * c1);
                 }
