@@ -563,22 +563,42 @@ IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, i
 // position on, and (optionally) the token just selected becomes the next input.
 // ---------------------------------------------------------------------------
 __global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __restrict__ selected,
-                                      int* __restrict__ positions, int* __restrict__ kv_len, int n) {
+                                      int* __restrict__ positions, int* __restrict__ kv_len,
+                                      const int* __restrict__ slot_ids, int pad_slot, int n) {
     pdl_trigger();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
+    // a row that only fills up a batch bucket stays where it is: at position 0 of the spare page
+    if (slot_ids && slot_ids[i] == pad_slot) return;
     positions[i] += 1;
     kv_len[i] += 1;
     if (selected) tokens[i] = selected[i];
 }
 
+// ---------------------------------------------------------------------------
+// The first launch of every step.  The kernels of this package start under the
+// tail of their predecessor (programmatic dependent launch) and some read what
+// describes the step - positions, block tables, row offsets - before they wait
+// for it.  Those must be complete by then, whoever wrote them (a copy from the
+// host, or the advance kernel of the step before).  This kernel is launched
+// the ordinary way, so it starts only when everything before it in the stream
+// is complete, and the kernels after it cannot start before it does.
+// ---------------------------------------------------------------------------
+__global__ void step_fence_kernel() {}
+
+IB_EXPORT int ib_step_fence(void* stream) {
+    step_fence_kernel<<<1, 1, 0, (cudaStream_t)stream>>>();
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
 IB_EXPORT int ib_decode_advance(int* tokens, const int* selected, int* positions, int* kv_len,
-                                int n, void* stream) {
+                                const int* slot_ids, int pad_slot, int n, void* stream) {
     if (n <= 0) return IB_OK;
     if (!tokens || !positions || !kv_len) return IB_ERR_BAD_ARG;
     { cudaError_t le__ = launch_kernel(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, tokens, selected,
-                                                                             positions, kv_len, n); if (le__ != cudaSuccess) return (int)le__; }
+                                                                             positions, kv_len, slot_ids, pad_slot, n); if (le__ != cudaSuccess) return (int)le__; }
     IB_LAUNCH_CHECK();
     return IB_OK;
 }

@@ -170,7 +170,8 @@ class DecodeRunner:
             core.sample(slot.logits, slot.params, slot.recent, slot.sampled)
             slot.selected.copy_(torch.where(slot.mask, slot.sampled, slot.selected))
         if device_feed:
-            core.decode_advance(slot.ctx.token_ids, slot.selected, slot.ctx.positions, slot.ctx.kv_len)
+            core.decode_advance(slot.ctx.token_ids, slot.selected, slot.ctx.positions, slot.ctx.kv_len,
+                                slot.ctx.slot_ids, self.cache.pad_slot)
         else:
             # what the host reads after the step, in one piece
             torch.cat((slot.selected, self.rt.err), out=slot.result)

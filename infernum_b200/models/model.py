@@ -13,6 +13,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..errors import ConfigError
+from ..ops import core
 from ..parts import (EMBEDDINGS, HEADS, NORMS, Block, ModelSpec, PagedCacheSpec, ResidualStream,
                      Runtime, StateSpec, WeightSpec, build_layer)
 
@@ -88,6 +89,8 @@ class Model:
         [wanted rows, vocab], or None when no row is wanted."""
         if not self.bound:
             raise ConfigError("the model has no weights bound")
+        # nothing of this step starts before what describes it (positions, tables) is complete
+        core.step_fence(self.rt.device)
         stream = ResidualStream(self.embedding.forward(ctx.token_ids))
         for item, cache in zip(self.schedule, caches):
             self.layers[item.layer].forward(stream, ctx, cache)

@@ -50,6 +50,8 @@ def core_lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         lib = load_module("core", CORE_SOURCES)
+        lib.ib_step_fence.argtypes = [_c_void_p]
+        lib.ib_step_fence.restype = _c_int
         lib.ib_embed.argtypes = [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
                                  _c_void_p, _c_void_p]
         lib.ib_add_rmsnorm.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
@@ -70,7 +72,8 @@ def core_lib() -> ctypes.CDLL:
                                   _c_void_p]
         lib.ib_sample.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                                   _c_void_p, _c_void_p]
-        lib.ib_decode_advance.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p]
+        lib.ib_decode_advance.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                          _c_void_p]
         for fn in ("ib_decode_advance", "ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
                    "ib_silu_mul", "ib_attention_plain", "ib_gemm_plain", "ib_argmax", "ib_sample"):
             getattr(lib, fn).restype = _c_int
@@ -123,6 +126,15 @@ def _int32(t: Optional[torch.Tensor], name: str) -> None:
 
 def new_error_word(device) -> torch.Tensor:
     return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def step_fence(device) -> None:
+    """The first launch of a step: an empty kernel launched the ordinary way, so
+    that no kernel of the step starts before everything earlier in the stream -
+    the copies and kernels that wrote the step's positions and tables - is
+    complete (the package's other kernels start under their predecessor's tail
+    and read those early)."""
+    check(core_lib().ib_step_fence(torch.cuda.current_stream(device).cuda_stream), "step_fence")
 
 
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
@@ -323,11 +335,14 @@ def sample(logits: torch.Tensor, params: torch.Tensor, recent: Optional[torch.Te
 
 
 def decode_advance(tokens: torch.Tensor, selected: Optional[torch.Tensor], positions: torch.Tensor,
-                   kv_len: torch.Tensor) -> None:
-    """positions += 1, kv_len += 1, and tokens = selected when given."""
-    require_cuda(tokens, selected, positions, kv_len)
-    for t, name in ((tokens, "tokens"), (selected, "selected"), (positions, "positions"), (kv_len, "kv_len")):
+                   kv_len: torch.Tensor, slot_ids: Optional[torch.Tensor] = None, pad_slot: int = -1) -> None:
+    """positions += 1, kv_len += 1, and tokens = selected when given; rows whose
+    slot is ``pad_slot`` (they only fill up a batch bucket) are left alone."""
+    require_cuda(tokens, selected, positions, kv_len, slot_ids)
+    for t, name in ((tokens, "tokens"), (selected, "selected"), (positions, "positions"), (kv_len, "kv_len"),
+                    (slot_ids, "slot_ids")):
         _int32(t, name)
     check(core_lib().ib_decode_advance(tokens.data_ptr(), _ptr(selected), positions.data_ptr(),
-                                       kv_len.data_ptr(), tokens.numel(), stream_ptr(tokens)),
+                                       kv_len.data_ptr(), _ptr(slot_ids), int(pad_slot), tokens.numel(),
+                                       stream_ptr(tokens)),
           "decode_advance")

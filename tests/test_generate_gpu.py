@@ -220,3 +220,44 @@ def test_decode_steps_planned_ahead_survive_ends_and_arrivals(folders, dtype):
         assert h2.tokens == alone[2][: len(h2.tokens)]
     engine.step()
     assert engine.cache.free_pages() == [96] and engine.cache.num_free_slots == 4
+
+
+def test_self_feeding_decode_steps_with_and_without_graph_equal_the_engine(folders):
+    """Decode steps that feed themselves on the device (the selected token and the
+    advanced position of one step are the input of the next, with no copy from
+    the host between them) launched kernel by kernel, the same replayed from a
+    graph, and the engine's host-fed steps give the same tokens.  Kernels start
+    under their predecessor's tail and read positions early: the step before
+    must be complete by then."""
+    import infernum_b200 as ib
+    from infernum_b200.cache import CacheManager
+    from infernum_b200.engine.decode import DecodeRunner
+    from infernum_b200.engine.step import ModelRunner, StepEntry
+    from infernum_b200.ops import core
+    model = ib.load_model(folders["B"], dtype="float32")
+    prompts = [random_tokens(n, 320, 90 + n) for n in (7, 30, 12)]
+    steps = 40
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=4, block_size=8, num_blocks=96))
+    want = engine.generate_batch(prompts, ib.GenerateOptions(max_new_tokens=steps + 1))
+    for use_graph in (False, True):
+        cache = CacheManager(model.cache_needs(), page_size=8, num_pages=96, max_requests=4,
+                             dtype=model.rt.dtype, device=model.rt.device)
+        runner = ModelRunner(model, cache, max_rows=64, max_entries=4)
+        caches, first = [], []
+        for i, p in enumerate(prompts):
+            rc = cache.admit(("r", i))
+            logits = runner.step([StepEntry(rc, p, [len(p) - 1])])
+            out = torch.empty(1, dtype=torch.int32, device=logits.device)
+            core.argmax(logits, out)
+            caches.append(rc)
+            first.append(int(out.item()))
+        assert first == [w[0] for w in want]
+        session = DecodeRunner(runner, 128, use_graph=use_graph)
+        session.pin(caches, first, steps)
+        # nothing is launched between the steps; a token or position read too early
+        # in any of them changes what the last one selects
+        for _ in range(steps):
+            last = session.step_pinned()
+        torch.cuda.synchronize()
+        runner.check_errors()
+        assert last.tolist() == [w[steps] for w in want], f"use_graph={use_graph}"
