@@ -685,7 +685,6 @@ constexpr int TMA_STAGE_BYTES = 2 * TMA_TILE_BYTES;         // K and V
 constexpr int TMA_STAGES = 3;
 constexpr int TMA_SMEM_BYTES = TMA_STAGES * TMA_STAGE_BYTES + 1024;
 constexpr int TMA_THREADS = 160;
-constexpr unsigned WAIT_LIMIT = 1u << 20;
 static_assert(4 * 8 * HD * 4 + 4 * 8 * 2 * 4 + 8 * HD * 4 + 8 * 2 * 4 <= TMA_STAGES * TMA_STAGE_BYTES,
               "the merge buffers reuse the stages");
 
@@ -700,16 +699,7 @@ __device__ __forceinline__ void mbar_arrive(void* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
+    return mbar_wait_bounded<false>(smem_u32(bar), parity);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x, int y) {
     asm volatile(

@@ -42,7 +42,6 @@ constexpr int BM = 128;                 // packed rows per CTA
 constexpr int BN = 64;                  // keys per tile
 constexpr int KB = HD / 64;             // 64-wide blocks of the head dimension
 constexpr int NUM_THREADS = 192;        // 4 softmax warps, producer, MMA
-constexpr unsigned WAIT_LIMIT = 1u << 20;
 constexpr int Q_BYTES = BM * HD * 2;
 constexpr int K_BYTES = BN * HD * 2;
 constexpr int V_BYTES = BN * HD * 2;
@@ -84,16 +83,7 @@ __device__ __forceinline__ void mbar_arrive(void* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
+    return mbar_wait_bounded<false>(smem_u32(bar), parity);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x, int y) {
     asm volatile(

@@ -60,6 +60,46 @@ typedef __nv_bfloat16 bf16;
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
+// ---------------------------------------------------------------------------
+// Bounded wait on an mbarrier in this CTA's shared memory: polls until the phase
+// with the given parity is complete, gives up after IB_WAIT_LIMIT_NS of wall
+// time (read from %globaltimer once in a while, not on the fast path) and
+// returns false then.  `cluster`: arrivals may come from other CTAs of the
+// cluster, so the successful poll acquires at cluster scope.
+// ---------------------------------------------------------------------------
+constexpr unsigned long long IB_WAIT_LIMIT_NS = 2000000000ull;  // two seconds
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+
+template <bool CLUSTER = false>
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar_addr, unsigned parity,
+                                                  unsigned long long limit_ns = IB_WAIT_LIMIT_NS) {
+    unsigned long long t0 = 0;
+    for (;;) {
+        for (int i = 0; i < 2048; ++i) {
+            unsigned done;
+            if (CLUSTER)
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                    "selp.u32 %0, 1, 0, p;\n\t}\n"
+                    : "=r"(done) : "r"(bar_addr), "r"(parity) : "memory");
+            else
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                    "selp.u32 %0, 1, 0, p;\n\t}\n"
+                    : "=r"(done) : "r"(bar_addr), "r"(parity) : "memory");
+            if (done) return true;
+        }
+        const unsigned long long now = global_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > limit_ns) return false;
+    }
+}
+
 inline int& pdl_flag() {
     static int enabled = 1;
     return enabled;

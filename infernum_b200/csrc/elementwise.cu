@@ -593,6 +593,27 @@ IB_EXPORT int ib_step_fence(void* stream) {
     return IB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// A wait that nothing ends, for testing the bounded wait itself: one thread
+// waits `limit_ns` for a barrier on which nobody arrives, sets the time-out
+// flag (with the site bit `site`) and returns.  Nothing faults and nothing
+// hangs; the context stays usable.
+// ---------------------------------------------------------------------------
+__global__ void wait_probe_kernel(unsigned* __restrict__ err, unsigned long long limit_ns, int site) {
+    __shared__ __align__(8) unsigned long long bar;
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(&bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(addr));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if (!mbar_wait_bounded<false>(addr, 0, limit_ns)) atomicOr(err, IB_TIMEOUT_AT(site));
+}
+
+IB_EXPORT int ib_wait_probe(unsigned* err, long long limit_ns, int site, void* stream) {
+    if (!err || limit_ns <= 0 || limit_ns > 1000000000ll || site < 0 || site > 20) return IB_ERR_BAD_ARG;
+    wait_probe_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(err, (unsigned long long)limit_ns, site);
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
 IB_EXPORT int ib_decode_advance(int* tokens, const int* selected, int* positions, int* kv_len,
                                 const int* slot_ids, int pad_slot, int n, void* stream) {
     if (n <= 0) return IB_OK;

@@ -40,7 +40,6 @@ constexpr int BM = 128;       // weight rows per CTA (MMA M)
 constexpr int BK = 64;        // k elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;    // k elements per tcgen05.mma (bf16)
 constexpr int NUM_THREADS = 192;
-constexpr unsigned WAIT_LIMIT = 1u << 20;  // polls of try_wait before giving up (about a second)
 
 __host__ __device__ constexpr int stage_bytes(int bn) { return BM * BK * 2 + bn * BK * 2; }
 __host__ __device__ constexpr int num_stages(int bn) {
@@ -70,19 +69,7 @@ __device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
 }
 // Bounded wait: false when the limit was reached.
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
+    return mbar_wait_bounded<false>(smem_u32(bar), parity);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, void* bar, int x,
                                             int y) {

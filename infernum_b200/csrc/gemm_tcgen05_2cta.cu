@@ -52,7 +52,6 @@ constexpr int STAGE_BYTES = X_BYTES + BNH * BK * 2;   // 32 KiB
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
 constexpr int NUM_THREADS = 320;   // producer, MMA and eight epilogue warps
 constexpr unsigned TMEM_COLS = 512;   // two accumulators of 256 columns
-constexpr unsigned WAIT_LIMIT = 1u << 20;
 constexpr unsigned PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -83,29 +82,11 @@ __device__ __forceinline__ void mbar_arrive_leader(void* bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(remote) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
+    return mbar_wait_bounded<false>(smem_u32(bar), parity);
 }
 // The same, when arrivals come from the other CTA of the pair too.
 __device__ __forceinline__ bool mbar_wait_cluster(void* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
+    return mbar_wait_bounded<true>(smem_u32(bar), parity);
 }
 // A box into this CTA's shared memory; the bytes are counted on the barrier at
 // the same offset in the leader CTA (rank bit cleared).

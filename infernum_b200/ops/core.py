@@ -50,6 +50,8 @@ def core_lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         lib = load_module("core", CORE_SOURCES)
+        lib.ib_wait_probe.argtypes = [_c_void_p, _c_ll, _c_int, _c_void_p]
+        lib.ib_wait_probe.restype = _c_int
         lib.ib_step_fence.argtypes = [_c_void_p]
         lib.ib_step_fence.restype = _c_int
         lib.ib_embed.argtypes = [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
@@ -126,6 +128,15 @@ def _int32(t: Optional[torch.Tensor], name: str) -> None:
 
 def new_error_word(device) -> torch.Tensor:
     return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def wait_probe(err: torch.Tensor, limit_ms: float, site: int) -> None:
+    """Runs a kernel whose one wait nothing ends: after ``limit_ms`` it sets the
+    time-out flag with the bit of ``site`` in ``err`` and returns.  For testing
+    that a wait that runs out is reported and leaves the device usable."""
+    require_cuda(err)
+    check(core_lib().ib_wait_probe(err.data_ptr(), int(limit_ms * 1e6), int(site), stream_ptr(err)),
+          "wait_probe")
 
 
 def step_fence(device) -> None:

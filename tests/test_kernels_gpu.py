@@ -606,3 +606,32 @@ def test_attention_tcgen05_far_key_and_edges():
         assert attention_fast.run(q, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt)
         assert rt.err.item() == 0
         assert rel_err(out, plain_result(refs)) < 1e-2, (L, key)
+
+
+# --------------------------------------------------------------------------
+# a wait that runs out
+# --------------------------------------------------------------------------
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """Every wait of the kernels on a barrier is bounded in time.  Here a probe
+    kernel waits 30 ms for a barrier on which nobody arrives: it returns, the
+    error word says that a wait ran out and which one, and the next kernel runs
+    as if nothing had happened."""
+    import time
+    from infernum_b200.errors import KernelError
+    c = core()
+    err = c.new_error_word(DEV)
+    t0 = time.perf_counter()
+    c.wait_probe(err, 30.0, 7)
+    torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert 0.02 < took < 5.0
+    flags = int(err.item())
+    assert flags & c.FLAG_WAIT_TIMEOUT
+    assert "prompt attention: MMA issuer" in c.describe_flags(flags)
+    assert "a device-side wait ran out" in c.describe_flags(flags)
+    with pytest.raises(KernelError):
+        c.wait_probe(err, 5000.0, 0)  # longer than a second is refused
+    x = torch.randn(4, 64).to(DEV)
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    c.argmax(x, out)
+    assert out.tolist() == x.argmax(dim=1).tolist()
