@@ -34,14 +34,20 @@ PAIR_TILE_OVERHEAD = 66
 
 # Which products the kernel takes: "all", "none", or a largest token count.
 POLICY = {"mode": os.environ.get("INFERNUM_GEMM", "auto"), "max_tokens": 64, "pair_max_padding": 1.13,
-          "sm_count": 148}
+          "pair_min_tokens_plain": 600, "sm_count": 148}
 
 
-def pair_suits(T: int) -> bool:
+def pair_suits(T: int, fused_activation: bool = False) -> bool:
     """The kernel on pairs of SMs works on 256 tokens at a time; it is taken when
-    rounding ``T`` up to that wastes little (measured on the 8B gate/up product:
-    ahead of the library at 256, 512, 768, 1024 and 2048 tokens, behind it at 320
-    and 520)."""
+    rounding ``T`` up to that wastes little (measured on the 8B gate/up product
+    with its activation: ahead of the library product plus activation kernel at
+    256, 512, 768, 1024 and 2048 tokens, behind them at 320 and 520).  A plain
+    product has too few tiles for the 74 pairs below three token tiles (the O
+    product at 256 tokens: 18 us against the library's 11; at 512: 18.6 against
+    14.8; at 768: 21.2 against 21.1), so it is taken from ``pair_min_tokens_plain``
+    tokens on."""
+    if not fused_activation and T < POLICY["pair_min_tokens_plain"]:
+        return False
     return -(-T // 256) * 256 <= POLICY["pair_max_padding"] * T
 
 
@@ -213,7 +219,7 @@ def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor
     if T <= min(POLICY["max_tokens"], 64):
         gemm_tc(x, w_interleaved, out, splits=1, swiglu=True)
         return True
-    if pair_suits(T):
+    if pair_suits(T, fused_activation=True):
         gemm_pair(x, w_interleaved, out, swiglu=True)
         return True
     return False
