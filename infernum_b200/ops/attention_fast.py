@@ -90,7 +90,7 @@ def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count
         return 1
     if 16 * base <= slots and tiles >= 128:
         # (one request of 32,768 keys: 33 us in 16 slices, 30 us in 24, 31 us in 32)
-        return 24 if 10 * base * 24 <= 7 * slots else 16
+        return 24 if tiles >= 256 and 10 * base * 24 <= 7 * slots else 16
     return max(1, min(8, slots // base, tiles))
 
 
