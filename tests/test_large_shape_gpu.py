@@ -64,7 +64,6 @@ def test_8b_class_layers_under_every_cut(models):
     scale = max(v.abs().max().item() for v in ref.values())
 
     def check(rows, tol, what):
-        assert set(rows) >= set(ref) or True
         for key, row in rows.items():
             if key in ref:
                 err = (row - ref[key]).abs().max().item() / scale
@@ -85,8 +84,10 @@ def test_8b_class_layers_under_every_cut(models):
     plan = [[("a", 512, [0, 1, 63, 64, 511]), ("b", 100, [0]), ("d", 39, [])],
             [("a", 150, [0]), ("b", 29, []), ("c", 250, [5]), ("d", 1, [0])],
             [("a", 2, []), ("b", 1, [0]), ("c", 49, [])]]
-    plan += [[("a", 1, [0] if 662 + 2 + i == 699 else []), ("c", 1, [0] if 299 + i == 299 else [])]
-             if i == 0 else [("a", 1, [0] if 664 + i == 699 else [])] for i in range(36)]
+    # after these three steps a has 664 of its 700 tokens, c 299 of 300, b and d are done:
+    # c's last token rides with a's next one, then a decodes alone; the last row of each is wanted
+    plan.append([("a", 1, []), ("c", 1, [0])])
+    plan += [[("a", 1, [0] if 665 + i == 699 else [])] for i in range(35)]
     rows = run(models["bfloat16"], seqs, plan)
     assert ("a", 699) in rows and ("b", 129) in rows and ("c", 299) in rows and ("d", 39) in rows
     check(rows, 4e-2, "bfloat16 mixed")
