@@ -850,6 +850,8 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
                         *reinterpret_cast<uint4*>(const_cast<bf16*>(swz(vs_, row, (c % CH) * 8))) =
                             make_uint4(0u, 0u, 0u, 0u);
                 }
+                // these ordinary stores come before the bulk copy that refills the stage later
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncwarp();
             }
 
