@@ -4,6 +4,7 @@ plain to get the number, or under ``ncu -k regex:<kernel> -c 3`` for counters.
 
     python -m infernum_b200.cli.kernel_bench attention-decode --batch 64 --kv-len 1100
     python -m infernum_b200.cli.kernel_bench attention-prefill --tokens 2048
+    python -m infernum_b200.cli.kernel_bench attention-prefill --tokens 512 --prefix 3584
     python -m infernum_b200.cli.kernel_bench gemm --tokens 8 --n 4096 --k 4096
     python -m infernum_b200.cli.kernel_bench norm --tokens 2048 --hidden 4096
     python -m infernum_b200.cli.kernel_bench rope --tokens 2048
@@ -92,6 +93,7 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--kv-len", type=int, default=1100)
+    ap.add_argument("--prefix", type=int, default=0, help="attention-prefill: cached tokens before the portion")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -100,7 +102,7 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--splits", type=int, default=0, help="force a slice count (attention-decode, gemm)")
+    ap.add_argument("--splits", type=int, default=0, help="force a slice count (attention-decode, attention-prefill, gemm)")
     ap.add_argument("--reps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--library", action="store_true", help="gemm: time the library product instead")
@@ -129,7 +131,8 @@ def main(argv=None) -> int:
         decode = args.kernel == "attention-decode"
         batch = args.batch if decode else 1
         rows = 1 if decode else args.tokens
-        kv_len = args.kv_len if decode else args.tokens
+        # a prompt portion may come after a cached prefix: --prefix tokens already in the cache
+        kv_len = args.kv_len if decode else args.tokens + args.prefix
         cases = [_attention_case(batch, rows, kv_len, nh, nkv, hd, args.page_size, dev)
                  for _ in range(2 if decode else 1)]
         outs = torch.empty(batch * rows, nh * hd, dtype=torch.bfloat16, device=dev)
@@ -138,6 +141,8 @@ def main(argv=None) -> int:
         for q, kp, vp, tables, ctx in cases:
             if decode and args.splits:
                 ctx.attention_mode = (2, args.splits)
+            if not decode and args.splits:
+                ctx.prompt_splits = args.splits
             fns.append(lambda q=q, kp=kp, vp=vp, tables=tables, ctx=ctx: attention_fast.run(
                 q, kp, vp, outs, ctx, tables, nh, scale, 0, rt))
         us = _time(fns, args.reps, args.warmup, not args.no_graph)
@@ -146,8 +151,8 @@ def main(argv=None) -> int:
             out.update(batch=batch, kv_len=kv_len, us=us, gbs=nbytes / us / 1e3,
                        frac_of_hbm=nbytes / us / 1e3 / peaks["hbm_gbs"])
         else:
-            flops = 4.0 * nh * hd * rows * (rows + 1) / 2
-            out.update(tokens=rows, us=us, tflops=flops / us / 1e6,
+            flops = 4.0 * nh * hd * (rows * (rows + 1) / 2 + rows * args.prefix)
+            out.update(tokens=rows, prefix=args.prefix, us=us, tflops=flops / us / 1e6,
                        frac_of_bf16=flops / us / 1e6 / peaks["bf16_tflops"])
     elif args.kernel == "gemm":
         T, N, K = args.tokens, args.n, args.k

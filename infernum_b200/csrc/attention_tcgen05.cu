@@ -53,6 +53,7 @@ constexpr int BAR_BYTES = 128;  // the mbarriers and the TMEM address, behind th
 // tiles need no padding in front; what is left of the budget is slack for it.
 constexpr int SMEM_BYTES = (HD == 128) ? (233472 / 2 - 1024) : (TILE_BYTES + BAR_BYTES + 1024);
 static_assert(TILE_BYTES + BAR_BYTES <= SMEM_BYTES, "tiles and barriers exceed the shared memory asked for");
+static_assert(HD * BM * 4 + 2 * BM * 4 <= TILE_BYTES, "the merge of key slices reuses the tiles' shared memory");
 constexpr unsigned TMEM_COLS = 256;     // two score tiles in columns [0, 64) and [64, 128), output from 128
 constexpr unsigned O_COL = 128;
 
@@ -64,6 +65,7 @@ struct Params {
     unsigned* err;
     int out_stride, max_blocks, nh, nkv, page_size, num_pages;
     int small_rows;     // entries with rows * min(group, 8) <= small_rows belong to split mode
+    int splits;         // CTAs (one cluster) that share the keys of a row tile: 1, 2 or 4
     float scale_log2;
 };
 
@@ -94,6 +96,18 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, v
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// A float from the shared memory of CTA `rank` of this cluster, at the address `local` has here.
+__device__ __forceinline__ float ld_peer_smem(const float* local, unsigned rank) {
+    unsigned raddr;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(raddr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -181,9 +195,11 @@ __host__ __device__ constexpr unsigned make_idesc(int n, bool b_n_major) {
            ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(NUM_THREADS)
-attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+// SPLIT: the variant whose CTAs share a row tile's keys and merge at the end (it
+// carries more state; two CTAs per SM still leave it up to 170 registers).
+template <bool SPLIT>
+__device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const CUtensorMap& map_k,
+                                               const CUtensorMap& map_v, const Params& p) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     if (smem + TILE_BYTES + BAR_BYTES > smem_dyn + SMEM_BYTES) {
@@ -222,12 +238,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int pos0 = p.q_start[e];
     const int gs_split = G < 8 ? G : 8;
     if (rows_e * gs_split <= p.small_rows) return;  // split mode takes this entry
+    // The CTAs of a cluster (p.splits of them, consecutive in x) share one row tile
+    // and take a slice of its key tiles each; they are merged at the end.
+    const int S = SPLIT ? p.splits : 1;
+    const int rank = (int)blockIdx.x % S;
     // the last rows see the most keys: their CTAs go first
-    const int r_begin = ((int)gridDim.x - 1 - (int)blockIdx.x) * rq;
-    if (r_begin >= rows_e) return;
+    const int r_begin = ((int)gridDim.x / S - 1 - (int)blockIdx.x / S) * rq;
+    if (r_begin >= rows_e) return;  // (the whole cluster leaves)
     const int r_count = min(rq, rows_e - r_begin);
     const int kv_hi = pos0 + r_begin + r_count;
-    const int n_tiles = (kv_hi + BN - 1) / BN;
+    const int all_tiles = (kv_hi + BN - 1) / BN;
+    const int per = (all_tiles + S - 1) / S;
+    const int t_off = rank * per;                            // my first key tile
+    const int n_tiles = max(0, min(all_tiles, t_off + per) - t_off);  // and how many are mine
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
@@ -254,6 +277,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tc_fence_after();
     const unsigned tmem = tmem_slot;
     pdl_wait();  // queries, keys and values come from the kernels before this one
+    // what a softmax thread carries to the merge of the slices
+    float m_keep = -INFINITY, l_keep = 0.f;
+    bool sm_ok = true;
 
     if (warp == 4) {
         // ---- producer: the whole warp ------------------------------------------------
@@ -281,7 +307,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             w.page = page;
         };
         Window wk, wv;
-        refill(wk, 0);
+        refill(wk, t_off * ppt);
         wv = wk;
         auto load = [&](unsigned char* dst, const CUtensorMap* map, void* full, int t, Window& w) {
             const int pi0 = t * ppt;
@@ -304,12 +330,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (t < n_tiles) {
                 const int b = t & 1;
                 if (t >= 2 && !mbar_wait(&k_empty[b], ((t - 2) >> 1) & 1)) { ok = false; break; }
-                load(k_s + b * K_BYTES, &map_k, &k_full[b], t, wk);
+                load(k_s + b * K_BYTES, &map_k, &k_full[b], t_off + t, wk);
             }
             if (t >= 1) {
                 const int tv = t - 1;
                 if (tv >= 1 && !mbar_wait(&v_empty, (tv - 1) & 1)) { ok = false; break; }
-                load(v_s, &map_v, &v_full, tv, wv);
+                load(v_s, &map_v, &v_full, t_off + tv, wv);
             }
         }
         if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_PRODUCER));
@@ -336,7 +362,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 umma_commit(&s_full[b]);
                 return true;
             };
-            if (ok) ok = issue_scores(0);
+            if (ok && n_tiles > 0) ok = issue_scores(0);
             for (int t = 0; t < n_tiles && ok; ++t) {
                 // The scores of tile t + 1 are computed while the softmax warps work on
                 // tile t.  Their buffer held tile t - 1, which the softmax warps read
@@ -376,7 +402,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tmem_ld64_wait(lane_addr + (t & 1) * BN, s);
             // The running maximum is kept in raw scores (the scale is positive); the
             // scale and the maximum enter the exponent in one multiply-add.
-            const int tile_start = t * BN;
+            const int tile_start = (t_off + t) * BN;
             float m_new = m_run;
             if (tile_start + BN - 1 > pos0 + r_begin || !valid) {
 #pragma unroll
@@ -447,34 +473,133 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_fence_after();
         }
         if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_SOFTMAX));
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        bf16* dst = valid ? p.out + (size_t)(row0 + r_begin + r) * p.out_stride + (size_t)(g * G + h) * HD : nullptr;
+        if (SPLIT) {
+            sm_ok = ok;
+            m_keep = m_run;
+            l_keep = l_run;
+        }
+        if (S == 1) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* dst = valid ? p.out + (size_t)(row0 + r_begin + r) * p.out_stride + (size_t)(g * G + h) * HD : nullptr;
 #pragma unroll
-        for (int c = 0; c < HD; c += 16) {
-            unsigned v[16];
-            tmem_ld16(lane_addr + O_COL + c, v);
-            tmem_ld_wait();
-            if (valid && ok) {
-                uint4 lo, hi;
-                __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+            for (int c = 0; c < HD; c += 16) {
+                unsigned v[16];
+                tmem_ld16(lane_addr + O_COL + c, v);
+                tmem_ld_wait();
+                if (valid && ok) {
+                    uint4 lo, hi;
+                    __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    l2[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]) * inv, __uint_as_float(v[2 * j + 1]) * inv);
-                    h2[j] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * j]) * inv,
-                                                  __uint_as_float(v[8 + 2 * j + 1]) * inv);
+                    for (int j = 0; j < 4; ++j) {
+                        l2[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]) * inv, __uint_as_float(v[2 * j + 1]) * inv);
+                        h2[j] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * j]) * inv,
+                                                      __uint_as_float(v[8 + 2 * j + 1]) * inv);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c) = lo;
+                    *reinterpret_cast<uint4*>(dst + c + 8) = hi;
                 }
-                *reinterpret_cast<uint4*>(dst + c) = lo;
-                *reinterpret_cast<uint4*>(dst + c + 8) = hi;
             }
+        } else if (rank != 0) {
+            // My slice's unnormalised output row, its reference maximum and its sum go to
+            // shared memory (the tiles are done with), value c of row m at [c][m] so that
+            // neither these stores nor the leader's loads meet in a bank.
+            float* mo = reinterpret_cast<float*>(smem);
+            float* mm = mo + HD * BM;
+#pragma unroll
+            for (int c = 0; c < HD; c += 16) {
+                unsigned v[16];
+                if (n_tiles > 0) {
+                    tmem_ld16(lane_addr + O_COL + c, v);
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) mo[(c + j) * BM + m] = n_tiles > 0 ? __uint_as_float(v[j]) : 0.f;
+            }
+            mm[m] = m_run;
+            mm[BM + m] = l_run;
         }
         tc_fence_before();
+    }
+    if (S > 1) {
+        // ---- merge of the slices: the leader adds the others' rows to its own ----------
+        cluster_sync_all();
+        if (warp < 4 && rank == 0) {
+            tc_fence_after();
+            const int m = threadIdx.x;
+            const int r = m / G, h = m % G;
+            const bool valid = r < r_count;
+            const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
+            const float* mo = reinterpret_cast<const float*>(smem);
+            const float* mm = mo + HD * BM;
+            float m_all = m_keep;
+            float m_peer[3], l_peer[3];
+            for (int q = 1; q < S; ++q) {
+                m_peer[q - 1] = ld_peer_smem(mm + m, (unsigned)q);
+                l_peer[q - 1] = ld_peer_smem(mm + BM + m, (unsigned)q);
+                m_all = fmaxf(m_all, m_peer[q - 1]);
+            }
+            // weights 2^((m_i - m_all) * scale); a slice that saw no key of this row weighs nothing
+            const float base = m_all == -INFINITY ? 0.f : m_all * p.scale_log2;
+            const float w0 = (n_tiles > 0 && m_keep > -INFINITY) ? fast_exp2(fmaf(m_keep, p.scale_log2, -base)) : 0.f;
+            float w[3], l_all = w0 * l_keep;
+            for (int q = 1; q < S; ++q) {
+                w[q - 1] = m_peer[q - 1] > -INFINITY ? fast_exp2(fmaf(m_peer[q - 1], p.scale_log2, -base)) : 0.f;
+                l_all += w[q - 1] * l_peer[q - 1];
+            }
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+            bf16* dst = valid ? p.out + (size_t)(row0 + r_begin + r) * p.out_stride + (size_t)(g * G + h) * HD : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 16) {
+                unsigned v[16];
+                float acc[16];
+                if (n_tiles > 0) {
+                    tmem_ld16(lane_addr + O_COL + c, v);
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] = n_tiles > 0 ? w0 * __uint_as_float(v[j]) : 0.f;
+                for (int q = 1; q < S; ++q) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[j] += w[q - 1] * ld_peer_smem(mo + (c + j) * BM + m, (unsigned)q);
+                }
+                if (valid && sm_ok) {
+                    uint4 lo, hi;
+                    __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        l2[j] = __floats2bfloat162_rn(acc[2 * j] * inv, acc[2 * j + 1] * inv);
+                        h2[j] = __floats2bfloat162_rn(acc[8 + 2 * j] * inv, acc[8 + 2 * j + 1] * inv);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c) = lo;
+                    *reinterpret_cast<uint4*>(dst + c + 8) = hi;
+                }
+            }
+            tc_fence_before();
+        }
+        cluster_sync_all();  // nobody leaves while the leader may still read its rows
     }
     __syncthreads();
     if (warp == 5) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
     }
+}
+
+// Left alone the compiler settles at 96 registers with spills, as if for three CTAs per
+// SM; shared memory allows two, so it may as well use the registers of two.
+__global__ void __maxnreg__(128)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+    attention_body<false>(map_q, map_k, map_v, p);
+}
+
+// two CTAs per SM still leave this one up to 170 registers per thread
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attention_tcgen05_split_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                               const __grid_constant__ CUtensorMap map_v, const Params p) {
+    attention_body<true>(map_q, map_k, map_v, p);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -499,16 +624,20 @@ EncodeTiledFn get_encode_fn() {
 IB_EXPORT int ib_attention_tc_head_dim() { return HD; }
 
 // Tile-mode attention for every entry with more rows than split mode takes.
+// `splits` (1, 2 or 4): the key tiles of a row tile are shared out over so many
+// CTAs of one cluster, which merge their results through distributed shared
+// memory; for prompt portions with a long cached prefix, whose row tiles alone
+// would leave most SMs idle.
 // Needs: bf16, head size 64 or 128, (heads / kv_heads) a divisor of 128,
 // page_size a multiple of 8 that divides 64, no window, 16-byte aligned q rows.
 IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, void* out,
                               int out_stride, const int* cu_rows, const int* q_start, const int* block_tables,
                               int max_blocks, int n_entries, int n_rows, int max_rows_per_entry, int nh, int nkv,
-                              int page_size, int num_pages, float scale, int small_rows, unsigned* err,
-                              void* stream) {
+                              int page_size, int num_pages, float scale, int small_rows, int splits,
+                              unsigned* err, void* stream) {
     if (n_entries <= 0 || n_rows <= 0) return IB_OK;
     if (!q || !k_pool || !v_pool || !out || !cu_rows || !q_start || !block_tables || !err) return IB_ERR_BAD_ARG;
-    if (nh <= 0 || nkv <= 0 || nh % nkv) return IB_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || (splits != 1 && splits != 2 && splits != 4)) return IB_ERR_BAD_ARG;
     const int G = nh / nkv;
     if (BM % G || page_size % 8 || BN % page_size || (q_stride % 8) || (out_stride % 8) ||
         ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
@@ -554,17 +683,40 @@ IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, c
     p.page_size = page_size;
     p.num_pages = num_pages;
     p.small_rows = small_rows;
+    p.splits = splits;
     p.scale_log2 = scale * 1.4426950408889634f;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e1 = cudaFuncSetAttribute(attention_tcgen05_kernel,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e1 != cudaSuccess) return (int)e1;
+        e1 = cudaFuncSetAttribute(attention_tcgen05_split_kernel,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e1 != cudaSuccess) return (int)e1;
         attr_done = true;
     }
-    dim3 grid((max_rows_per_entry + rq - 1) / rq, n_entries, nkv);
-    cudaError_t le = launch_kernel(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), (size_t)SMEM_BYTES,
-                                   (cudaStream_t)stream, mq, mk, mv, p);
+    dim3 grid(((max_rows_per_entry + rq - 1) / rq) * splits, n_entries, nkv);
+    cudaError_t le;
+    if (splits == 1) {
+        le = launch_kernel(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), (size_t)SMEM_BYTES,
+                           (cudaStream_t)stream, mq, mk, mv, p);
+    } else {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_flag() ? 2 : 1;
+        le = cudaLaunchKernelEx(&cfg, attention_tcgen05_split_kernel, mq, mk, mv, p);
+    }
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

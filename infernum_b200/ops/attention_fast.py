@@ -55,8 +55,8 @@ def tc_lib_for(head_dim: int) -> ctypes.CDLL:
         lib = load_module(f"attn_tc_hd{head_dim}", ["attention_tcgen05.cu"], [f"-DIB_HD={head_dim}"])
         lib.ib_attention_tc.argtypes = [
             _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
-            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
-            _c_void_p]
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+            _c_void_p, _c_void_p]
         lib.ib_attention_tc.restype = _c_int
         _tc_libs[head_dim] = lib
     return lib
@@ -94,6 +94,24 @@ def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count
     return max(1, min(8, slots // base, tiles))
 
 
+def choose_prompt_splits(rows, rows_per_cta: int, nkv: int, max_kv_len: int, rt) -> int:
+    """Into how many slices (1, 2 or 4 CTAs of one cluster) the prompt kernel
+    cuts the keys of a row tile.  A portion of a few hundred tokens after a
+    long cached prefix has few row tiles, each of which walks all the keys: 128
+    CTAs for 512 tokens of 32 heads take 82 us over 4,096 keys, as long as
+    1,024 tokens take.  Slices pay while the row tiles leave half of the CTA
+    slots (two per SM) idle and every slice keeps at least eight key tiles."""
+    if rows is None:
+        return 1
+    sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
+    ctas = sum(-(-r // rows_per_cta) for r in rows if r > 0) * nkv
+    tiles = -(-max_kv_len // 64)
+    for s in (4, 2):
+        if ctas * s <= 2 * sm and tiles >= 8 * s:
+            return s
+    return 1
+
+
 def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool:
     num_pages, nkv, page_size, hd = k_pool.shape
     if not supported(hd):
@@ -109,11 +127,11 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
     n_hsub = -(-G // gs)
     small_limit = 8 // gs  # rows an entry may have to go to split mode
     forced = getattr(ctx, "attention_mode", None)
+    cu = ctx.host_cu_rows
+    rows = [cu[i + 1] - cu[i] for i in range(ctx.n_entries)]
     if forced is not None:
         mode, splits = forced
     else:
-        cu = ctx.host_cu_rows
-        rows = [cu[i + 1] - cu[i] for i in range(ctx.n_entries)]
         any_small = any(r <= small_limit for r in rows)
         any_big = any(r > small_limit for r in rows)
         mode = (1 if any_big else 0) | (2 if any_small else 0)
@@ -129,8 +147,9 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
             q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
             out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
             tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
-            page_size, num_pages, float(scale), 8 if (mode & 2) else -1, rt.err.data_ptr(),
-            core.stream_ptr(q))
+            page_size, num_pages, float(scale), 8 if (mode & 2) else -1,
+            getattr(ctx, "prompt_splits", None) or choose_prompt_splits(rows, 128 // G, nkv, ctx.max_kv_len, rt),
+            rt.err.data_ptr(), core.stream_ptr(q))
         core.check(code, "attention_tcgen05")
         if not (mode & 2):
             return True

@@ -592,6 +592,39 @@ def test_attention_tcgen05_against_plain(case):
     assert rel_err(out, out2.double()) < 1e-2
 
 
+@pytest.mark.parametrize("splits", [2, 4])
+@pytest.mark.parametrize("nh, nkv, hd, ps, lens, rows", [
+    (8, 2, 128, 16, [1500, 700], [200, 130]),     # portions after long cached prefixes
+    (8, 2, 128, 16, [257, 64, 100], [257, 64, 3]),  # whole prompts, fewer key tiles than slices, a short entry
+    (4, 4, 64, 8, [900], [77]),                     # head size 64, pages of 8
+    (32, 1, 128, 64, [640, 2000], [9, 300]),        # G = 32, pages of 64
+])
+def test_attention_tcgen05_with_key_slices(nh, nkv, hd, ps, lens, rows, splits):
+    """The keys of a row tile shared out over 2 or 4 CTAs of a cluster and merged
+    through distributed shared memory: the result is that of one CTA, also when a
+    slice gets no key tile at all, and one key that carries the answer is found
+    in whichever slice it lies."""
+    from infernum_b200.ops import attention_fast
+    from infernum_b200.parts.base import Runtime
+    c = core()
+    for far in (None, 0, 33, -1):
+        q, kp, vp, tables, ctx, refs = paged_case(lens, rows, nh, nkv, hd, ps, torch.bfloat16, 17,
+                                                  scale_key=far)
+        wide = torch.zeros(q.shape[0], (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device=DEV)
+        wide[:, : nh * hd] = q
+        outs = []
+        for s in (1, splits):
+            ctx.prompt_splits = s
+            rt = Runtime(torch.device(DEV), torch.bfloat16, err=c.new_error_word(DEV))
+            out = torch.full((q.shape[0], nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+            assert attention_fast.run(wide, kp, vp, out, ctx, tables, nh, 1 / math.sqrt(hd), 0, rt)
+            assert rt.err.item() == 0 and torch.isfinite(out).all()
+            assert rel_err(out, plain_result(refs)) < 1e-2, (far, s)
+            outs.append(out)
+        # both are rounded to bfloat16: one unit in the last place of the largest value apart at most
+        assert rel_err(outs[1], outs[0].double()) < 2 ** -7, far
+
+
 def test_attention_tcgen05_far_key_and_edges():
     """One key carries the answer, at tile and page edges of a long prompt."""
     from infernum_b200.ops import attention_fast
