@@ -66,6 +66,7 @@ struct Params {
     int out_stride, max_blocks, nh, nkv, page_size, num_pages;
     int small_rows;     // entries with rows * min(group, 8) <= small_rows belong to split mode
     int splits;         // CTAs (one cluster) that share the keys of a row tile: 1, 2 or 4
+    int entry_offset;   // the grid's y starts at this entry (those before it are all split mode's)
     float scale_log2;
 };
 
@@ -230,7 +231,7 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.y, g = blockIdx.z;
+    const int e = blockIdx.y + p.entry_offset, g = blockIdx.z;
     const int G = p.nh / p.nkv;
     const int rq = BM / G;  // query rows per CTA
     const int row0 = p.cu_rows[e];
@@ -627,17 +628,20 @@ IB_EXPORT int ib_attention_tc_head_dim() { return HD; }
 // `splits` (1, 2 or 4): the key tiles of a row tile are shared out over so many
 // CTAs of one cluster, which merge their results through distributed shared
 // memory; for prompt portions with a long cached prefix, whose row tiles alone
-// would leave most SMs idle.
+// would leave most SMs idle.  `entry_offset`: the first entry the grid covers (a
+// step lists its decoded tokens first; no CTA is launched for them here).
 // Needs: bf16, head size 64 or 128, (heads / kv_heads) a divisor of 128,
 // page_size a multiple of 8 that divides 64, no window, 16-byte aligned q rows.
 IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, void* out,
                               int out_stride, const int* cu_rows, const int* q_start, const int* block_tables,
                               int max_blocks, int n_entries, int n_rows, int max_rows_per_entry, int nh, int nkv,
                               int page_size, int num_pages, float scale, int small_rows, int splits,
-                              unsigned* err, void* stream) {
+                              int entry_offset, unsigned* err, void* stream) {
     if (n_entries <= 0 || n_rows <= 0) return IB_OK;
     if (!q || !k_pool || !v_pool || !out || !cu_rows || !q_start || !block_tables || !err) return IB_ERR_BAD_ARG;
-    if (nh <= 0 || nkv <= 0 || nh % nkv || (splits != 1 && splits != 2 && splits != 4)) return IB_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || (splits != 1 && splits != 2 && splits != 4) || entry_offset < 0 ||
+        entry_offset >= n_entries)
+        return IB_ERR_BAD_ARG;
     const int G = nh / nkv;
     if (BM % G || page_size % 8 || BN % page_size || (q_stride % 8) || (out_stride % 8) ||
         ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
@@ -684,6 +688,7 @@ IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, c
     p.num_pages = num_pages;
     p.small_rows = small_rows;
     p.splits = splits;
+    p.entry_offset = entry_offset;
     p.scale_log2 = scale * 1.4426950408889634f;
     static bool attr_done = false;
     if (!attr_done) {
@@ -695,7 +700,7 @@ IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, c
         if (e1 != cudaSuccess) return (int)e1;
         attr_done = true;
     }
-    dim3 grid(((max_rows_per_entry + rq - 1) / rq) * splits, n_entries, nkv);
+    dim3 grid(((max_rows_per_entry + rq - 1) / rq) * splits, n_entries - entry_offset, nkv);
     cudaError_t le;
     if (splits == 1) {
         le = launch_kernel(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), (size_t)SMEM_BYTES,

@@ -55,7 +55,7 @@ def tc_lib_for(head_dim: int) -> ctypes.CDLL:
         lib = load_module(f"attn_tc_hd{head_dim}", ["attention_tcgen05.cu"], [f"-DIB_HD={head_dim}"])
         lib.ib_attention_tc.argtypes = [
             _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
-            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
             _c_void_p, _c_void_p]
         lib.ib_attention_tc.restype = _c_int
         _tc_libs[head_dim] = lib
@@ -94,7 +94,7 @@ def choose_splits(n_entries: int, kv_heads_x_sub: int, max_kv_len: int, sm_count
     return max(1, min(8, slots // base, tiles))
 
 
-def choose_prompt_splits(rows, rows_per_cta: int, nkv: int, max_kv_len: int, rt) -> int:
+def choose_prompt_splits(rows, rows_per_cta: int, nkv: int, max_kv_len: int, rt, small_limit: int = 0) -> int:
     """Into how many slices (1, 2 or 4 CTAs of one cluster) the prompt kernel
     cuts the keys of a row tile.  A portion of a few hundred tokens after a
     long cached prefix has few row tiles, each of which walks all the keys: 128
@@ -104,7 +104,8 @@ def choose_prompt_splits(rows, rows_per_cta: int, nkv: int, max_kv_len: int, rt)
     if rows is None:
         return 1
     sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
-    ctas = sum(-(-r // rows_per_cta) for r in rows if r > 0) * nkv
+    # (entries of at most small_limit rows are decoded tokens: another kernel takes them)
+    ctas = sum(-(-r // rows_per_cta) for r in rows if r > small_limit) * nkv
     tiles = -(-max_kv_len // 64)
     for s in (4, 2):
         if ctas * s <= 2 * sm and tiles >= 8 * s:
@@ -148,7 +149,10 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
             out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
             tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
             page_size, num_pages, float(scale), 8 if (mode & 2) else -1,
-            getattr(ctx, "prompt_splits", None) or choose_prompt_splits(rows, 128 // G, nkv, ctx.max_kv_len, rt),
+            getattr(ctx, "prompt_splits", None) or choose_prompt_splits(rows, 128 // G, nkv, ctx.max_kv_len, rt,
+                                                                           small_limit if (mode & 2) else 0),
+            # decoded tokens come first in a step: the grid starts at the first longer entry
+            next((i for i, r in enumerate(rows) if r > small_limit), 0) if (mode & 2) else 0,
             rt.err.data_ptr(), core.stream_ptr(q))
         core.check(code, "attention_tcgen05")
         if not (mode & 2):
