@@ -321,3 +321,51 @@ def test_no_plan_ahead_when_a_request_is_about_to_reach_its_limit_or_pages_are_s
     sched.commit(plan, commit_cache=True)
     assert sched.plan_decode_ahead() is None  # token 9 would need a fifth page
     cache.check_invariants()
+
+
+def test_planning_ahead_under_random_arrivals_ends_and_tight_pages():
+    """The engine's way of driving the scheduler - plan the next decode step while
+    one is in flight, use the plan if it still holds - under random prompt
+    lengths, arrivals between steps, end-of-sequence tokens and so few pages
+    that requests are preempted: every request gets the tokens it gets alone,
+    no page is lost, and plans made ahead are both used and voided."""
+    import random
+    rng = random.Random(11)
+    sched, cache = make(num_blocks=48, block_size=4, max_batch=5, chunk=9, budget=20, max_len=200)
+    pending = [([rng.randrange(3, 90) for _ in range(rng.randint(1, 40))], rng.randint(1, 25)) for _ in range(30)]
+    expect, seqs = [], []
+    used = voided = 0
+    ahead = None
+    steps = 0
+    while pending or sched.has_work():
+        steps += 1
+        assert steps < 5000
+        if pending and rng.random() < 0.3:
+            p, n = pending.pop()
+            want = solo_tokens(p, n)
+            eos = want[len(want) // 2] if (len(want) > 3 and rng.random() < 0.4) else None
+            seqs.append(sched.add_request(p, GenerateOptions(max_new_tokens=n, eos_token_id=eos)))
+            expect.append(want if eos is None else want[: want.index(eos)])
+        plan = None
+        if ahead is not None:
+            if sched.ahead_still_holds(ahead):
+                plan, used = ahead, used + 1
+            else:
+                voided += 1
+            ahead = None
+        if plan is None:
+            plan = sched.schedule()
+        cache.check_invariants()
+        for p in plan.portions:
+            assert p.tokens == p.seq.tokens[p.seq.num_computed: p.seq.num_computed + p.count]
+        sched.commit(plan, commit_cache=True)
+        if plan.portions and all(p.count == 1 and p.wants_logits for p in plan.portions):
+            ahead = sched.plan_decode_ahead()  # before the tokens of `plan` are appended
+            cache.check_invariants()
+        for p in plan.portions:
+            if p.wants_logits:
+                sched.append_token(p.seq, fake_token(p.seq))
+    sched.schedule()
+    cache.check_invariants()
+    assert [s.generated_ids for s in seqs] == expect
+    assert cache.free_pages() == [48] and used > 5 and voided > 3
