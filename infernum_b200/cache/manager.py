@@ -63,6 +63,17 @@ class RequestCache:
     reserved_tokens: int = 0  # tokens that pages are held for (>= num_tokens)
     tables: List[List[int]] = field(default_factory=list)  # per group; -1 = given back
     released: bool = False
+    version: int = 0  # counts changes of the tables (the manager bumps it)
+    _arrays: Optional[tuple] = None  # (version, the tables as int32 arrays)
+
+    def table_arrays(self):
+        """The block tables as numpy int32 arrays, rebuilt only after a change
+        (a step copies them into its upload buffer)."""
+        import numpy as np
+
+        if self._arrays is None or self._arrays[0] != self.version:
+            self._arrays = (self.version, [np.asarray(t, dtype=np.int32) for t in self.tables])
+        return self._arrays[1]
 
 
 class CacheManager:
@@ -187,7 +198,9 @@ class CacheManager:
                 raise OutOfPagesError(
                     f"request {rc.request_id!r} needs {n} more pages, {g.pool.num_free} are free")
         for n, g, table in zip(need, self.groups, rc.tables):
-            table.extend(g.pool.allocate_many(n))
+            if n:
+                table.extend(g.pool.allocate_many(n))
+                rc.version += 1
         rc.reserved_tokens += new_tokens
 
     def commit(self, rc: RequestCache, new_tokens: int) -> None:
@@ -209,6 +222,7 @@ class CacheManager:
                 if table[i] >= 0:
                     g.pool.free(table[i])
                     table[i] = -1
+                    rc.version += 1
                 i += 1
 
     def cancel_reservation(self, rc: RequestCache) -> None:
@@ -221,6 +235,7 @@ class CacheManager:
                 if page >= 0:
                     g.pool.free(page)
         rc.reserved_tokens = rc.num_tokens
+        rc.version += 1
 
     def release(self, rc: RequestCache) -> None:
         """The request ended (or is preempted): pages and slot go back."""
@@ -232,6 +247,7 @@ class CacheManager:
             table.clear()
         self._free_slots.append(rc.slot)
         rc.released = True
+        rc.version += 1
         rc.num_tokens = rc.reserved_tokens = 0
         del self._requests[rc.request_id]
 

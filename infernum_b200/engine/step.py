@@ -23,6 +23,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, RequestCache
@@ -80,8 +81,39 @@ class ModelRunner:
         self.steps_run = 0
         self.rows_run = 0
         self.last_upload_bytes = 0
+        # pinned staging buffers for the step inputs, used in turn; each carries the
+        # event of its last upload, which is waited for before the buffer is written again
+        self._staging: List[list] = []
+        self._staging_next = 0
 
     # ---- building the inputs -------------------------------------------------
+    STAGING_BUFFERS = 4
+
+    def _upload_buffer(self, n: int):
+        """A pinned int32 buffer of at least ``n`` values (tensor and numpy view)
+        whose last upload has completed."""
+        if len(self._staging) < self.STAGING_BUFFERS:
+            self._staging.append([None, None, None])
+            self._staging_next = len(self._staging) - 1
+        else:
+            self._staging_next = (self._staging_next + 1) % self.STAGING_BUFFERS
+        slot = self._staging[self._staging_next]
+        if slot[2] is not None:
+            slot[2].synchronize()
+        if slot[0] is None or slot[0].numel() < n:
+            t = torch.empty(max(n, 4096) * 2, dtype=torch.int32)
+            if self.device.type == "cuda":
+                t = t.pin_memory()
+            slot[0], slot[1] = t, t.numpy()
+        return slot[0], slot[1]
+
+    def _mark_uploaded(self) -> None:
+        if self.device.type == "cuda":
+            slot = self._staging[self._staging_next]
+            if slot[2] is None:
+                slot[2] = torch.cuda.Event()
+            slot[2].record()
+
     def _build(self, entries: Sequence[StepEntry]) -> StepContext:
         E = len(entries)
         if E == 0:
@@ -89,27 +121,17 @@ class ModelRunner:
         if E > self.max_entries:
             raise SchedulingError(f"{E} entries in one step, the limit is {self.max_entries}")
         n_groups = len(self.cache.groups)
-        tokens: List[int] = []
-        positions: List[int] = []
-        row_entry: List[int] = []
+        counts = [len(ent.tokens) for ent in entries]
         cu_rows = [0]
         q_start, kv_len, slots, logit_rows = [], [], [], []
-        for e, ent in enumerate(entries):
-            n = len(ent.tokens)
+        for e, (ent, n) in enumerate(zip(entries, counts)):
             if n == 0:
                 raise SchedulingError(f"entry {e} brings no tokens")
             start = ent.cache.num_tokens
             if ent.cache.reserved_tokens < start + n:
                 raise SchedulingError(f"entry {e}: pages are held for {ent.cache.reserved_tokens} "
                                       f"tokens, the step reaches {start + n}")
-            for t in ent.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise SchedulingError(f"token id {t} is outside the vocabulary "
-                                          f"of {self.vocab_size}")
             base = cu_rows[-1]
-            tokens.extend(int(t) for t in ent.tokens)
-            positions.extend(range(start, start + n))
-            row_entry.extend([e] * n)
             cu_rows.append(base + n)
             q_start.append(start)
             kv_len.append(start + n)
@@ -122,25 +144,47 @@ class ModelRunner:
         if N > self.max_rows:
             raise SchedulingError(f"{N} tokens in one step, the limit is {self.max_rows}")
         MB = max(1, max(self.cache.pages_for(k) for k in kv_len))
-        tables_flat: List[int] = []
-        for g in range(n_groups):
-            for ent in entries:
-                t = ent.cache.tables[g]
-                row = t[:MB] + [-1] * (MB - len(t))
-                tables_flat.extend(row)
         R = len(logit_rows)
-        pieces = [tokens, positions, row_entry, cu_rows, q_start, kv_len, slots, logit_rows,
-                  tables_flat]
-        sizes = [len(p) for p in pieces]
-        host = torch.tensor([v for p in pieces for v in p], dtype=torch.int32)
-        if self.device.type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(self.device, non_blocking=True)
-        self.last_upload_bytes = host.numel() * 4
-        views, off = [], 0
-        for s in sizes:
-            views.append(dev[off: off + s])
-            off += s
+        # one int32 buffer: tokens | positions | row_entry | cu_rows | q_start | kv_len | slots |
+        # logit_rows | block tables, filled through numpy in pinned memory and uploaded in one copy
+        sizes = [N, N, N, E + 1, E, E, E, R, n_groups * E * MB]
+        total = sum(sizes)
+        host_t, host = self._upload_buffer(total)
+        offs = [0]
+        for sz in sizes:
+            offs.append(offs[-1] + sz)
+        tok = host[offs[0]: offs[1]]
+        pos = host[offs[1]: offs[2]]
+        rowe = host[offs[2]: offs[3]]
+        for e, (ent, n) in enumerate(zip(entries, counts)):
+            lo, hi = cu_rows[e], cu_rows[e + 1]
+            try:
+                tok[lo:hi] = ent.tokens
+            except (OverflowError, ValueError, TypeError) as exc:
+                raise SchedulingError(f"entry {e}: token ids must be integers inside the vocabulary "
+                                      f"of {self.vocab_size} ({exc})") from None
+            pos[lo:hi] = np.arange(q_start[e], q_start[e] + n, dtype=np.int32)
+            rowe[lo:hi] = e
+        if N and (int(tok.min()) < 0 or int(tok.max()) >= self.vocab_size):
+            bad = int(tok[(tok < 0) | (tok >= self.vocab_size)][0])
+            raise SchedulingError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+        host[offs[3]: offs[4]] = cu_rows
+        host[offs[4]: offs[5]] = q_start
+        host[offs[5]: offs[6]] = kv_len
+        host[offs[6]: offs[7]] = slots
+        host[offs[7]: offs[8]] = logit_rows
+        tab = host[offs[8]: offs[9]].reshape(n_groups, E, MB) if n_groups else None
+        if n_groups:
+            tab.fill(-1)
+            for e, ent in enumerate(entries):
+                for g, t in enumerate(ent.cache.table_arrays()):
+                    k = min(len(t), MB)
+                    tab[g, e, :k] = t[:k]
+        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        dev.copy_(host_t[:total], non_blocking=True)
+        self._mark_uploaded()
+        self.last_upload_bytes = total * 4
+        views = [dev[offs[i]: offs[i + 1]] for i in range(9)]
         tables = [views[8][g * E * MB: (g + 1) * E * MB].view(E, MB) for g in range(n_groups)]
         return StepContext(
             n_rows=N, n_entries=E, token_ids=views[0], positions=views[1], row_entry=views[2],

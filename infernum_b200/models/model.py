@@ -89,12 +89,13 @@ class Model:
         [wanted rows, vocab], or None when no row is wanted."""
         if not self.bound:
             raise ConfigError("the model has no weights bound")
-        # nothing of this step starts before what describes it (positions, tables) is complete
-        core.step_fence(self.rt.device)
-        stream = ResidualStream(self.embedding.forward(ctx.token_ids))
-        for item, cache in zip(self.schedule, caches):
-            self.layers[item.layer].forward(stream, ctx, cache)
-        if ctx.logit_rows is None or ctx.logit_rows.numel() == 0:
-            return None
-        normed = self.final_norm.forward(stream, row_idx=ctx.logit_rows)
-        return self.head.forward(normed)
+        with core.step_stream(self.rt.device):
+            # nothing of this step starts before what describes it (positions, tables) is complete
+            core.step_fence(self.rt.device)
+            stream = ResidualStream(self.embedding.forward(ctx.token_ids))
+            for item, cache in zip(self.schedule, caches):
+                self.layers[item.layer].forward(stream, ctx, cache)
+            if ctx.logit_rows is None or ctx.logit_rows.numel() == 0:
+                return None
+            normed = self.final_norm.forward(stream, row_idx=ctx.logit_rows)
+            return self.head.forward(normed)

@@ -91,8 +91,33 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
 
 
+_step_stream: Optional[int] = None  # the stream of the step being launched, looked up once per step
+
+
 def stream_ptr(t: torch.Tensor) -> int:
+    if _step_stream is not None:
+        return _step_stream
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class step_stream:
+    """While a model step is being launched, every kernel goes to the stream that
+    was current at its start; looking it up for each launch costs as much as a
+    small launch itself."""
+
+    def __init__(self, device):
+        self.device = device
+
+    def __enter__(self):
+        global _step_stream
+        self.previous = _step_stream
+        _step_stream = torch.cuda.current_stream(self.device).cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _step_stream
+        _step_stream = self.previous
+        return False
 
 
 LAUNCHES = 0  # kernels of this package launched so far (benchmarks report the count)
