@@ -113,6 +113,45 @@ def choose_prompt_splits(rows, rows_per_cta: int, nkv: int, max_kv_len: int, rt,
     return 1
 
 
+def _step_plan(ctx, G: int, nkv: int, tc_ok: bool, rt) -> dict:
+    """How the entries of this step are spread over the kernels.  It depends on
+    the step and on the layer's head grouping only, so it is worked out once per
+    step (kept in ``ctx.scratch``), not once per layer."""
+    key = ("attention_plan", G, nkv, tc_ok, getattr(ctx, "prompt_splits", None), getattr(ctx, "attention_mode", None))
+    plan = ctx.scratch.get(key)
+    if plan is not None:
+        return plan
+    gs = min(G, 8)  # split mode packs rows x grouped heads on the 8-wide side of the MMA
+    n_hsub = -(-G // gs)
+    small_limit = 8 // gs  # rows an entry may have to go to split mode
+    sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
+    cu = ctx.host_cu_rows
+    rows = [cu[i + 1] - cu[i] for i in range(ctx.n_entries)]
+    forced = getattr(ctx, "attention_mode", None)
+    if forced is not None:
+        mode, splits = forced
+    else:
+        any_small = any(r <= small_limit for r in rows)
+        any_big = any(r > small_limit for r in rows)
+        mode = (1 if any_big else 0) | (2 if any_small else 0)
+        splits = choose_splits(ctx.n_entries, nkv * n_hsub, ctx.max_kv_len, sm) if mode == 2 else 1
+    plan = {"mode": mode, "splits": splits, "prompt_splits": 1, "first_prompt_entry": 0,
+            "splits_beside_prompts": splits}
+    if (mode & 1) and tc_ok:
+        beside = bool(mode & 2)
+        plan["prompt_splits"] = getattr(ctx, "prompt_splits", None) or choose_prompt_splits(
+            rows, 128 // G, nkv, ctx.max_kv_len, rt, small_limit if beside else 0)
+        # decoded tokens come first in a step: the prompt kernel's grid starts at the first longer entry
+        plan["first_prompt_entry"] = next((i for i, r in enumerate(rows) if r > small_limit), 0) if beside else 0
+        if beside and forced is None:
+            # the decoded tokens beside prompts are sliced as in a step of their own: a single
+            # CTA per request and kv head would walk a long context tile by tile
+            n_small = sum(1 for r in rows if r <= small_limit)
+            plan["splits_beside_prompts"] = min(8, choose_splits(n_small, nkv * n_hsub, ctx.max_kv_len, sm))
+    ctx.scratch[key] = plan
+    return plan
+
+
 def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool:
     num_pages, nkv, page_size, hd = k_pool.shape
     if not supported(hd):
@@ -124,46 +163,23 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool
             or k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_mma: bfloat16 tensors with unit inner stride are required")
     G = n_heads // nkv
-    gs = min(G, 8)  # split mode packs rows x grouped heads on the 8-wide side of the MMA
-    n_hsub = -(-G // gs)
-    small_limit = 8 // gs  # rows an entry may have to go to split mode
-    forced = getattr(ctx, "attention_mode", None)
-    cu = ctx.host_cu_rows
-    rows = [cu[i + 1] - cu[i] for i in range(ctx.n_entries)]
-    if forced is not None:
-        mode, splits = forced
-    else:
-        any_small = any(r <= small_limit for r in rows)
-        any_big = any(r > small_limit for r in rows)
-        mode = (1 if any_big else 0) | (2 if any_small else 0)
-        splits = 1
-        if mode == 2:
-            sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
-            splits = choose_splits(ctx.n_entries, nkv * n_hsub, ctx.max_kv_len, sm)
-    if (mode & 1) and rt.options.get("prompt_attention", "tcgen05") == "tcgen05" \
-            and tc_eligible(q, k_pool, out, n_heads, window):
+    tc_ok = rt.options.get("prompt_attention", "tcgen05") == "tcgen05" and tc_eligible(q, k_pool, out, n_heads, window)
+    plan = _step_plan(ctx, G, nkv, tc_ok, rt)
+    mode, splits = plan["mode"], plan["splits"]
+    if (mode & 1) and tc_ok:
         # prompt portions on the tcgen05 kernel; what is left (decoded tokens and
         # very short portions in the same step) goes to split mode below
         code = tc_lib_for(hd).ib_attention_tc(
             q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
             out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
             tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
-            page_size, num_pages, float(scale), 8 if (mode & 2) else -1,
-            getattr(ctx, "prompt_splits", None) or choose_prompt_splits(rows, 128 // G, nkv, ctx.max_kv_len, rt,
-                                                                           small_limit if (mode & 2) else 0),
-            # decoded tokens come first in a step: the grid starts at the first longer entry
-            next((i for i, r in enumerate(rows) if r > small_limit), 0) if (mode & 2) else 0,
-            rt.err.data_ptr(), core.stream_ptr(q))
+            page_size, num_pages, float(scale), 8 if (mode & 2) else -1, plan["prompt_splits"],
+            plan["first_prompt_entry"], rt.err.data_ptr(), core.stream_ptr(q))
         core.check(code, "attention_tcgen05")
         if not (mode & 2):
             return True
         mode = 2 | 4  # split mode for the small entries only; the others are done
-        if forced is None:
-            # they are sliced as in a step of decoded tokens alone: a single CTA per
-            # request and kv head would walk a long context tile by tile
-            n_small = sum(1 for r in rows if r <= small_limit)
-            sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
-            splits = min(8, choose_splits(n_small, nkv * n_hsub, ctx.max_kv_len, sm))
+        splits = plan["splits_beside_prompts"]
     if rt.options.get("split_copy", "tma") != "tma":
         mode |= 8  # keys and values by cp.async also where TMA could fetch them
     lib = lib_for(hd)
