@@ -60,6 +60,7 @@ class _Slot:
     ctx: StepContext
     rows: List[Optional[Tuple[object, List[int]]]] = field(default_factory=list)  # who sits where
     host_np: object = None  # host_ints' memory as a numpy array (cheap to fill from lists)
+    portion: int = 0  # rows of the prompt portion that rides along (0: decoded tokens only)
     uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
     prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
     result: Optional[torch.Tensor] = None  # device [size + 1]: the selected tokens, then the error word
@@ -97,25 +98,44 @@ class DecodeRunner:
         slot = self._slots.get(key)
         if slot is not None:
             return slot
-        size, kv_cap, sampling, _feed = key
+        size, kv_cap, sampling, _feed, portion = key
         dev = self.rt.device
         G = len(self.cache.groups)
-        ints = torch.zeros((4, size), dtype=torch.int32, device=dev)
-        tables = torch.full((G, size, self.MB), -1, dtype=torch.int32, device=dev)
         arange = torch.arange(size + 1, dtype=torch.int32, device=dev)
-        kv_heads = max([g.spec.kv_heads for g in self.cache.groups] + [1])
-        sm = self.rt.options.get("sm_count") or SM_COUNT_FALLBACK
-        ctx = StepContext(
-            n_rows=size, n_entries=size, token_ids=ints[0], positions=ints[1], row_entry=arange[:size],
-            cu_rows=arange, q_start=ints[1], kv_len=ints[2], slot_ids=ints[3], logit_rows=arange[:size],
-            block_tables=[tables[g] for g in range(G)], host_cu_rows=list(range(size + 1)),
-            host_kv_len=[], max_rows_per_entry=1, max_kv_len=kv_cap, all_decode=True)
-        ctx.attention_mode = (2, choose_splits(size, kv_heads, kv_cap, sm))
-        slot = _Slot(size=size, ints=ints, host_ints=torch.zeros((4, size), dtype=torch.int32).pin_memory(),
-                     tables=tables,
-                     host_tables=torch.full((G, size, self.MB), -1, dtype=torch.int32).pin_memory(),
+        if portion == 0:
+            ints = torch.zeros((4, size), dtype=torch.int32, device=dev)
+            host_ints = torch.zeros((4, size), dtype=torch.int32).pin_memory()
+            tables = torch.full((G, size, self.MB), -1, dtype=torch.int32, device=dev)
+            kv_heads = max([g.spec.kv_heads for g in self.cache.groups] + [1])
+            sm = self.rt.options.get("sm_count") or SM_COUNT_FALLBACK
+            ctx = StepContext(
+                n_rows=size, n_entries=size, token_ids=ints[0], positions=ints[1], row_entry=arange[:size],
+                cu_rows=arange, q_start=ints[1], kv_len=ints[2], slot_ids=ints[3], logit_rows=arange[:size],
+                block_tables=[tables[g] for g in range(G)], host_cu_rows=list(range(size + 1)),
+                host_kv_len=[], max_rows_per_entry=1, max_kv_len=kv_cap, all_decode=True)
+            ctx.attention_mode = (2, choose_splits(size, kv_heads, kv_cap, sm))
+        else:
+            # `size` decoded tokens (one row and one entry each), then one prompt portion of
+            # `portion` rows as the last entry.  One flat buffer holds what changes from step
+            # to step: tokens | positions (a row each) | q_start | kv_len | slots (an entry each).
+            rows, entries = size + portion, size + 1
+            ints = torch.zeros(2 * rows + 3 * entries, dtype=torch.int32, device=dev)
+            host_ints = torch.zeros(2 * rows + 3 * entries, dtype=torch.int32).pin_memory()
+            tables = torch.full((G, entries, self.MB), -1, dtype=torch.int32, device=dev)
+            row_entry = torch.cat([arange[:size], torch.full((portion,), size, dtype=torch.int32, device=dev)])
+            cu_rows = torch.cat([arange, torch.tensor([rows], dtype=torch.int32, device=dev)])
+            e0 = 2 * rows
+            ctx = StepContext(
+                n_rows=rows, n_entries=entries, token_ids=ints[:rows], positions=ints[rows: 2 * rows],
+                row_entry=row_entry, cu_rows=cu_rows, q_start=ints[e0: e0 + entries],
+                kv_len=ints[e0 + entries: e0 + 2 * entries], slot_ids=ints[e0 + 2 * entries: e0 + 3 * entries],
+                logit_rows=arange[:size], block_tables=[tables[g] for g in range(G)],
+                host_cu_rows=list(range(size + 1)) + [rows], host_kv_len=[], max_rows_per_entry=portion,
+                max_kv_len=kv_cap, all_decode=False)
+        slot = _Slot(size=size, ints=ints, host_ints=host_ints, tables=tables,
+                     host_tables=torch.full(tuple(tables.shape), -1, dtype=torch.int32).pin_memory(),
                      selected=torch.zeros(size, dtype=torch.int32, device=dev), ctx=ctx,
-                     rows=[None] * size)
+                     rows=[None] * tables.shape[1], portion=portion)
         slot.host_np = slot.host_ints.numpy()
         slot.result = torch.zeros(size + 1, dtype=torch.int32, device=dev)
         slot.host_result = torch.zeros(size + 1, dtype=torch.int32).pin_memory()
@@ -136,7 +156,7 @@ class DecodeRunner:
         changed = False
         pads = self.cache.pad_pages()
         windowed = [g.spec.window > 0 for g in self.cache.groups]
-        for r in range(slot.size):
+        for r in range(len(slot.rows)):
             rc = caches[r] if r < len(caches) else None
             who = rc.request_id if rc is not None else None
             prev = slot.rows[r]
@@ -192,14 +212,20 @@ class DecodeRunner:
             slot.launches_per_step = core.LAUNCHES - before
             slot.eager_steps += 1
 
-    def _key(self, caches: Sequence[RequestCache], sampling: bool, feed: str, ahead: int = 1) -> tuple:
+    def _key(self, caches: Sequence[RequestCache], sampling: bool, feed: str, ahead: int = 1,
+             portion: Optional[Tuple[RequestCache, int]] = None) -> tuple:
         longest = max(rc.num_tokens for rc in caches) + ahead
+        if portion is not None:
+            longest = max(longest, portion[0].num_tokens + portion[1])
         kv_cap = 256
         while kv_cap < longest:
             kv_cap *= 2
-        return (bucket_for(len(caches)), kv_cap, bool(sampling), feed)
+        return (bucket_for(len(caches)), kv_cap, bool(sampling), feed, portion[1] if portion else 0)
 
-    def can_take(self, caches: Sequence[RequestCache]) -> bool:
+    def can_take(self, caches: Sequence[RequestCache],
+                 portion: Optional[Tuple[RequestCache, int]] = None) -> bool:
+        if portion is not None and self.cache.pages_for(portion[0].num_tokens + portion[1]) > self.MB:
+            return False
         return all(self.cache.pages_for(rc.num_tokens + 1) <= self.MB for rc in caches)
 
     # ---- fed from the host ---------------------------------------------------------------
@@ -211,15 +237,41 @@ class DecodeRunner:
         selected token ids, int32 [len(caches)] on the device."""
         return self.launch(self.prepare(caches, sample is not None), caches, tokens, sample)
 
-    def prepare(self, caches: Sequence[RequestCache], sampling: bool) -> _Slot:
+    def prepare(self, caches: Sequence[RequestCache], sampling: bool,
+                portion: Optional[Tuple[RequestCache, int]] = None) -> _Slot:
         """The part of a step that does not need the input tokens: picks the
         buffers, fills positions, slots and block tables.  It may run while the
-        step before is still on the GPU (its uploads are waited for first)."""
+        step before is still on the GPU (its uploads are waited for first).
+        ``portion``: (request, rows) of one prompt portion that rides along with
+        the decoded tokens, continuing its request where the cache ends; such a
+        step is recorded per (bucket, rows of the portion, cache-length class)."""
         B = len(caches)
-        slot = self._slot(self._key(caches, sampling, "host"))
+        slot = self._slot(self._key(caches, sampling, "host", portion=portion))
         if slot.uploaded is not None:
             slot.uploaded.synchronize()  # the pinned mirrors are free to be written again
         pad = slot.size - B
+        if portion is not None:
+            prc, P = portion
+            size, rows, entries = slot.size, slot.size + P, slot.size + 1
+            hn = slot.host_np
+            pos, q0 = hn[rows: 2 * rows], hn[2 * rows: 2 * rows + entries]
+            kv, sl = hn[2 * rows + entries: 2 * rows + 2 * entries], hn[2 * rows + 2 * entries:]
+            q0[:B] = [rc.num_tokens for rc in caches]
+            sl[:B] = [rc.slot for rc in caches]
+            if pad:
+                hn[B:size] = 0
+                q0[B:size] = 0
+                sl[B:size] = self.cache.pad_slot
+            pos[:size] = q0[:size]
+            kv[:size] = q0[:size] + 1
+            start = prc.num_tokens
+            pos[size:] = range(start, start + P)
+            q0[size], kv[size], sl[size] = start, start + P, prc.slot
+            padded = list(caches) + [None] * pad + [prc]
+            if self._fill_tables(slot, padded):
+                slot.tables.copy_(slot.host_tables, non_blocking=True)
+            slot.prepared_for = tuple(rc.request_id for rc in caches) + (prc.request_id,)
+            return slot
         hn = slot.host_np
         hn[1, :B] = [rc.num_tokens for rc in caches]
         hn[3, :B] = [rc.slot for rc in caches]
@@ -234,14 +286,21 @@ class DecodeRunner:
         return slot
 
     def launch(self, slot: _Slot, caches: Sequence[RequestCache], tokens: Sequence[int],
-               sample: Optional[tuple] = None) -> torch.Tensor:
-        """Uploads the tokens (and sampling rows) and runs the prepared step."""
+               sample: Optional[tuple] = None,
+               portion: Optional[Tuple[RequestCache, Sequence[int]]] = None) -> torch.Tensor:
+        """Uploads the tokens (and sampling rows) and runs the prepared step.
+        ``portion``: (request, its tokens of this step) when the step was prepared with one."""
         B = len(caches)
-        if slot.prepared_for != tuple(rc.request_id for rc in caches):
+        expect = tuple(rc.request_id for rc in caches) + ((portion[0].request_id,) if portion else ())
+        if slot.prepared_for != expect or (slot.portion != (len(portion[1]) if portion else 0)):
             raise CacheError("decode step launched for other requests than it was prepared for")
         slot.prepared_for = None
         self.last = slot
-        slot.host_np[0, :B] = tokens
+        if portion is not None:
+            slot.host_np[:B] = tokens
+            slot.host_np[slot.size: slot.size + slot.portion] = portion[1]
+        else:
+            slot.host_np[0, :B] = tokens
         slot.ints.copy_(slot.host_ints, non_blocking=True)
         if sample is not None:
             params, recent, mask = sample
@@ -261,8 +320,10 @@ class DecodeRunner:
         self._run(slot, device_feed=False)
         for rc in caches:
             self.cache.commit(rc, 1)
+        if portion is not None:
+            self.cache.commit(portion[0], slot.portion)
         self.runner.steps_run += 1
-        self.runner.rows_run += B
+        self.runner.rows_run += B + slot.portion
         return slot.selected[:B]
 
     def read_result(self, n: int) -> Tuple[List[int], int]:

@@ -21,7 +21,7 @@ from ..cache.manager import CacheManager
 from ..errors import InfernumError
 from ..sampling.params import GenerateOptions
 from ..sampling.sampler import Sampler, pack_choices, recent_window
-from .decode import DecodeRunner
+from .decode import DecodeRunner, bucket_for
 from .scheduler import BatchConfig, FinishReason, Scheduler, Sequence_, StepPlan
 from .step import ModelRunner, StepEntry
 
@@ -143,7 +143,22 @@ class Engine:
             caches = [p.seq.cache for p in plan.portions]
             decode_only = self.decoder is not None and all(
                 p.count == 1 and p.wants_logits for p in plan.portions) and self.decoder.can_take(caches)
-            if decode_only:
+            riding = None if decode_only else self._portion_beside_decodes(plan)
+            if riding is not None:
+                # decoded tokens and one prompt portion: recorded per (bucket, rows of the portion)
+                wanting = [p for p in plan.portions if p is not riding]
+                caches = [p.seq.cache for p in wanting]
+                choices = choices[: len(wanting)]
+                sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) \
+                    if any(c is not None for c in choices) else None
+                prc = riding.seq.cache
+                prepared = self.decoder.prepare(caches, sample is not None, portion=(prc, riding.count))
+                chosen = self.decoder.launch(prepared, caches, [p.seq.token_at(p.start) for p in wanting], sample,
+                                             portion=(prc, riding.tokens))
+                self.h2d_bytes += 16 * len(wanting) + 8 * riding.count + 12
+                logits = self.decoder.last.logits
+                decode_only = True  # the result comes back the same way
+            elif decode_only:
                 sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) \
                     if any(c is not None for c in choices) else None
                 if prepared is None or prepared.prepared_for != tuple(rc.request_id for rc in caches):
@@ -203,6 +218,32 @@ class Engine:
                 del self._handles[handle.id]
         self.stats.step_seconds += time.perf_counter() - t0
         return events
+
+    GRAPH_PORTION_MIN = 64
+
+    def _portion_beside_decodes(self, plan: StepPlan):
+        """The step's one prompt portion if the step is "decoded tokens, then one
+        portion that does not reach its prompt's end": such steps recur with the
+        same shape while a long prompt is fed in portions, so they are run from
+        recorded graphs like steps of decoded tokens alone.  The portion is cut by
+        a few rows where that makes the rows of the recorded step (decoded tokens
+        rounded up to their bucket, plus the portion) a multiple of the prompt
+        kernels' tile."""
+        if self.decoder is None or len(plan.portions) < 2:
+            return None
+        *decodes, last = plan.portions
+        if last.count < self.GRAPH_PORTION_MIN or last.wants_logits \
+                or not all(p.count == 1 and p.wants_logits for p in decodes):
+            return None
+        m = self.config.token_multiple
+        if m > 0:
+            rows = bucket_for(len(decodes)) + last.count
+            extra = rows % m
+            if extra and extra * 16 <= rows and last.count - extra >= self.GRAPH_PORTION_MIN:
+                last.count -= extra  # its pages stay held for the next step
+        if not self.decoder.can_take([p.seq.cache for p in decodes], (last.seq.cache, last.count)):
+            return None
+        return last
 
     def run_until_done(self, handles: Optional[Sequence[RequestHandle]] = None) -> None:
         while self.has_work() and (handles is None or any(not h.finished for h in handles)):

@@ -75,6 +75,11 @@ class BatchConfig:
     # 1/16) is cut back to that multiple; the rows cut come with the next step.
     # 0: leave steps as they are.
     token_multiple: int = 256
+    # Budget that is left over beside a prompt portion of this step is not spent on a
+    # further portion of fewer tokens than this (and than an eighth of
+    # max_prefill_tokens) unless it finishes its prompt: a sliver costs a whole pass
+    # over the weights' tiles, and without it steps keep recurring shapes.
+    min_portion_tokens: int = 64
 
 
 @dataclass
@@ -299,6 +304,8 @@ class Scheduler:
                 self.waiting.popleft()
                 continue
             first = min(seq.remaining, cfg.max_prefill_tokens, budget)
+            if self._sliver(first, seq, plan):
+                break
             # A request that was preempted comes back only when all it has to
             # recompute fits: let back in for one portion it would run out of pages
             # again at once and be preempted again.
@@ -315,6 +322,12 @@ class Scheduler:
             self.running.append(seq)
             plan.admitted.append(seq)
             budget -= self._schedule_portion(seq, budget, plan)
+
+    def _sliver(self, count: int, seq: Sequence_, plan: StepPlan) -> bool:
+        """Whether ``count`` tokens of ``seq`` would be a sliver of a portion beside
+        another prompt portion of this step (see ``BatchConfig.min_portion_tokens``)."""
+        least = min(self.config.min_portion_tokens, self.config.max_prefill_tokens // 8)
+        return count < seq.remaining and count < least and any(p.count > 1 for p in plan.portions)
 
     def _to_reserve(self, seq: Sequence_, count: int) -> int:
         """Tokens to add to the pages held so that ``count`` more can be computed."""
@@ -336,7 +349,7 @@ class Scheduler:
         count = self._fit(seq.cache, self._to_reserve(seq, count)) + \
             (count - self._to_reserve(seq, count))
         count = min(count, seq.remaining)
-        if count <= 0:
+        if count <= 0 or self._sliver(count, seq, plan):
             return 0
         self.cache.extend(seq.cache, self._to_reserve(seq, count))
         plan.portions.append(Portion(seq, seq.num_computed, count,

@@ -261,3 +261,36 @@ def test_self_feeding_decode_steps_with_and_without_graph_equal_the_engine(folde
         torch.cuda.synchronize()
         runner.check_errors()
         assert last.tolist() == [w[steps] for w in want], f"use_graph={use_graph}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_decoded_tokens_beside_one_prompt_portion_run_from_graphs(folders, dtype):
+    """While a long prompt is fed in portions beside requests that decode, the
+    steps recur with the same shape (a batch bucket of decoded tokens, then one
+    portion): they are recorded as graphs like steps of decoded tokens alone.
+    Every request gets the tokens it gets alone."""
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype=dtype)
+    cfg = ib.BatchConfig(max_batch_size=8, block_size=8, num_blocks=128, max_prefill_tokens=64,
+                         max_tokens_per_step=80)
+    solo = ib.Engine(model, cfg)
+    short = [random_tokens(n, 320, 200 + n) for n in (5, 9, 3)]
+    long = random_tokens(230, 320, 77)
+    sampled = ib.SamplingParams(temperature=0.8, top_p=0.9, seed=11)
+    opts = [ib.GenerateOptions(max_new_tokens=40), ib.GenerateOptions(max_new_tokens=40, sampling=sampled),
+            ib.GenerateOptions(max_new_tokens=40)]
+    long_opts = ib.GenerateOptions(max_new_tokens=12)
+    alone = [solo.generate(p, o) for p, o in zip(short, opts)] + [solo.generate(long, long_opts)]
+    engine = ib.Engine(model, cfg)
+    handles = [engine.submit(p, o) for p, o in zip(short, opts)]
+    for _ in range(4):
+        engine.step()
+    handles.append(engine.submit(long, long_opts))  # fed 64 tokens at a time beside three decoding requests
+    engine.run_until_done(handles)
+    mixed = [k for k, s in engine.decoder._slots.items() if k[4] > 0]
+    assert mixed and all(k[4] >= 56 for k in mixed)
+    assert any(engine.decoder._slots[k].graph is not None for k in mixed)
+    for p, h, want in zip(short + [long], handles, alone):
+        if dtype == "float32" or h.seq.options.sampling is None:
+            assert_same_up_to_ties(folders["B"], p, h.tokens, want, dtype)
+    assert engine.cache.free_pages() == [128]

@@ -369,3 +369,30 @@ def test_planning_ahead_under_random_arrivals_ends_and_tight_pages():
     cache.check_invariants()
     assert [s.generated_ids for s in seqs] == expect
     assert cache.free_pages() == [48] and used > 5 and voided > 3
+
+
+def test_leftover_budget_is_not_spent_on_a_sliver_of_a_prompt():
+    """Beside a full portion, what is left of the budget starts no portion of a
+    few tokens (unless they finish the prompt); alone, or when they end their
+    prompt, few tokens are taken as they come."""
+    cfg = BatchConfig(max_batch_size=8, max_prefill_tokens=512, block_size=16, num_blocks=1024,
+                      max_tokens_per_step=560, token_multiple=0, min_portion_tokens=64)
+    need = SimpleNamespace(position=0, paged=PagedCacheSpec(1, 8, 0), state=None, cache_of=None)
+    cache = CacheManager([need], page_size=16, num_pages=1024, max_requests=8)
+    sched = Scheduler(cfg, cache, 4096)
+    opts = GenerateOptions(max_new_tokens=4, ignore_eos=True)
+    a = sched.add_request(list(range(3, 1203)), opts)   # 1200 tokens
+    b = sched.add_request(list(range(3, 903)), opts)    # 900 tokens
+    c = sched.add_request([7] * 30, opts)
+    plan = run_step(sched, cache)
+    # a takes 512; 48 are left: no sliver of b (it would not end b's prompt) ...
+    assert [(p.seq.id, p.count) for p in plan.portions] == [(a.id, 512)]
+    assert b.phase == Phase.WAITING and c.phase == Phase.WAITING  # ... and nobody is skipped
+    run_step(sched, cache)
+    plan = run_step(sched, cache)  # a's last 176 tokens; 384 left: a real portion of b
+    assert [(p.seq.id, p.count) for p in plan.portions] == [(a.id, 176), (b.id, 384)]
+    plan = run_step(sched, cache)  # a decodes, b takes 512; c's 30 tokens end its prompt: taken
+    assert [(p.seq.id, p.count) for p in plan.portions] == [(a.id, 1), (b.id, 512), (c.id, 30)]
+    drain(sched, cache)
+    assert a.generated_ids == solo_tokens(list(range(3, 1203)), 4)
+    cache.check_invariants()
