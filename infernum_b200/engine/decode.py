@@ -80,6 +80,10 @@ class _Slot:
 
 class DecodeRunner:
     RECENT_WIDTH = 64
+    # Buffers and graphs are kept for this many (bucket, cache-length class, sampling, feed,
+    # portion) keys; beyond it the one unused for longest is dropped (a graph holds its own
+    # activations: some hundred MB at large layer sizes).
+    MAX_RECORDED = 48
 
     def __init__(self, runner: ModelRunner, max_model_len: int, use_graph: bool = True):
         self.runner = runner
@@ -97,7 +101,14 @@ class DecodeRunner:
     def _slot(self, key: tuple) -> _Slot:
         slot = self._slots.get(key)
         if slot is not None:
+            self._slots[key] = self._slots.pop(key)  # most recently used last
             return slot
+        while len(self._slots) >= self.MAX_RECORDED:
+            pinned = self._pinned[0] if self._pinned else None
+            victim = next((k for k, v in self._slots.items() if k != pinned and v is not self.last), None)
+            if victim is None:
+                break
+            del self._slots[victim]
         size, kv_cap, sampling, _feed, portion = key
         dev = self.rt.device
         G = len(self.cache.groups)
