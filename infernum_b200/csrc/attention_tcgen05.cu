@@ -231,7 +231,10 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.y + p.entry_offset, g = blockIdx.z;
+    // Blocks start in the order x, then y, then z.  The row tile is on z, the last rows
+    // (which see the most keys) first, so that the long CTAs of every kv head and
+    // entry start before any short one; the kv head and the slice of keys are on x.
+    const int e = blockIdx.y + p.entry_offset;
     const int G = p.nh / p.nkv;
     const int rq = BM / G;  // query rows per CTA
     const int row0 = p.cu_rows[e];
@@ -243,8 +246,8 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
     // and take a slice of its key tiles each; they are merged at the end.
     const int S = SPLIT ? p.splits : 1;
     const int rank = (int)blockIdx.x % S;
-    // the last rows see the most keys: their CTAs go first
-    const int r_begin = ((int)gridDim.x / S - 1 - (int)blockIdx.x / S) * rq;
+    const int g = (int)blockIdx.x / S;
+    const int r_begin = ((int)gridDim.z - 1 - (int)blockIdx.z) * rq;
     if (r_begin >= rows_e) return;  // (the whole cluster leaves)
     const int r_count = min(rq, rows_e - r_begin);
     const int kv_hi = pos0 + r_begin + r_count;
@@ -700,7 +703,9 @@ IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, c
         if (e1 != cudaSuccess) return (int)e1;
         attr_done = true;
     }
-    dim3 grid(((max_rows_per_entry + rq - 1) / rq) * splits, n_entries - entry_offset, nkv);
+    const int row_tiles = (max_rows_per_entry + rq - 1) / rq;
+    if (row_tiles > 65535) return IB_ERR_TOO_LARGE;
+    dim3 grid(nkv * splits, n_entries - entry_offset, row_tiles);
     cudaError_t le;
     if (splits == 1) {
         le = launch_kernel(attention_tcgen05_kernel, grid, dim3(NUM_THREADS), (size_t)SMEM_BYTES,
