@@ -63,6 +63,7 @@ class RequestCache:
     reserved_tokens: int = 0  # tokens that pages are held for (>= num_tokens)
     tables: List[List[int]] = field(default_factory=list)  # per group; -1 = given back
     released: bool = False
+    serial: int = 0  # which admission this is: a request that comes back after preemption gets a new one
     version: int = 0  # counts changes of the tables (the manager bumps it)
     _arrays: Optional[tuple] = None  # (version, the tables as int32 arrays)
 
@@ -96,6 +97,7 @@ class CacheManager:
         self.layer_caches: List[LayerCache] = []
         self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
         self._requests: Dict[object, RequestCache] = {}
+        self._admissions = 0
         self._state_tensors: List[torch.Tensor] = []
         # One extra slot, and one extra page behind every group's pool (page id
         # num_pages, never handed out), belong to no request: rows that only pad
@@ -166,7 +168,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         for st in self._state_tensors:
             st[slot].zero_()
-        rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups])
+        self._admissions += 1
+        rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups], serial=self._admissions)
         self._requests[request_id] = rc
         return rc
 

@@ -169,7 +169,9 @@ class DecodeRunner:
         windowed = [g.spec.window > 0 for g in self.cache.groups]
         for r in range(len(slot.rows)):
             rc = caches[r] if r < len(caches) else None
-            who = rc.request_id if rc is not None else None
+            # (a request that was preempted and admitted again holds other pages: its
+            # admission's serial number tells the two apart)
+            who = (rc.request_id, rc.serial) if rc is not None else None
             prev = slot.rows[r]
             if prev is None or prev[0] != who:
                 for g in range(len(self.cache.groups)):

@@ -294,3 +294,40 @@ def test_steps_of_decoded_tokens_beside_one_prompt_portion_run_from_graphs(folde
         if dtype == "float32" or h.seq.options.sampling is None:
             assert_same_up_to_ties(folders["B"], p, h.tokens, want, dtype)
     assert engine.cache.free_pages() == [128]
+
+
+def test_a_request_admitted_again_does_not_inherit_its_old_block_table(folders):
+    """The decode runner mirrors block tables row by row and refreshes only what
+    changed.  A request that was released (preempted) and admitted again under
+    the same id holds other pages, possibly as many as before: its row must be
+    rewritten, or the step would read the pages it used to own."""
+    import infernum_b200 as ib
+    from infernum_b200.cache import CacheManager
+    from infernum_b200.engine.decode import DecodeRunner
+    from infernum_b200.engine.step import ModelRunner, StepEntry
+    model = ib.load_model(folders["B"], dtype="float32")
+    cfg, weights = pl.read_config(folders["B"]), pl.read_weights(folders["B"])
+    cache = CacheManager(model.cache_needs(), page_size=8, num_pages=32, max_requests=4,
+                         dtype=model.rt.dtype, device=model.rt.device)
+    runner = ModelRunner(model, cache, max_rows=64, max_entries=4)
+    session = DecodeRunner(runner, 64, use_graph=True)
+    seq = random_tokens(22, 320, 5)
+
+    def prefill_and_decode(rc):
+        runner.step([StepEntry(rc, seq[:20], [])])
+        cache.extend(rc, 1)
+        session.step([rc], [seq[20]])
+        logits = session.last.logits[0].float().cpu()
+        want = pl.forward(cfg, weights, seq[:21])[-1]
+        assert float((logits - want).abs().max() / want.abs().max()) < 2e-5
+
+    first = cache.admit("a")
+    prefill_and_decode(first)
+    old_pages = list(first.tables[0])
+    cache.release(first)
+    squatter = cache.admit("x")          # takes the pages that were just given back
+    cache.extend(squatter, 8 * len(old_pages))
+    runner.step([StepEntry(squatter, random_tokens(8 * len(old_pages), 320, 6), [])])
+    again = cache.admit("a")             # the same id, other pages, the same number of them
+    prefill_and_decode(again)
+    assert len(again.tables[0]) == len(old_pages) and set(again.tables[0]).isdisjoint(old_pages)
