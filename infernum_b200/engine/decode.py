@@ -60,6 +60,8 @@ class _Slot:
     ctx: StepContext
     rows: List[Optional[Tuple[object, List[int]]]] = field(default_factory=list)  # who sits where
     host_np: object = None  # host_ints' memory as a numpy array (cheap to fill from lists)
+    host_tables_np: object = None  # the same for host_tables
+    rows_written: List[bool] = field(default_factory=list)  # a row that pads the bucket is written once
     portion: int = 0  # rows of the prompt portion that rides along (0: decoded tokens only)
     uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
     prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
@@ -146,7 +148,7 @@ class DecodeRunner:
         slot = _Slot(size=size, ints=ints, host_ints=host_ints, tables=tables,
                      host_tables=torch.full(tuple(tables.shape), -1, dtype=torch.int32).pin_memory(),
                      selected=torch.zeros(size, dtype=torch.int32, device=dev), ctx=ctx,
-                     rows=[None] * tables.shape[1], portion=portion)
+                     rows=[None] * tables.shape[1], rows_written=[False] * tables.shape[1], portion=portion)
         slot.host_np = slot.host_ints.numpy()
         slot.result = torch.zeros(size + 1, dtype=torch.int32, device=dev)
         slot.host_result = torch.zeros(size + 1, dtype=torch.int32).pin_memory()
@@ -163,36 +165,31 @@ class DecodeRunner:
         return slot
 
     def _fill_tables(self, slot: _Slot, caches: Sequence[RequestCache]) -> bool:
-        """Brings the host mirror of the block tables up to date; True if it changed."""
+        """Brings the host mirror of the block tables up to date; True if it changed.
+        A row is rewritten when another request (or another admission of the same
+        request) sits in it, or when its request's tables changed since the row
+        was last written (the cache manager counts those changes)."""
         changed = False
+        if slot.host_tables_np is None:
+            slot.host_tables_np = slot.host_tables.numpy()
+        tab = slot.host_tables_np
         pads = self.cache.pad_pages()
-        windowed = [g.spec.window > 0 for g in self.cache.groups]
         for r in range(len(slot.rows)):
             rc = caches[r] if r < len(caches) else None
-            # (a request that was preempted and admitted again holds other pages: its
-            # admission's serial number tells the two apart)
-            who = (rc.request_id, rc.serial) if rc is not None else None
-            prev = slot.rows[r]
-            if prev is None or prev[0] != who:
-                for g in range(len(self.cache.groups)):
-                    slot.host_tables[g, r].fill_(-1)
-                    if rc is None:
-                        slot.host_tables[g, r, 0] = pads[g]
-                prev = (who, [0] * len(self.cache.groups))
-                slot.rows[r] = prev
-                changed = True
-            if rc is None:
+            seen = (rc.request_id, rc.serial, rc.version) if rc is not None else None
+            if slot.rows[r] == seen and (seen is not None or slot.rows_written[r]):
                 continue
-            for g, table in enumerate(rc.tables):
-                n = min(len(table), self.MB)
-                if windowed[g]:
-                    slot.host_tables[g, r, :n] = torch.tensor(table[:n], dtype=torch.int32)
-                    changed = True
-                elif n != prev[1][g]:
-                    lo = min(prev[1][g], n)
-                    slot.host_tables[g, r, lo:n] = torch.tensor(table[lo:n], dtype=torch.int32)
-                    prev[1][g] = n
-                    changed = True
+            slot.rows[r] = seen
+            slot.rows_written[r] = True
+            changed = True
+            tab[:, r, :] = -1
+            if rc is None:
+                for g in range(len(self.cache.groups)):
+                    tab[g, r, 0] = pads[g]
+                continue
+            for g, t in enumerate(rc.table_arrays()):
+                n = min(len(t), self.MB)
+                tab[g, r, :n] = t[:n]
         return changed
 
     # ---- the recorded body -----------------------------------------------------------
