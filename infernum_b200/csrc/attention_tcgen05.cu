@@ -17,10 +17,19 @@
 //                   swizzled layout the MMA reads, and rescale the output
 //                   accumulator in tensor memory when a maximum moved
 //
-// Scores and K are double-buffered: while the softmax warps work on tile t the
+// Scores, K and P are double-buffered: while the softmax warps work on tile t the
 // tensor cores already compute the scores of tile t+1, and K of tile t+2 loads.
-// V's buffer is free once O has been updated.  Two CTAs share an SM and fill
+// V's buffer is free once O has been updated.  The exponents refer to a
+// reference maximum that follows the true one only when that rose by more than
+// 2^8, so the accumulator is rescaled seldom.  Two CTAs share an SM and fill
 // each other's gaps.  Every wait is bounded.
+//
+// The grid has the kv head on x, the request on y and the row tile on z, the
+// last rows first: blocks start in that order, so every long CTA starts before
+// any short one.  For a portion after a long cached prefix, whose few row
+// tiles would leave the SMs idle, the key tiles of a row tile are shared out
+// over 2 or 4 CTAs of one cluster (consecutive in x), which merge their
+// unnormalised outputs, maxima and sums through distributed shared memory.
 //
 // Same mathematics as attention_plain.cu; what it restates of the reference is
 // cited there.  The reference has no tensor-core attention kernel.
