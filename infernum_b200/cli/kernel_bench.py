@@ -106,6 +106,8 @@ def main(argv=None) -> int:
     ap.add_argument("--reps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--library", action="store_true", help="gemm: time the library product instead")
+    ap.add_argument("--token-group", type=int, default=0,
+                    help="gemm --pair: token tiles of 256 per group (default: chosen from the sizes)")
     ap.add_argument("--bn", type=int, default=0, help="gemm --pair: force the tile's weight rows")
     ap.add_argument("--swiglu", action="store_true", help="gemm --pair: SiLU(gate) * up in the epilogue")
     ap.add_argument("--pair", action="store_true", help="gemm: the kernel on pairs of SMs (many tokens)")
@@ -165,7 +167,8 @@ def main(argv=None) -> int:
             fns = [lambda w=w: torch.mm(x, w.t(), out=o) for w in ws]
         elif args.pair:
             fns = [lambda w=w: gemm_tc.gemm_pair(x, w, o, err=rt.err, swiglu=args.swiglu,
-                                                 tiling=(args.bn, 1 << 20, args.bn) if args.bn else None)
+                                                 tiling=(args.bn, 1 << 20, args.bn) if args.bn else None,
+                                                 token_group=args.token_group or None)
                    for w in ws]
         else:
             fns = [lambda w=w: gemm_tc.gemm_tc(x, w, o, splits=args.splits or None) for w in ws]

@@ -165,6 +165,7 @@ struct Params {
     unsigned* err;
     int T, N, K, ldo;
     int t_tiles;   // token tiles of 256
+    int t_group;   // token tiles of a group: the first region is walked group by group
     int tiles;     // all tiles
     int tiles_a;   // those of the first region
     int bn_a;      // weight rows of a tile (the pair's) there: a multiple of 16, at most 256
@@ -179,15 +180,27 @@ struct TilePlace {
     bool second; // in the second region
 };
 __device__ __forceinline__ TilePlace locate(const Params& p, int tile) {
+    // Neighbours in the list share weights and differ in their tokens.  The first
+    // region takes the tokens in groups: all its weight columns for the first
+    // `t_group` token tiles, then for the next, so that the tokens which a round of
+    // tiles reads stay in L2 however many there are; the weights are then read once
+    // per group.  The second region, the list's last round, runs over all tokens.
     TilePlace at;
-    at.t0 = (tile % p.t_tiles) * TILE;   // neighbours share weights
     at.second = tile >= p.tiles_a;
     if (!at.second) {
+        const int cols_a = p.tiles_a / p.t_tiles;
+        const int per_group = p.t_group * cols_a;
+        const int g = tile / per_group, r = tile - g * per_group;
+        const int left = p.t_tiles - g * p.t_group;
+        const int tg = left < p.t_group ? left : p.t_group;
         at.bn = p.bn_a;
-        at.n0 = (tile / p.t_tiles) * p.bn_a;
+        at.t0 = (g * p.t_group + r % tg) * TILE;
+        at.n0 = (r / tg) * p.bn_a;
     } else {
+        const int r = tile - p.tiles_a;
         at.bn = p.bn_b;
-        at.n0 = p.n_split + ((tile - p.tiles_a) / p.t_tiles) * p.bn_b;
+        at.t0 = (r % p.t_tiles) * TILE;
+        at.n0 = p.n_split + (r / p.t_tiles) * p.bn_b;
     }
     return at;
 }
@@ -410,8 +423,8 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap&
 // rows and the rest into columns of `bn_b` rows (multiples of 16 from 32 to 256; of
 // 128 with `swiglu`).
 IB_EXPORT int ib_gemm_pair(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int T, int N,
-                           int K, int swiglu, int bn_a, int cols_a, int bn_b, int sm_count, unsigned* err,
-                           void* stream) {
+                           int K, int swiglu, int bn_a, int cols_a, int bn_b, int t_group, int sm_count,
+                           unsigned* err, void* stream) {
     if (T <= 0 || N <= 0) return IB_OK;
     if (!x || !w || !out || !err || K <= 0 || sm_count < 2 || cols_a < 0) return IB_ERR_BAD_ARG;
     const int out_cols = swiglu ? N / 2 : N;
@@ -428,6 +441,7 @@ IB_EXPORT int ib_gemm_pair(const void* x, int ldx, const void* w, int ldw, void*
     p.K = K;
     p.ldo = ldo;
     p.t_tiles = (T + TILE - 1) / TILE;
+    p.t_group = t_group < 1 || t_group > p.t_tiles ? p.t_tiles : t_group;
     const long long all_a = (N + bn_a - 1) / bn_a;
     const long long a_cols = cols_a < all_a ? cols_a : all_a;
     p.bn_a = bn_a;

@@ -81,3 +81,21 @@ def test_block_table_mirrors_follow_every_change():
     again = cache.admit("a")
     assert again.serial == 2 and again is not rc
     cache.check_invariants()
+
+
+def test_token_groups_are_even_and_bounded():
+    """Groups of token tiles keep the tokens of a round inside the byte bound,
+    never fewer than two tiles, and are evened out over the prompt."""
+    from infernum_b200.ops import gemm_tc
+    bound, most = gemm_tc.POLICY["pair_group_bytes"], gemm_tc.POLICY["pair_group_max_tiles"]
+    for T in (256, 600, 2048, 2049, 4096, 5000, 8192, 16384, 40000):
+        for K in (64, 4096, 14336, 28672, 200000):
+            tg = gemm_tc.choose_token_group(T, K)
+            t_tiles = -(-T // 256)
+            assert 1 <= tg <= max(2, most)
+            assert tg <= 2 or tg * 256 * K * 2 <= bound
+            groups = -(-t_tiles // tg)
+            assert groups * tg - t_tiles < groups  # no group more than one tile short
+    assert gemm_tc.choose_token_group(2048, 4096) == 8      # one group: as before there were groups
+    assert gemm_tc.choose_token_group(2048, 14336) == 8
+    assert gemm_tc.choose_token_group(8192, 14336) == 8     # four groups of 2,048 tokens

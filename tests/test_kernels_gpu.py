@@ -514,6 +514,25 @@ def test_gemm_pair(T, N, K, tiling):
     assert rel_err(out[:few.shape[0]], few.double().cpu()) < 5e-3
 
 
+@pytest.mark.parametrize("T, group", [(1300, 1), (1300, 4), (1300, 5), (1300, 6), (2048, 3), (700, 2)])
+@pytest.mark.parametrize("tiling", [None, (256, 2, 144), (128, 1 << 20, 128), (256, 0, 192)])
+def test_gemm_pair_token_groups(T, group, tiling):
+    """The tokens walked in groups of token tiles, even and uneven ones, beside a
+    second region that runs over all tokens: every output element is written, once."""
+    from infernum_b200.ops import gemm_tc
+    N, K = 1000, 136
+    g = torch.Generator().manual_seed(T + group)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_pair(x.to(DEV), w.to(DEV), out, tiling=tiling, token_group=group)
+    assert gemm_tc.error_flags(DEV) == 0
+    assert rel_err(out, x.double() @ w.double().T) < 5e-3
+    whole = torch.empty_like(out)
+    gemm_tc.gemm_pair(x.to(DEV), w.to(DEV), whole, tiling=tiling, token_group=1 << 20)
+    assert torch.equal(out, whole)  # the order of the tiles changes no value
+
+
 @pytest.mark.parametrize("T, I, K", [(256, 128, 64), (300, 192, 200), (700, 1024, 1024), (64, 320, 520)])
 @pytest.mark.parametrize("tiling", [None, (128, 1 << 20, 128), (256, 1, 128), (128, 3, 256)])
 def test_gemm_pair_with_swiglu_epilogue(T, I, K, tiling):
