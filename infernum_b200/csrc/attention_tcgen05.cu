@@ -9,17 +9,20 @@
 //                   of K and of V through the request's block table (2-D
 //                   boxes of page_size x 64, 128-byte swizzle)
 //   MMA warp        S = Q K^T into tensor memory (8 MMAs of 128 x 64 x 16),
-//                   then O += P V (4 MMAs of 128 x HD x 16, V as an N-major
-//                   operand straight from its [key][dim] rows)
+//                   then O += P V (4 MMAs of 128 x HD x 16, P from tensor
+//                   memory, V as an N-major operand straight from its
+//                   [key][dim] rows)
 //   4 softmax warps one thread per packed row = one TMEM lane: read the
 //                   scores with tcgen05.ld, mask, running maximum and sum in
-//                   32-bit, write P as bf16 into shared memory in the
-//                   swizzled layout the MMA reads, and rescale the output
-//                   accumulator in tensor memory when a maximum moved
+//                   32-bit, write P as bf16 back into tensor memory
+//                   (tcgen05.st), and rescale the output accumulator there
+//                   when a maximum moved.  (Two threads per row, one for each
+//                   half of a tile's keys, were slower: 560 against 521 us
+//                   for 8,192 tokens.)
 //
-// Scores, K and P are double-buffered: while the softmax warps work on tile t the
-// tensor cores already compute the scores of tile t+1, and K of tile t+2 loads.
-// V's buffer is free once O has been updated.  The exponents refer to a
+// Scores, K and V are double-buffered: while the softmax warps work on tile t the
+// tensor cores already compute the scores of tile t+1, and K of tile t+2 and V of
+// tile t+1 load.  P goes back into tensor memory, over the scores it came from.  The exponents refer to a
 // reference maximum that follows the true one only when that rose by more than
 // 2^8, so the accumulator is rescaled seldom.  Two CTAs share an SM and fill
 // each other's gaps.  Every wait is bounded.
@@ -50,18 +53,18 @@ static_assert(HD == 64 || HD == 128, "this kernel is built for head sizes 64 and
 constexpr int BM = 128;                 // packed rows per CTA
 constexpr int BN = 64;                  // keys per tile
 constexpr int KB = HD / 64;             // 64-wide blocks of the head dimension
-constexpr int NUM_THREADS = 192;        // 4 softmax warps, producer, MMA
+constexpr int SOFTMAX_WARPS = 4;        // one thread per packed row = TMEM lane
+constexpr int SOFTMAX_THREADS = SOFTMAX_WARPS * 32;
+constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1;
+constexpr int NUM_THREADS = SOFTMAX_THREADS + 64;
 constexpr int Q_BYTES = BM * HD * 2;
 constexpr int K_BYTES = BN * HD * 2;
 constexpr int V_BYTES = BN * HD * 2;
-constexpr int P_BYTES = BM * BN * 2;
-constexpr int TILE_BYTES = Q_BYTES + 2 * K_BYTES + V_BYTES + 2 * P_BYTES;  // K and P are double-buffered
+constexpr int TILE_BYTES = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES;  // K and V are double-buffered
 constexpr int BAR_BYTES = 128;  // the mbarriers and the TMEM address, behind the tiles
-// Two CTAs must fit an SM (228 KB, 1 KB of it taken per CTA): the kernel has no
-// static shared memory, so its dynamic window starts on a 1 KB boundary and the
-// tiles need no padding in front; what is left of the budget is slack for it.
-constexpr int SMEM_BYTES = (HD == 128) ? (233472 / 2 - 1024) : (TILE_BYTES + BAR_BYTES + 1024);
-static_assert(TILE_BYTES + BAR_BYTES <= SMEM_BYTES, "tiles and barriers exceed the shared memory asked for");
+// (1 KB more than is used: the tiles start on the next 1 KB boundary of the window)
+constexpr int SMEM_BYTES = TILE_BYTES + BAR_BYTES + 1024;
+static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs must fit an SM (228 KB, 1 KB of it taken per CTA)");
 static_assert(HD * BM * 4 + 2 * BM * 4 <= TILE_BYTES, "the merge of key slices reuses the tiles' shared memory");
 constexpr unsigned TMEM_COLS = 256;     // two score tiles in columns [0, 64) and [64, 128), output from 128
 constexpr unsigned O_COL = 128;
@@ -127,6 +130,15 @@ __device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint6
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the A operand in tensor memory: row i in lane i, two bf16 of
+// consecutive k per 32-bit column (k even in the low half), 8 columns per MMA.
+__device__ __forceinline__ void umma_bf16_a_tmem(unsigned tmem_d, unsigned tmem_a, uint64_t bdesc, unsigned idesc,
+                                                 unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(void* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
@@ -205,8 +217,7 @@ __host__ __device__ constexpr unsigned make_idesc(int n, bool b_n_major) {
            ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 }
 
-// SPLIT: the variant whose CTAs share a row tile's keys and merge at the end (it
-// carries more state; two CTAs per SM still leave it up to 170 registers).
+// SPLIT: the variant whose CTAs share a row tile's keys and merge at the end.
 template <bool SPLIT>
 __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const CUtensorMap& map_k,
                                                const CUtensorMap& map_v, const Params& p) {
@@ -220,22 +231,22 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
     unsigned char* q_s = smem;
     unsigned char* k_s = q_s + Q_BYTES;
     unsigned char* v_s = k_s + 2 * K_BYTES;
-    unsigned char* p_s = v_s + V_BYTES;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 2 * P_BYTES);
-    // o_done[b]: the output update of a tile t with t % 2 == b is complete (two
-    // barriers, because the softmax warps wait for tile t - 2 when tile t - 1 may
-    // be complete as well: one barrier's parity could not tell those apart)
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(v_s + 2 * V_BYTES);
     unsigned long long& q_full = bars[0];
     unsigned long long* k_full = bars + 1;
     unsigned long long* k_empty = bars + 3;
-    unsigned long long& v_full = bars[5];
-    unsigned long long& v_empty = bars[6];
-    unsigned long long* s_full = bars + 7;
-    // p_full[b]: P of a tile t with t % 2 == b is written.  Two barriers, as for
-    // o_done: with two P buffers the softmax warps may finish tile t + 1 before the
-    // MMA thread has looked at tile t.
-    unsigned long long* p_full = bars + 9;
-    unsigned long long* o_done = bars + 11;
+    unsigned long long* v_full = bars + 5;
+    unsigned long long* v_empty = bars + 7;
+    unsigned long long* s_full = bars + 9;
+    // p_full: P of tile t is written (phase t).  o_done: the output update of tile t
+    // is complete (phase t).  One barrier each is enough, because every waiter
+    // follows every phase: the MMA thread waits for p_full of every tile in turn
+    // (and P of tile t + 1 needs scores that it issues itself); every softmax thread
+    // waits for o_done of tile t - 1 before it hands over P of tile t, without
+    // which the update of tile t cannot begin.  A thread that skipped phases could
+    // not tell by the parity whether the one it waits for has come.
+    unsigned long long& p_full = bars[11];
+    unsigned long long& o_done = bars[12];
     unsigned& tmem_slot = *reinterpret_cast<unsigned*>(bars + 13);
 
     pdl_trigger();
@@ -271,16 +282,14 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
             mbar_init(&k_full[i], 1);
             mbar_init(&k_empty[i], 1);
             mbar_init(&s_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
         }
-        mbar_init(&v_full, 1);
-        mbar_init(&v_empty, 1);
-        mbar_init(&p_full[0], 128);
-        mbar_init(&p_full[1], 128);
-        mbar_init(&o_done[0], 1);
-        mbar_init(&o_done[1], 1);
+        mbar_init(&p_full, SOFTMAX_THREADS);
+        mbar_init(&o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
@@ -294,7 +303,7 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
     float m_keep = -INFINITY, l_keep = 0.f;
     bool sm_ok = true;
 
-    if (warp == 4) {
+    if (warp == PRODUCER_WARP) {
         // ---- producer: the whole warp ------------------------------------------------
         // Block-table entries are fetched 32 at a time (one per lane) and handed
         // round with shuffles, so that no TMA copy waits for a dependent load; the
@@ -335,9 +344,11 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
                     tma_load_2d(dst + kb * (BN * 128) + lane * p.page_size * 128, map, full, kb * 64, y);
             }
         };
-        // K of tile t goes to buffer t % 2 (free once the scores of tile t - 2 are
-        // computed), V of tile t to the single V buffer (free once tile t - 1's
-        // output update is done).  K runs one tile ahead of V.
+        // K of tile t goes to K buffer t % 2 (free once the scores of tile t - 2 are
+        // computed), V of tile t to V buffer t % 2 (free once tile t - 2's output
+        // update is done), so that a tile's fetch has the time of a whole tile: with
+        // one V buffer every output update waited out the latency of its V, which
+        // could start only when the update before had ended.  K runs one tile ahead.
         bool ok = true;
         for (int t = 0; t < n_tiles + 1 && ok; ++t) {
             if (t < n_tiles) {
@@ -347,12 +358,12 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
             }
             if (t >= 1) {
                 const int tv = t - 1;
-                if (tv >= 1 && !mbar_wait(&v_empty, (tv - 1) & 1)) { ok = false; break; }
-                load(v_s, &map_v, &v_full, t_off + tv, wv);
+                if (tv >= 2 && !mbar_wait(&v_empty[tv & 1], ((tv - 2) >> 1) & 1)) { ok = false; break; }
+                load(v_s + (tv & 1) * V_BYTES, &map_v, &v_full[tv & 1], t_off + tv, wv);
             }
         }
         if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_PRODUCER));
-    } else if (warp == 5) {
+    } else if (warp == MMA_WARP) {
         // ---- MMA issuer -------------------------------------------------------------
         if (elect_one()) {
             constexpr unsigned idesc_s = make_idesc(BN, false);
@@ -378,20 +389,21 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
             if (ok && n_tiles > 0) ok = issue_scores(0);
             for (int t = 0; t < n_tiles && ok; ++t) {
                 // The scores of tile t + 1 are computed while the softmax warps work on
-                // tile t.  Their buffer held tile t - 1, which the softmax warps read
-                // before they signalled p_full(t - 1), waited for in the last round.
+                // tile t.  Their buffer held the scores and then P of tile t - 1, which
+                // the output update issued in the last round read; MMAs run in order.
                 if (t + 1 < n_tiles && !issue_scores(t + 1)) { ok = false; break; }
                 // O += P V once the softmax warps have written P (and rescaled O)
-                if (!mbar_wait(&p_full[t & 1], (t >> 1) & 1) || !mbar_wait(&v_full, t & 1)) { ok = false; break; }
+                if (!mbar_wait(&p_full, t & 1) || !mbar_wait(&v_full[t & 1], (t >> 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t a = desc_k_major(p_s + (t & 1) * P_BYTES);
-                const uint64_t b = desc_n_major(v_s, BN * 128);
+                // P lies over the first 32 columns of the tile's score buffer
+                const unsigned a = tmem + (unsigned)((t & 1) * BN);
+                const uint64_t b = desc_n_major(v_s + (t & 1) * V_BYTES, BN * 128);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
-                    umma_bf16(tmem + O_COL, a + 2 * kk, b + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_o,
-                              (t > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&v_empty);
-                umma_commit(&o_done[t & 1]);
+                    umma_bf16_a_tmem(tmem + O_COL, a + 8 * kk, b + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_o,
+                                     (t > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&v_empty[t & 1]);
+                umma_commit(&o_done);
             }
             if (!ok) {
                 atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_MMA));
@@ -405,7 +417,7 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
         const bool valid = r < r_count;
         const int my_pos = valid ? pos0 + r_begin + r : -1;
         const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;   // the row's reference maximum and its sum
         bool ok = true;
         for (int t = 0; t < n_tiles; ++t) {
             if (ok && !mbar_wait(&s_full[t & 1], (t >> 1) & 1)) ok = false;
@@ -413,14 +425,14 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
             static_assert(BN == 64, "the score tile is read 64 columns at a time");
             float s[BN];
             tmem_ld64_wait(lane_addr + (t & 1) * BN, s);
-            // The running maximum is kept in raw scores (the scale is positive); the
-            // scale and the maximum enter the exponent in one multiply-add.
-            const int tile_start = (t_off + t) * BN;
+            // The maxima are kept in raw scores (the scale is positive); the scale and
+            // the reference enter the exponent in one multiply-add.
+            const int key0 = (t_off + t) * BN;
             float m_new = m_run;
-            if (tile_start + BN - 1 > pos0 + r_begin || !valid) {
+            if (key0 + BN - 1 > pos0 + r_begin || !valid) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
-                    s[c] = (tile_start + c <= my_pos) ? s[c] : -INFINITY;
+                    s[c] = (key0 + c <= my_pos) ? s[c] : -INFINITY;
                     m_new = fmaxf(m_new, s[c]);
                 }
             } else {
@@ -431,11 +443,12 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
             // that has risen by more than 2^8 in the exponent: softmax does not depend
             // on the reference, P stays below 256 (fine in bfloat16, the sum is 32-bit),
             // and the output accumulator is rescaled seldom instead of at most tiles.
-            const bool move = m_new > -INFINITY && (m_run == -INFINITY || (m_new - m_run) * p.scale_log2 > 8.f);
-            const float m_ref = move ? m_new : m_run;
-            const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-            const float corr = move ? fast_exp2(fmaf(m_run, p.scale_log2, -m_scaled)) : 1.f;
-            m_run = m_ref;
+            float corr = 1.f;
+            if (m_new > -INFINITY && (m_run == -INFINITY || (m_new - m_run) * p.scale_log2 > 8.f)) {
+                corr = fast_exp2((m_run - m_new) * p.scale_log2);  // 0 from a reference of -inf
+                m_run = m_new;
+            }
+            const float m_scaled = m_run == -INFINITY ? 0.f : m_run * p.scale_log2;
             float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
             for (int c = 0; c < BN; c += 2) {
@@ -445,44 +458,46 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
                 sum1 += s[c + 1];
             }
             l_run = l_run * corr + (sum0 + sum1);
+            // The update of tile t - 1 began when the exponentials of this tile did and is
+            // long complete; the wait is there to follow the barrier's phases, and for the
+            // rescaling below.
+            if (t > 0 && ok && !mbar_wait(&o_done, (t - 1) & 1)) ok = false;
             // the output accumulator holds tiles 0..t-1: rescale it if any row of
-            // this warp moved its reference (tile t-1's update must have completed)
+            // this warp moved its reference
             if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-                if (ok && !mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) ok = false;
                 tc_fence_after();
-                {
 #pragma unroll
-                    for (int c = 0; c < HD; c += 16) {
-                        unsigned v[16];
-                        tmem_ld16(lane_addr + O_COL + c, v);
-                        tmem_ld_wait();
+                for (int c = 0; c < HD; c += 16) {
+                    unsigned v[16];
+                    tmem_ld16(lane_addr + O_COL + c, v);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
-                        tmem_st16(lane_addr + O_COL + c, v);
-                    }
-                    tmem_st_wait();
+                    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+                    tmem_st16(lane_addr + O_COL + c, v);
                 }
             }
-            // P (bf16) into the K-major swizzled tile [128 rows][64 keys]: row m,
-            // 16-byte chunk ch sits at chunk position ch ^ (m % 8) of its 128-byte row.
-            // Two P buffers: this one was last read by the output update of tile t - 2.
-            if (t >= 2 && ok && !mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1)) ok = false;
-            unsigned char* p_t = p_s + (t & 1) * P_BYTES;
+            // P (bf16) into tensor memory, where the output update reads it as its A
+            // operand: 32 columns of two keys each, over the first half of this tile's
+            // score buffer (this lane's scores are in registers).  Through shared memory,
+            // P cost a store and a read of 16 KB a tile on the path that also feeds K, V
+            // and Q to the tensor core, and that path was the busiest unit of the kernel.
 #pragma unroll
-            for (int ch = 0; ch < BN / 8; ++ch) {
-                uint4 pk;
-                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+            for (int i = 0; i < BN / 32; ++i) {
+                unsigned pk[16];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(s[ch * 8 + 2 * j], s[ch * 8 + 2 * j + 1]);
-                *reinterpret_cast<uint4*>(p_t + m * 128 + ((ch ^ (m & 7)) << 4)) = pk;
+                for (int j = 0; j < 16; ++j) {
+                    __nv_bfloat162 two = __floats2bfloat162_rn(s[32 * i + 2 * j], s[32 * i + 2 * j + 1]);
+                    pk[j] = *reinterpret_cast<unsigned*>(&two);
+                }
+                tmem_st16(lane_addr + (t & 1) * BN + 16 * i, pk);
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_full[t & 1]);
+            mbar_arrive(&p_full);
         }
         // ---- epilogue: O / l -------------------------------------------------------
         if (n_tiles > 0) {
-            if (ok && !mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) ok = false;
+            if (ok && !mbar_wait(&o_done, (n_tiles - 1) & 1)) ok = false;
             tc_fence_after();
         }
         if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_ATTN_TC_SOFTMAX));
@@ -537,7 +552,7 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
     if (S > 1) {
         // ---- merge of the slices: the leader adds the others' rows to its own ----------
         cluster_sync_all();
-        if (warp < 4 && rank == 0) {
+        if (warp < SOFTMAX_WARPS && rank == 0) {
             tc_fence_after();
             const int m = threadIdx.x;
             const int r = m / G, h = m % G;
@@ -594,21 +609,20 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
         cluster_sync_all();  // nobody leaves while the leader may still read its rows
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
     }
 }
 
 // Left alone the compiler settles at 96 registers with spills, as if for three CTAs per
-// SM; shared memory allows two, so it may as well use the registers of two.
+// SM; tensor memory allows two, so it may as well use the registers of two.
 __global__ void __maxnreg__(128)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Params p) {
     attention_body<false>(map_q, map_k, map_v, p);
 }
 
-// two CTAs per SM still leave this one up to 170 registers per thread
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attention_tcgen05_split_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                const __grid_constant__ CUtensorMap map_v, const Params p) {
