@@ -195,10 +195,14 @@ def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks
     return result
 
 
-def time_e2e(model, batch, prompt_len, steps, warmup, page_size, seed):
+def time_e2e(model, batch, prompt_len, steps, warmup, page_size, seed, launch_ahead=True):
     """The same through ``Engine``: requests are submitted as host token lists,
     every step copies its inputs from pinned memory and reads the selected
-    tokens back."""
+    tokens back.  With ``launch_ahead`` (the engine's default) a decode step is
+    launched behind the one in flight and takes that one's tokens on the device;
+    its positions, lengths and slots still come from the host every step.
+    Without it every step is launched after the one before was read and gets
+    its tokens from the host too."""
     import torch
 
     import infernum_b200 as ib
@@ -207,7 +211,8 @@ def time_e2e(model, batch, prompt_len, steps, warmup, page_size, seed):
     pages = batch * (-(-total // page_size)) + 8
     engine = ib.Engine(model, ib.BatchConfig(max_batch_size=batch, max_prefill_tokens=2048,
                                              block_size=page_size, num_blocks=pages,
-                                             max_tokens_per_step=2048, max_model_len=total + 8))
+                                             max_tokens_per_step=2048, max_model_len=total + 8,
+                                             launch_ahead=launch_ahead))
     g = torch.Generator().manual_seed(seed)
     opts = ib.GenerateOptions(max_new_tokens=steps + warmup + 6, ignore_eos=True)
     handles = [engine.submit(torch.randint(0, model.spec.vocab_size, (prompt_len,), generator=g).tolist(), opts)
@@ -330,6 +335,12 @@ def main() -> int:
         main_run = time_decode(model, args.batch, args.prompt_len, args.steps, warmup, args.page_size,
                                args.seed, clocks)
         e2e = time_e2e(model, args.batch, args.prompt_len, args.steps, warmup, args.page_size, args.seed + 1)
+        e2e["tokens"] = "fed on the device to a step launched ahead; positions, lengths and slots from the host"
+        if not args.skip_extras:
+            fed = time_e2e(model, args.batch, args.prompt_len, min(args.steps, 64), warmup, args.page_size,
+                           args.seed + 1, launch_ahead=False)
+            e2e["value_host_fed"] = round(fed["value"], 2)  # every step launched after the one before was read
+            e2e["h2d_bytes_per_step_host_fed"] = fed["h2d_bytes_per_step"]
         points = {}
         if not args.skip_extras:
             for b in (1, 64):

@@ -26,6 +26,7 @@ rebuild and run eagerly every step (:1549-1598).
 
 from __future__ import annotations
 
+import collections
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -66,7 +67,9 @@ class _Slot:
     uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
     prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
     result: Optional[torch.Tensor] = None  # device [size + 1]: the selected tokens, then the error word
-    host_result: Optional[torch.Tensor] = None  # pinned mirror
+    host_results: Optional[list] = None  # two pinned mirrors, used in turn
+    result_events: Optional[list] = None  # and the events after their copies
+    result_turn: int = 0
     sampled: Optional[torch.Tensor] = None
     params: Optional[torch.Tensor] = None
     host_params: Optional[torch.Tensor] = None
@@ -98,6 +101,8 @@ class DecodeRunner:
         self._slots: Dict[tuple, _Slot] = {}
         self._pinned: Optional[Tuple[tuple, List[RequestCache]]] = None
         self.last: Optional[_Slot] = None
+        # results of launched steps on their way to the host, oldest first
+        self._reads: collections.deque = collections.deque(maxlen=4)
 
     # ---- buffers -------------------------------------------------------------------
     def _slot(self, key: tuple) -> _Slot:
@@ -151,7 +156,8 @@ class DecodeRunner:
                      rows=[None] * tables.shape[1], rows_written=[False] * tables.shape[1], portion=portion)
         slot.host_np = slot.host_ints.numpy()
         slot.result = torch.zeros(size + 1, dtype=torch.int32, device=dev)
-        slot.host_result = torch.zeros(size + 1, dtype=torch.int32).pin_memory()
+        slot.host_results = [torch.zeros(size + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        slot.result_events = [torch.cuda.Event(), torch.cuda.Event()]
         if sampling:
             f = core.SAMPLE_PARAM_FLOATS
             slot.sampled = torch.zeros(size, dtype=torch.int32, device=dev)
@@ -245,7 +251,9 @@ class DecodeRunner:
         with the given input tokens.  ``sample``: (params, recent, mask) host
         tensors from ``pack_choices`` when some row samples.  Returns the
         selected token ids, int32 [len(caches)] on the device."""
-        return self.launch(self.prepare(caches, sample is not None), caches, tokens, sample)
+        out = self.launch(self.prepare(caches, sample is not None), caches, tokens, sample)
+        self._reads.pop()  # the caller reads the device tensor itself
+        return out
 
     def prepare(self, caches: Sequence[RequestCache], sampling: bool,
                 portion: Optional[Tuple[RequestCache, int]] = None) -> _Slot:
@@ -295,11 +303,17 @@ class DecodeRunner:
         slot.prepared_for = tuple(rc.request_id for rc in caches)
         return slot
 
-    def launch(self, slot: _Slot, caches: Sequence[RequestCache], tokens: Sequence[int],
+    def launch(self, slot: _Slot, caches: Sequence[RequestCache], tokens: Optional[Sequence[int]],
                sample: Optional[tuple] = None,
-               portion: Optional[Tuple[RequestCache, Sequence[int]]] = None) -> torch.Tensor:
+               portion: Optional[Tuple[RequestCache, Sequence[int]]] = None,
+               feed_from: Optional[_Slot] = None) -> torch.Tensor:
         """Uploads the tokens (and sampling rows) and runs the prepared step.
-        ``portion``: (request, its tokens of this step) when the step was prepared with one."""
+        ``portion``: (request, its tokens of this step) when the step was prepared with one.
+        ``feed_from``: instead of ``tokens``, the step takes what the step launched
+        before it (that slot's, which may be this one) selects, row for row: it can
+        be launched while that step still runs, before the host has seen its tokens.
+        The step's result starts on its way to the host at once; ``read_result``
+        returns the results in the order of the launches."""
         B = len(caches)
         expect = tuple(rc.request_id for rc in caches) + ((portion[0].request_id,) if portion else ())
         if slot.prepared_for != expect or (slot.portion != (len(portion[1]) if portion else 0)):
@@ -307,11 +321,15 @@ class DecodeRunner:
         slot.prepared_for = None
         self.last = slot
         if portion is not None:
+            if feed_from is not None:
+                raise CacheError("a step with a prompt portion takes its tokens from the host")
             slot.host_np[:B] = tokens
             slot.host_np[slot.size: slot.size + slot.portion] = portion[1]
-        else:
+        elif feed_from is None:
             slot.host_np[0, :B] = tokens
         slot.ints.copy_(slot.host_ints, non_blocking=True)
+        if feed_from is not None:
+            slot.ints[0, :B].copy_(feed_from.selected[:B])
         if sample is not None:
             params, recent, mask = sample
             slot.host_params.zero_()
@@ -328,6 +346,11 @@ class DecodeRunner:
             slot.uploaded = torch.cuda.Event()
         slot.uploaded.record()
         self._run(slot, device_feed=False)
+        turn = slot.result_turn
+        slot.result_turn ^= 1
+        slot.host_results[turn].copy_(slot.result, non_blocking=True)
+        slot.result_events[turn].record()
+        self._reads.append((slot.host_results[turn], slot.result_events[turn], slot.size))
         for rc in caches:
             self.cache.commit(rc, 1)
         if portion is not None:
@@ -337,13 +360,13 @@ class DecodeRunner:
         return slot.selected[:B]
 
     def read_result(self, n: int) -> Tuple[List[int], int]:
-        """The tokens selected by the last host-fed step and the error word, read
-        through pinned memory (this waits for the step)."""
-        slot = self.last
-        slot.host_result.copy_(slot.result, non_blocking=True)
-        torch.cuda.current_stream(self.rt.device).synchronize()
-        host = slot.host_result.tolist()
-        return host[:n], host[slot.size]
+        """The tokens selected by the oldest launched step not read yet and the
+        error word after it, through pinned memory (this waits for that step, not
+        for one launched after it)."""
+        buf, event, size = self._reads.popleft()
+        event.synchronize()
+        host = buf.tolist()
+        return host[:n], host[size]
 
     # ---- fed from the device ---------------------------------------------------------------
     def pin(self, caches: Sequence[RequestCache], tokens: Sequence[int], steps: int) -> None:

@@ -69,6 +69,7 @@ class EngineStats:
     step_seconds: float = 0.0
     ahead_used: int = 0    # decode steps that ran from a plan made while the step before them ran
     ahead_voided: int = 0  # such plans dropped because a request ended or arrived meanwhile
+    ahead_launched: int = 0  # of the former, those launched before the step before them was read
 
 
 class Engine:
@@ -89,7 +90,8 @@ class Engine:
         self._handles: Dict[int, RequestHandle] = {}
         self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if cfg.cuda_graphs else None
         # the next decode step, planned and prepared while the one before it ran
-        self._ahead: Optional[Tuple[StepPlan, object]] = None
+        # (plan, prepared buffers, whether it is on the GPU already)
+        self._ahead: Optional[Tuple[StepPlan, object, bool]] = None
         self.h2d_bytes = 0  # bytes of step inputs copied to the device so far
         self.d2h_bytes = 0  # bytes of step results read back so far
 
@@ -112,17 +114,24 @@ class Engine:
         self.scheduler.cancel(handle.seq)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        # (a step launched ahead is taken back by the next ``step`` even if its requests have all ended)
+        return self.scheduler.has_work() or (self._ahead is not None and self._ahead[2])
 
     # ---- one iteration -------------------------------------------------------------
     def step(self) -> List[Tuple[RequestHandle, GenerationEvent]]:
         """One scheduling round and one model step; returns the new events."""
         t0 = time.perf_counter()
-        prepared = None
+        prepared, in_flight = None, False
         if self._ahead is not None:
-            plan, prepared = self._ahead
+            plan, prepared, in_flight = self._ahead
             self._ahead = None
-            if self.scheduler.ahead_still_holds(plan):
+            if in_flight:
+                # It runs already, on the tokens the step before it selected.  Requests that
+                # ended meanwhile (end-of-sequence, cancel) computed one token in vain, which
+                # is dropped below; one that arrived waits for the next step.
+                self.stats.ahead_used += 1
+                self.stats.ahead_launched += 1
+            elif self.scheduler.ahead_still_holds(plan):
                 self.stats.ahead_used += 1
             else:
                 self.stats.ahead_voided += 1
@@ -141,10 +150,12 @@ class Engine:
                 choices.append(None if sp is None else
                                (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
             caches = [p.seq.cache for p in plan.portions]
-            decode_only = self.decoder is not None and all(
-                p.count == 1 and p.wants_logits for p in plan.portions) and self.decoder.can_take(caches)
+            decode_only = in_flight or (self.decoder is not None and all(
+                p.count == 1 and p.wants_logits for p in plan.portions) and self.decoder.can_take(caches))
             riding = None if decode_only else self._portion_beside_decodes(plan)
-            if riding is not None:
+            if in_flight:
+                chosen = True
+            elif riding is not None:
                 # decoded tokens and one prompt portion: recorded per (bucket, rows of the portion)
                 wanting = [p for p in plan.portions if p is not riding]
                 caches = [p.seq.cache for p in wanting]
@@ -174,15 +185,18 @@ class Engine:
                 self.h2d_bytes += self.runner.last_upload_bytes
                 chosen = self.sampler.select(logits, choices) if logits is not None and wanting else None
             self.scheduler.commit(plan)
-            if decode_only:
+            # (after a step launched ahead in which a request turned out to have ended, the
+            # next step comes from the scheduler, which takes that request's pages back)
+            if decode_only and not (in_flight and any(p.seq.finished for p in plan.portions)):
                 # While this step runs: plan the next one and fill in all of it but the
                 # tokens, so that little is left to do between the two steps.
                 ahead = self.scheduler.plan_decode_ahead()
                 if ahead is not None:
                     nxt = [p.seq.cache for p in ahead.portions]
                     samples = any(p.seq.options.sampling is not None for p in ahead.portions)
-                    self._ahead = (ahead, self.decoder.prepare(nxt, samples)
-                                   if self.decoder.can_take(nxt) else None)
+                    ready = self.decoder.prepare(nxt, samples) if self.decoder.can_take(nxt) else None
+                    launched = ready is not None and riding is None and self._launch_ahead(plan, ahead, ready, nxt)
+                    self._ahead = (ahead, ready, launched)
             if chosen is not None:
                 if decode_only:
                     picked, flags = self.decoder.read_result(len(wanting))
@@ -193,7 +207,9 @@ class Engine:
                 if flags:
                     self.runner.check_errors()
                 for p, tok in zip(wanting, picked):
-                    handle = self._handles[p.seq.id]
+                    handle = self._handles.get(p.seq.id)
+                    if handle is None or p.seq.finished:
+                        continue  # it ended while this step, launched ahead, ran
                     emitted = self.scheduler.append_token(p.seq, tok)
                     if emitted is not None:
                         self.stats.generated_tokens += 1
@@ -218,6 +234,29 @@ class Engine:
                 del self._handles[handle.id]
         self.stats.step_seconds += time.perf_counter() - t0
         return events
+
+    def _launch_ahead(self, plan: StepPlan, ahead: StepPlan, ready, caches) -> bool:
+        """Launches the planned next decode step now, behind the one in flight, fed
+        on the device with the tokens that one selects: the host then reads a step's
+        tokens while the next step runs, and the GPU does not wait for the host
+        between the two.  Possible when the rows are those of the step in flight,
+        in its order, and no row's sampling needs the tokens not yet seen (a
+        repetition penalty looks at the most recent ones)."""
+        if not self.config.launch_ahead or self.decoder.last is None or self.decoder.last.portion:
+            return False
+        if [p.seq.id for p in ahead.portions] != [p.seq.id for p in plan.portions]:
+            return False
+        choices = []
+        for p in ahead.portions:
+            sp = p.seq.options.sampling
+            if sp is not None and sp.repetition_penalty != 1.0:
+                return False
+            # (the token of the step in flight is not appended yet: this will be the one after it)
+            choices.append(None if sp is None else (sp, len(p.seq.generated_ids) + 1, ()))
+        sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) if any(c is not None for c in choices) else None
+        self.decoder.launch(ready, caches, None, sample, feed_from=self.decoder.last)
+        self.h2d_bytes += 12 * len(caches)
+        return True
 
     GRAPH_PORTION_MIN = 64
 
@@ -248,6 +287,8 @@ class Engine:
     def run_until_done(self, handles: Optional[Sequence[RequestHandle]] = None) -> None:
         while self.has_work() and (handles is None or any(not h.finished for h in handles)):
             self.step()
+        while self._ahead is not None and self._ahead[2] and not self.scheduler.has_work():
+            self.step()  # a step launched ahead for requests that have all ended: take it back
         self.scheduler._reap()
 
     # ---- the reference's entry points ------------------------------------------------

@@ -80,6 +80,12 @@ class BatchConfig:
     # max_prefill_tokens) unless it finishes its prompt: a sliver costs a whole pass
     # over the weights' tiles, and without it steps keep recurring shapes.
     min_portion_tokens: int = 64
+    # Launch the next decode step behind the one in flight, before its tokens are
+    # read, whenever that step is certain but for those tokens (nobody waits,
+    # nobody reaches a length limit, pages are there).  A request that ends on a
+    # token nobody could foresee (end-of-sequence, cancel) then has computed one
+    # token in vain.
+    launch_ahead: bool = True
 
 
 @dataclass

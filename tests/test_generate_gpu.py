@@ -222,6 +222,51 @@ def test_decode_steps_planned_ahead_survive_ends_and_arrivals(folders, dtype):
     assert engine.cache.free_pages() == [96] and engine.cache.num_free_slots == 4
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_launched_ahead_of_their_tokens(folders, dtype):
+    """The next decode step is launched behind the one in flight, fed on the device,
+    before the host has read that one's tokens.  A request that then turns out to
+    have ended (end-of-sequence, cancel) drops the token computed in vain, one that
+    arrives joins a step later; nobody's tokens change against an engine that
+    launches every step after reading the one before, greedy or sampled."""
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype=dtype)
+    prompts = [random_tokens(n, 320, 170 + n) for n in (5, 9, 14, 6)]
+    sampled = ib.SamplingParams(temperature=0.9, top_p=0.95, seed=3)  # no penalty: nothing to wait for
+    base = dict(max_batch_size=4, block_size=8, num_blocks=96, max_prefill_tokens=64)
+    solo = ib.Engine(model, ib.BatchConfig(launch_ahead=False, **base))
+    stop = solo.generate(prompts[0], ib.GenerateOptions(max_new_tokens=30))[10]
+
+    def run(ahead):
+        engine = ib.Engine(model, ib.BatchConfig(launch_ahead=ahead, **base))
+        h0 = engine.submit(prompts[0], ib.GenerateOptions(max_new_tokens=30, eos_token_id=stop))
+        h1 = engine.submit(prompts[1], ib.GenerateOptions(max_new_tokens=40, sampling=sampled))
+        h2 = engine.submit(prompts[2], ib.GenerateOptions(max_new_tokens=40))
+        for _ in range(5):
+            engine.step()
+        h3 = engine.submit(prompts[3], ib.GenerateOptions(max_new_tokens=12))  # arrives
+        while len(h2.tokens) < 20:
+            engine.step()
+        engine.cancel(h2)
+        engine.run_until_done([h0, h1, h3])
+        while engine.has_work():
+            engine.step()
+        assert engine.cache.free_pages() == [96] and engine.cache.num_free_slots == 4
+        assert engine.decoder is None or not engine.decoder._reads  # every launched step was read
+        return [h.tokens for h in (h0, h1, h2, h3)], [h.finish_reason for h in (h0, h1, h2, h3)], engine.stats
+
+    on, on_reasons, on_stats = run(True)
+    off, off_reasons, off_stats = run(False)
+    assert on_stats.ahead_launched > 20 and off_stats.ahead_launched == 0
+    assert on_reasons == off_reasons == [ib.FinishReason.STOP, ib.FinishReason.LENGTH,
+                                         ib.FinishReason.CANCELLED, ib.FinishReason.LENGTH]
+    assert [len(t) for t in on] == [len(t) for t in off] or dtype == "bfloat16"
+    if dtype == "float32":  # token for token; in bfloat16 a near-tie may round otherwise in another batch
+        assert on == off
+    else:
+        assert_same_up_to_ties(folders["B"], prompts[3], on[3], off[3], dtype)
+
+
 def test_self_feeding_decode_steps_with_and_without_graph_equal_the_engine(folders):
     """Decode steps that feed themselves on the device (the selected token and the
     advanced position of one step are the input of the next, with no copy from
