@@ -345,6 +345,7 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int qkv_stride,
 // bf16 variant that moves 16 bytes at a time: an item is 8 consecutive pairs
 // (elements j..j+7 and j+rd/2..j+rd/2+7 of one head), 8 unrotated elements, or
 // 8 elements of v.  Needs rd % 16 == 0, hd % 8 == 0 and 16-byte aligned rows.
+constexpr int ROPE_VEC8_MAX_PAIRS = 256;  // rotated pairs of a head the vectorised kernel takes (rd <= 512)
 __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
                                         const int* __restrict__ positions,
                                         const int* __restrict__ row_entry,
@@ -355,9 +356,13 @@ __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
                                         unsigned* __restrict__ err) {
     pdl_trigger();
     // Positions, block tables and frequencies were complete before this chain of
-    // kernels began: the page look-up and the sines and cosines of this thread's
-    // first item are done while the product before this kernel still runs, and
-    // only then is its result waited for.
+    // kernels began: the page look-up and the row's sines and cosines are done
+    // while the product before this kernel still runs, and only then is its
+    // result waited for.  The angles depend on the position and the pair, not on
+    // the head: the block works them out once (a pair per thread) and every head's
+    // items read them from shared memory.
+    __shared__ __align__(16) float sn_s[ROPE_VEC8_MAX_PAIRS];
+    __shared__ __align__(16) float cs_s[ROPE_VEC8_MAX_PAIRS];
     const int row = blockIdx.x;
     const int rot_items = rd >> 4;             // per head: items of 8 pairs
     const int pass_items = (hd - rd) >> 3;     // per head: items of 8 unrotated elements
@@ -382,19 +387,11 @@ __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
     const int half = rd >> 1;
 
     const int first_it = blockIdx.y * blockDim.x + threadIdx.x;
-    float sn[8], cs[8];
-    auto angles = [&](int it) {
-        if (it < items_qk && it % per_head < rot_items) {
-            const int j = (it % per_head) << 3;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) sincosf((float)pos * inv_freq[j + k], &sn[k], &cs[k]);
-        }
-    };
-    angles(first_it);
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sn_s[j], &cs_s[j]);
+    __syncthreads();
     pdl_wait();
 
     for (int it = first_it; it < items; it += gridDim.y * blockDim.x) {
-        if (it != first_it) angles(it);
         if (it < items_qk) {
             const int head = it / per_head, p = it % per_head;
             bf16* x = base + (size_t)head * hd;
@@ -406,6 +403,11 @@ __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
                 uint4 b4 = *reinterpret_cast<const uint4*>(x + j + half);
                 __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a4);
                 __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b4);
+                float sn[8], cs[8];
+                *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sn_s + j);
+                *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sn_s + j + 4);
+                *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(cs_s + j);
+                *reinterpret_cast<float4*>(cs + 4) = *reinterpret_cast<const float4*>(cs_s + j + 4);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const float2 xa = __bfloat1622float2(a2[k]), xb = __bfloat1622float2(b2[k]);
@@ -451,7 +453,7 @@ IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int
     const int threads = 128;
     int by = (items + threads - 1) / threads;
     if (by > 16) by = 16;
-    if (act_dtype == 1 && rd % 16 == 0 && hd % 8 == 0 && qkv_stride % 8 == 0 &&
+    if (act_dtype == 1 && rd % 16 == 0 && rd / 2 <= ROPE_VEC8_MAX_PAIRS && hd % 8 == 0 && qkv_stride % 8 == 0 &&
         !(((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15)) {
         const int vitems = (nh + nkv) * ((rd >> 4) + ((hd - rd) >> 3)) + (write_kv ? nkv * (hd >> 3) : 0);
         int vby = (vitems + threads - 1) / threads;
