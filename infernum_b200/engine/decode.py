@@ -11,9 +11,13 @@ bucket.  Requests may come and go between steps without a new recording; a
 graph is recorded per (bucket, cache-length class, sampling or not), the first
 time it is needed, after one eager step.
 
-Two ways to feed it:
+Three ways to feed it:
   * from the host (``Engine``): tokens, positions and lengths are copied from
     pinned memory every step, changed block-table rows too;
+  * from the step before (``launch(feed_from=...)``): positions, lengths and
+    tables come from the host as above, the tokens are the ones the step
+    launched before selects, copied on the device, so the step can be launched
+    while that one still runs and the host reads its tokens meanwhile;
   * from the device (``pin``): a fixed set of requests whose tokens are the ones
     the previous step selected and whose positions advance on the device; the
     host only reserves pages ahead and uploads the tables once.  Nothing is read
