@@ -287,9 +287,13 @@ class Engine:
     def run_until_done(self, handles: Optional[Sequence[RequestHandle]] = None) -> None:
         while self.has_work() and (handles is None or any(not h.finished for h in handles)):
             self.step()
-        while self._ahead is not None and self._ahead[2] and not self.scheduler.has_work():
-            self.step()  # a step launched ahead for requests that have all ended: take it back
+        self._take_back_ahead()
         self.scheduler._reap()
+
+    def _take_back_ahead(self) -> None:
+        """A step launched ahead for requests that have all ended meanwhile is read and dropped."""
+        while self._ahead is not None and self._ahead[2] and not self.scheduler.has_work():
+            self.step()
 
     # ---- the reference's entry points ------------------------------------------------
     def generate(self, prompt_ids: Sequence[int], options: Optional[GenerateOptions] = None) -> List[int]:
@@ -309,6 +313,7 @@ class Engine:
                     yield ev.token
                 elif h is handle and ev.kind == "error":
                     raise InfernumError(ev.message or "generation failed")
+        self._take_back_ahead()
         self.scheduler._reap()
 
     def generate_batch(self, prompts: Sequence[Sequence[int]],

@@ -267,6 +267,24 @@ def test_decode_steps_launched_ahead_of_their_tokens(folders, dtype):
         assert_same_up_to_ties(folders["B"], prompts[3], on[3], off[3], dtype)
 
 
+def test_stream_that_ends_on_a_stop_token_leaves_no_step_behind(folders):
+    """A streamed request that ends on its end-of-sequence token has a step in
+    flight that was launched ahead; it is read and dropped before the call
+    returns, and the next request starts from a clean engine."""
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype="float32")
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=8, num_blocks=32))
+    prompt = random_tokens(9, 320, 411)
+    whole = engine.generate(prompt, ib.GenerateOptions(max_new_tokens=24))
+    stop = whole[12]
+    got = list(engine.generate_stream(prompt, ib.GenerateOptions(max_new_tokens=24, eos_token_id=stop)))
+    assert got == whole[: whole.index(stop)]
+    assert engine.stats.ahead_launched > 0
+    assert (engine._ahead is None or not engine._ahead[2]) and not engine.decoder._reads
+    assert engine.cache.free_pages() == [32] and engine.cache.num_free_slots == 2
+    assert engine.generate(prompt, ib.GenerateOptions(max_new_tokens=24)) == whole
+
+
 def test_self_feeding_decode_steps_with_and_without_graph_equal_the_engine(folders):
     """Decode steps that feed themselves on the device (the selected token and the
     advanced position of one step are the input of the next, with no copy from
