@@ -45,7 +45,7 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
     float m = -INFINITY, l = 0.f;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     for (int j = lo; j <= pos; ++j) {
-        const int page = table[j / page_size];
+        const int page = j / page_size < max_blocks ? table[j / page_size] : -1;  // beyond the row: reported, not read
         if (page < 0 || page >= num_pages) {
             if (lane == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
             continue;

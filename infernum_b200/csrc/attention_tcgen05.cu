@@ -492,6 +492,22 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
                 tmem_st16(lane_addr + (t & 1) * BN + 16 * i, pk);
             }
             tmem_st_wait();
+            if (t == n_tiles - 1 && t_off + t == all_tiles - 1 && key0 + BN > kv_hi) {
+                // The last tile of the row tile ends beyond the request's keys: what lies
+                // there in the page (left by whoever held it before) or in the page that
+                // stands in for a missing table entry may be anything, and 0 x Inf or
+                // 0 x NaN is NaN in the product P V.  The rows of V from key kv_hi on are
+                // cleared in shared memory once the tile has landed (whole 128-byte rows,
+                // which the swizzle permutes only within themselves).
+                if (ok && !mbar_wait(&v_full[t & 1], (t >> 1) & 1)) ok = false;
+                const int first = kv_hi - key0;  // 1..63
+                unsigned char* vt = v_s + (t & 1) * V_BYTES;
+                for (int i = m; i < (BN - first) * KB * 8; i += SOFTMAX_THREADS) {
+                    const int chunk = i & 7, row = first + (i >> 3) % (BN - first), kb = (i >> 3) / (BN - first);
+                    *reinterpret_cast<uint4*>(vt + kb * (BN * 128) + row * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            }
             tc_fence_before();
             mbar_arrive(&p_full);
         }

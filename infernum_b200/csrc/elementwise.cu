@@ -294,7 +294,9 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int qkv_stride,
     long long slot_base = -1;  // element offset of (page, kv head 0, slot, 0)
     if (write_kv) {
         const int e = row_entry[row];
-        const int page = block_tables[(size_t)e * max_blocks + pos / page_size];
+        // (a position beyond the row of the table is reported like a bad entry, not followed)
+        const int slot_idx = pos / page_size;
+        const int page = (pos >= 0 && slot_idx < max_blocks) ? block_tables[(size_t)e * max_blocks + slot_idx] : -1;
         if (page < 0 || page >= num_pages) {
             if (threadIdx.x == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
         } else {
@@ -376,7 +378,9 @@ __global__ void rope_append_vec8_kernel(bf16* __restrict__ qkv, int qkv_stride,
     long long slot_base = -1;
     if (write_kv) {
         const int e = row_entry[row];
-        const int page = block_tables[(size_t)e * max_blocks + pos / page_size];
+        // (a position beyond the row of the table is reported like a bad entry, not followed)
+        const int slot_idx = pos / page_size;
+        const int page = (pos >= 0 && slot_idx < max_blocks) ? block_tables[(size_t)e * max_blocks + slot_idx] : -1;
         if (page < 0 || page >= num_pages) {
             if (threadIdx.x == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
         } else {

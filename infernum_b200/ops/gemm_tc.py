@@ -82,6 +82,8 @@ def pair_lib() -> ctypes.CDLL:
 
 
 def _error_word(device) -> torch.Tensor:
+    """The word for calls that bring none (a kernel run on its own, outside a
+    model step); a model's products always bring their engine's word."""
     ws = _workspaces.get(device)
     if ws is None:
         ws = {"err": core.new_error_word(device)}
@@ -198,7 +200,7 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
     core.check(code, "gemm_pair")
 
 
-def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> bool:
     """Takes a product or leaves it to the library.  ``auto``: up to
     ``max_tokens`` tokens go to the kernel that streams the weights once, prompts
     whose length suits its tiles to the kernel on pairs of SMs (inside a model
@@ -211,15 +213,16 @@ def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     if T > POLICY["max_tokens"]:
         if (pair_suits(T) and out.dtype == torch.bfloat16 and out.stride(0) % 8 == 0
                 and out.data_ptr() % 16 == 0):
-            gemm_pair(x, w, out)
+            gemm_pair(x, w, out, err=err)
             return True
         if mode != "all":
             return False
-    gemm_tc(x, w, out)
+    gemm_tc(x, w, out, err=err)
     return True
 
 
-def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor) -> bool:
+def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
+                 err: Optional[torch.Tensor] = None) -> bool:
     """The gate/up product with SiLU(gate) * up applied in its epilogue, when
     the policy and the operands allow; ``out`` is [T, I].  Up to 64 tokens go to
     the kernel that streams the weights once (decode), prompts to the kernel on
@@ -233,10 +236,10 @@ def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor
         return False
     T = x.shape[0]
     if T <= min(POLICY["max_tokens"], 64):
-        gemm_tc(x, w_interleaved, out, splits=1, swiglu=True)
+        gemm_tc(x, w_interleaved, out, splits=1, swiglu=True, err=err)
         return True
     if pair_suits(T, fused_activation=True):
-        gemm_pair(x, w_interleaved, out, swiglu=True)
+        gemm_pair(x, w_interleaved, out, swiglu=True, err=err)
         return True
     return False
 

@@ -77,8 +77,8 @@ class Attention(Mixer):
         mats = [weights[self.prefix + n] for n in names]
         if len({m.dtype for m in mats}) != 1:
             raise ConfigError(f"{self.prefix}: q/k/v projections are stored in different dtypes")
-        self.qkv = Linear(torch.cat(mats, dim=0) if len(mats) > 1 else mats[0])
-        self.o = Linear(weights[self.prefix + "o_proj.weight"])
+        self.qkv = Linear(torch.cat(mats, dim=0) if len(mats) > 1 else mats[0], self.rt)
+        self.o = Linear(weights[self.prefix + "o_proj.weight"], self.rt)
 
     def weight_bytes(self) -> int:
         return self.qkv.nbytes + self.o.nbytes

@@ -119,6 +119,15 @@ class Runtime:
     def is_fp32(self) -> bool:
         return self.dtype == torch.float32
 
+    def error_word(self) -> torch.Tensor:
+        """The device error word, made on first use: every kernel of a step is
+        given this one word, and the engine reads it after the step."""
+        if self.err is None:
+            from ..ops import core
+
+            self.err = core.new_error_word(self.device)
+        return self.err
+
 
 # --------------------------------------------------------------------------
 # Part interfaces

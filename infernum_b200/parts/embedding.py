@@ -62,7 +62,7 @@ class LinearHead(Part):
                                              fallback=self.fallback)}
 
     def bind(self, weights) -> None:
-        self.proj = Linear(weights[self.tied_to or self.weight_name])
+        self.proj = Linear(weights[self.tied_to or self.weight_name], self.rt)
 
     def weight_bytes(self) -> int:
         return self.proj.nbytes

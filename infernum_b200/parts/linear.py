@@ -23,14 +23,16 @@ import torch
 from ..errors import KernelError
 from ..ops import core
 
-# Optional hand-written bf16 GEMM routes: callables (x, w, out) -> bool that
+# Optional hand-written bf16 GEMM routes: callables (x, w, out, err) -> bool that
 # return True when they took the product.  Filled by ops modules at import.
-BF16_ROUTES: List[Callable[[torch.Tensor, torch.Tensor, torch.Tensor], bool]] = []
+BF16_ROUTES: List[Callable[..., bool]] = []
 
 
 def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x [M, K] @ w [N, K]^T -> [M, N]`` in ``out_dtype`` (default: x's)."""
+              out: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [M, K] @ w [N, K]^T -> [M, N]`` in ``out_dtype`` (default: x's).
+    ``err``: the device error word in which the package's tensor-core kernels
+    report a wait that ran out (the engine's, so that its check sees it)."""
     core.require_cuda(x, w)
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise KernelError(f"matmul_nt: cannot multiply {tuple(x.shape)} by {tuple(w.shape)}^T")
@@ -46,7 +48,7 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
 
             BF16_ROUTES.append(gemm_tc.route)
         for route in BF16_ROUTES:
-            if route(x, w, out):
+            if route(x, w, out, err):
                 return out
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
@@ -60,10 +62,15 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
 class Linear:
     """A weight and its product; ``parts`` own these, they are not parts."""
 
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, rt=None):
         if weight.dim() != 2:
             raise KernelError("Linear: weight must be [out, in]")
         self.weight = weight.contiguous()
+        self.rt = rt  # the owning part's Runtime: its error word is handed to the kernels
+
+    @property
+    def err(self) -> Optional[torch.Tensor]:
+        return self.rt.error_word() if self.rt is not None else None
 
     @property
     def out_features(self) -> int:
@@ -74,4 +81,4 @@ class Linear:
         return self.weight.numel() * self.weight.element_size()
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        return matmul_nt(x, self.weight, out_dtype)
+        return matmul_nt(x, self.weight, out_dtype, err=self.err)

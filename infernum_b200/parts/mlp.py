@@ -51,11 +51,11 @@ class SwiGLU(FeedForward):
         self.block = None  # None: [all gates | all ups]; 64: interleaved 64 by 64
         if i % 64 == 0:
             fused = torch.stack([gate.view(i // 64, 64, h), up.view(i // 64, 64, h)], dim=1)
-            self.gate_up = Linear(fused.reshape(2 * i, h))
+            self.gate_up = Linear(fused.reshape(2 * i, h), self.rt)
             self.block = 64
         else:
-            self.gate_up = Linear(torch.cat([gate, up], dim=0))
-        self.down = Linear(weights[self.prefix + "down_proj.weight"])
+            self.gate_up = Linear(torch.cat([gate, up], dim=0), self.rt)
+        self.down = Linear(weights[self.prefix + "down_proj.weight"], self.rt)
 
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes + self.down.nbytes
@@ -66,7 +66,7 @@ class SwiGLU(FeedForward):
         if self.block == 64 and x.dtype == torch.bfloat16 and self.gate_up.weight.dtype == torch.bfloat16:
             from ..ops import gemm_tc
 
-            fused = gemm_tc.swiglu_route(x, self.gate_up.weight, act)
+            fused = gemm_tc.swiglu_route(x, self.gate_up.weight, act, self.gate_up.err)
         if not fused:
             core.silu_mul(self.gate_up(x), act, block=self.block)
         return self.down(act)

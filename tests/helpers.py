@@ -238,3 +238,50 @@ def peak_tokens(steps: List[dict]) -> int:
         for rid in s.get("end", []):
             held.pop(rid, None)
     return peak
+
+
+# --------------------------------------------------------------------------
+# generated tokens
+# --------------------------------------------------------------------------
+TIE = {"float32": 1e-4, "bfloat16": 5e-2}
+
+
+def assert_same_up_to_ties(folder_or_plain, prompt: Sequence[int], got: Sequence[int], want: Sequence[int],
+                           dtype: str, sampling=None) -> int:
+    """Two token lists for one request must be equal, up to the first step that
+    the plain implementation calls a near-tie: two runs that went through
+    different kernels or batches may round such a step differently, and nothing
+    after it can be compared.  Everything before it is.
+
+    Greedy: at the first difference the two tokens' plain logits differ by less
+    than ``TIE[dtype]`` of the largest logit.  Sampled (``sampling`` has
+    temperature, top_p, seed, repetition_penalty and its window): the step's
+    uniform number lies within ``TIE[dtype]`` of the interval that the plain
+    distribution gives to the token that was got.  Returns the number of
+    tokens that were compared and equal."""
+    got, want = list(got), list(want)
+    if got == want:
+        return len(got)
+    i = next((k for k in range(min(len(got), len(want))) if got[k] != want[k]), None)
+    assert i is not None, f"lengths differ: {len(got)} against {len(want)} tokens"
+    plain = folder_or_plain if isinstance(folder_or_plain, Plain) else Plain(folder_or_plain)
+    seq = list(prompt) + want[:i]
+    logits = plain.logits(seq)[-1]
+    limit = TIE[dtype]
+    if sampling is None:
+        gap = float((logits[want[i]] - logits[got[i]]).abs() / logits.abs().max())
+        assert gap < limit, (f"token {i}: {got[i]} against {want[i]}, whose plain logits differ by {gap:.4f} "
+                             f"of the largest: no near-tie")
+        return i
+    w = sampling.repetition_penalty_window
+    recent = seq[len(seq) - w:] if w else []
+    probs = plain_llama.sample_probabilities(logits, sampling.temperature, sampling.top_p,
+                                             sampling.repetition_penalty, recent)
+    u = plain_llama.uniform_number(sampling.seed, i)
+    cdf = torch.cumsum(probs, dim=0)
+    hi = float(cdf[got[i]])
+    lo = hi - float(probs[got[i]])
+    away = max(lo - u, u - hi, 0.0)
+    assert away < limit, (f"sampled token {i}: {got[i]} against {want[i]}; u = {u:.4f} lies {away:.4f} away from "
+                          f"the plain interval [{lo:.4f}, {hi:.4f}) of the token that was got")
+    return i

@@ -229,6 +229,26 @@ def sample_index_order(probs: torch.Tensor, u: float) -> int:
     return last
 
 
+def uniform_number(seed: int, n_generated: int) -> float:
+    """The uniform number of a request's next token: state = seed ^ tokens
+    generated so far (infernum-runtime/src/engine.rs:283,406), one xorshift64
+    round (engine.rs:491-494), then + 1 and four more rounds, u = state / 2^64
+    (infernum-cuda/src/inner/cuda/ops/sample.rs:143-149)."""
+    mask = (1 << 64) - 1
+
+    def xorshift(s: int) -> int:
+        s ^= (s << 13) & mask
+        s ^= s >> 7
+        s ^= (s << 17) & mask
+        return s & mask
+
+    s = xorshift((int(seed) ^ int(n_generated)) & mask)
+    s = (s + 1) & mask
+    for _ in range(4):
+        s = xorshift(s)
+    return s / float(1 << 64)
+
+
 def greedy_generate(cfg: dict, weights: Dict[str, torch.Tensor], prompt: Sequence[int],
                     n_new: int, dtype=torch.float64) -> List[int]:
     """Recomputes the whole sequence for every new token."""

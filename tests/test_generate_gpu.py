@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_llama as pl
-from helpers import CONFIGS, ROOT, make_model_folder, random_tokens
+from helpers import CONFIGS, ROOT, Plain, assert_same_up_to_ties, make_model_folder, random_tokens
 
 pytestmark = pytest.mark.gpu
 
@@ -36,22 +36,6 @@ def plain_greedy_with_margin(folder, prompt, n):
     return out, margin
 
 
-def assert_same_up_to_ties(folder, prompt, got, want, dtype):
-    """Token lists must be equal.  In bfloat16 two runs that went through
-    different kernels (a recomputed prompt against decoded tokens) may round a
-    near-tie differently: then the first difference must be such a near-tie by
-    the plain implementation's logits, and nothing after it is compared."""
-    if got == want:
-        return
-    assert dtype == "bfloat16", "float32 runs must agree token for token"
-    assert len(got) == len(want)
-    i = next(k for k in range(len(got)) if got[k] != want[k])
-    cfg, w = pl.read_config(folder), pl.read_weights(folder)
-    logits = pl.forward(cfg, w, list(prompt) + want[:i])[-1]
-    gap = float((logits[want[i]] - logits[got[i]]).abs() / logits.abs().max())
-    assert gap < 5e-2, f"token {i}: {got[i]} vs {want[i]} differ by {gap:.3f} of the largest logit"
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_equals_plain(folders, name, dtype):
@@ -66,15 +50,15 @@ def test_greedy_generation_equals_plain(folders, name, dtype):
     n_new = {"A": 16, "B": 24}[name]
     opts = ib.GenerateOptions(max_new_tokens=n_new)
     got_batch = engine.generate_batch(prompts, opts)
+    plain = Plain(folders[name])
+    compared = 0
     for p, got in zip(prompts, got_batch):
-        want, margin = plain_greedy_with_margin(folders[name], p, n_new)
-        # compare up to the first step whose top-2 gap is within the dtype's noise
-        limit = 1e-4 if dtype == "float32" else 5e-2
-        if margin > limit:
-            assert got == want
-        else:
-            assert got[:4] == want[:4] or margin < limit
+        want, _ = plain_greedy_with_margin(folders[name], p, n_new)
+        # token for token, up to the first step at which the engine took another token; that
+        # step must be a near-tie by the plain logits (within the dtype's noise)
+        compared += assert_same_up_to_ties(plain, p, got, want, dtype)
         assert engine.generate(p, opts) == got  # alone equals batched
+    assert compared >= (len(prompts) * n_new if dtype == "float32" else n_new)
     assert engine.cache.free_pages() == [64] and engine.cache.num_free_slots == 4
 
 
@@ -133,10 +117,7 @@ def test_preemption_leaves_output_unchanged(folders, dtype):
     got = tight.generate_batch(prompts, opts)
     assert tight.stats.preemptions > 0
     for p, o, g, w in zip(prompts, opts, got, want):
-        if o.sampling is None:
-            assert_same_up_to_ties(folders["A"], p, g, w, dtype)
-        else:
-            assert g == w or dtype == "bfloat16"  # sampled: the same random numbers, logits within rounding
+        assert_same_up_to_ties(folders["A"], p, g, w, dtype, sampling=o.sampling)
     assert tight.cache.free_pages() == [24]
 
 
@@ -214,10 +195,15 @@ def test_decode_steps_planned_ahead_survive_ends_and_arrivals(folders, dtype):
     engine.run_until_done([h0, h1, h3])
     assert engine.stats.ahead_used > 10 and engine.stats.ahead_voided >= 2
     assert h3.finish_reason == ib.FinishReason.LENGTH and len(h3.tokens) == 12 and len(h1.tokens) == 30
-    if dtype == "float32":  # token for token; in bfloat16 the solo engine may round a near-tie otherwise
+    # token for token; in bfloat16 the solo engine may round a near-tie otherwise, and what comes
+    # after such a step is not compared
+    plain = Plain(folders["B"])
+    assert_same_up_to_ties(plain, prompts[0], h0.tokens, alone[0][: len(h0.tokens)], dtype)
+    if dtype == "float32":
         assert h0.tokens == alone[0][: alone[0].index(stop)] and h0.finish_reason == ib.FinishReason.STOP
-        assert h1.tokens == alone[1] and h3.tokens == alone[3]
-        assert h2.tokens == alone[2][: len(h2.tokens)]
+    assert_same_up_to_ties(plain, prompts[1], h1.tokens, alone[1], dtype, sampling=sampled)
+    assert_same_up_to_ties(plain, prompts[2], h2.tokens, alone[2][: len(h2.tokens)], dtype)
+    assert_same_up_to_ties(plain, prompts[3], h3.tokens, alone[3], dtype)
     engine.step()
     assert engine.cache.free_pages() == [96] and engine.cache.num_free_slots == 4
 
@@ -260,11 +246,12 @@ def test_decode_steps_launched_ahead_of_their_tokens(folders, dtype):
     assert on_stats.ahead_launched > 20 and off_stats.ahead_launched == 0
     assert on_reasons == off_reasons == [ib.FinishReason.STOP, ib.FinishReason.LENGTH,
                                          ib.FinishReason.CANCELLED, ib.FinishReason.LENGTH]
-    assert [len(t) for t in on] == [len(t) for t in off] or dtype == "bfloat16"
-    if dtype == "float32":  # token for token; in bfloat16 a near-tie may round otherwise in another batch
+    if dtype == "float32":  # token for token
         assert on == off
-    else:
-        assert_same_up_to_ties(folders["B"], prompts[3], on[3], off[3], dtype)
+    plain = Plain(folders["B"])  # in bfloat16 a near-tie may round otherwise in another batch
+    for k, samp in enumerate([None, sampled, None, None]):
+        n = min(len(on[k]), len(off[k]))  # (a request that was cancelled or stopped may have ended a token apart)
+        assert_same_up_to_ties(plain, prompts[k], on[k][:n], off[k][:n], dtype, sampling=samp)
 
 
 def test_stream_that_ends_on_a_stop_token_leaves_no_step_behind(folders):
@@ -353,9 +340,9 @@ def test_steps_of_decoded_tokens_beside_one_prompt_portion_run_from_graphs(folde
     mixed = [k for k, s in engine.decoder._slots.items() if k[4] > 0]
     assert mixed and all(k[4] >= 56 for k in mixed)
     assert any(engine.decoder._slots[k].graph is not None for k in mixed)
+    plain = Plain(folders["B"])
     for p, h, want in zip(short + [long], handles, alone):
-        if dtype == "float32" or h.seq.options.sampling is None:
-            assert_same_up_to_ties(folders["B"], p, h.tokens, want, dtype)
+        assert_same_up_to_ties(plain, p, h.tokens, want, dtype, sampling=h.seq.options.sampling)
     assert engine.cache.free_pages() == [128]
 
 
@@ -394,3 +381,24 @@ def test_a_request_admitted_again_does_not_inherit_its_old_block_table(folders):
     again = cache.admit("a")             # the same id, other pages, the same number of them
     prefill_and_decode(again)
     assert len(again.tables[0]) == len(old_pages) and set(again.tables[0]).isdisjoint(old_pages)
+
+
+def test_a_product_whose_wait_ran_out_surfaces_from_engine_step(folders):
+    """The engine reads one device word after every step.  A bit that a matrix
+    product sets there (here set from the host: no kernel has to misbehave)
+    ends the step with a KernelError that names the product and the wait."""
+    import infernum_b200 as ib
+    from infernum_b200.ops import core
+    for graphs in (True, False):
+        model = ib.load_model(folders["B"], dtype="bfloat16")
+        engine = ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=8, num_blocks=32, cuda_graphs=graphs))
+        prompt = random_tokens(9, 320, 3)
+        engine.generate(prompt, ib.GenerateOptions(max_new_tokens=4))  # graphs recorded, nothing reported
+        site = core.TIMEOUT_SITES.index("product for few tokens: MMA issuer")
+        engine.submit(prompt, ib.GenerateOptions(max_new_tokens=8))
+        engine.step()
+        model.rt.err.fill_(core.FLAG_WAIT_TIMEOUT | (1 << (8 + site)))
+        with pytest.raises(ib.KernelError, match="product for few tokens: MMA issuer"):
+            for _ in range(4):
+                engine.step()
+        assert int(model.rt.err.item()) == 0  # reported once, then cleared

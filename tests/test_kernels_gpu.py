@@ -227,10 +227,13 @@ def test_sample_distribution_over_many_draws():
 # --------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------
-def paged_case(seqs_len, q_rows, nh, nkv, hd, ps, dtype, seed, extra_pages=5, scale_key=None):
+def paged_case(seqs_len, q_rows, nh, nkv, hd, ps, dtype, seed, extra_pages=5, scale_key=None, poison=False):
     """Requests with ``seqs_len[i]`` cached+new tokens of which the last
     ``q_rows[i]`` are this step's rows.  Pages are handed out in a shuffled
-    order.  Returns what the kernels take plus the plain result."""
+    order.  Returns what the kernels take plus the plain result.  ``poison``:
+    every slot of the pools that holds no key of a request - the rest of a
+    request's last page, pages nobody holds (page 0 among them) - is NaN, as a
+    request that went wrong might have left them."""
     g = torch.Generator().manual_seed(seed)
     E = len(seqs_len)
     n_pages = sum(-(-L // ps) for L in seqs_len) + extra_pages
@@ -239,6 +242,10 @@ def paged_case(seqs_len, q_rows, nh, nkv, hd, ps, dtype, seed, extra_pages=5, sc
     tables = torch.full((E, MB), -1, dtype=torch.int32)
     kp = torch.randn(n_pages, nkv, ps, hd, generator=g).to(dtype)  # stale data in unused slots
     vp = torch.randn(n_pages, nkv, ps, hd, generator=g).to(dtype)
+    if poison:
+        perm.remove(0)  # nobody holds page 0, which kernels may fetch in place of a missing table entry
+        kp.fill_(float("nan"))
+        vp.fill_(float("nan"))
     qs, refs, positions, row_entry, cu, q_start = [], [], [], [], [0], []
     for e, (L, n) in enumerate(zip(seqs_len, q_rows)):
         k = torch.randn(L, nkv, hd, generator=g).to(dtype)
@@ -586,13 +593,17 @@ TC_CASES = [
 ]
 
 
+@pytest.mark.parametrize("poison", [False, True], ids=["stale", "nan"])
 @pytest.mark.parametrize("case", TC_CASES, ids=[f"nh{c[0]}kv{c[1]}hd{c[2]}ps{c[3]}r{max(c[5])}" for c in TC_CASES])
-def test_attention_tcgen05_against_plain(case):
+def test_attention_tcgen05_against_plain(case, poison):
+    """``poison``: what pages hold beyond a request's last key, and pages it does
+    not hold, are NaN (values only, nothing faults): masked keys have P = 0, but
+    0 x NaN is NaN in the product P V unless those rows of V are cleared."""
     from infernum_b200.ops import attention_fast
     from infernum_b200.parts.base import Runtime
     nh, nkv, hd, ps, lens, rows = case
     c = core()
-    q, kp, vp, tables, ctx, refs = paged_case(lens, rows, nh, nkv, hd, ps, torch.bfloat16, 11)
+    q, kp, vp, tables, ctx, refs = paged_case(lens, rows, nh, nkv, hd, ps, torch.bfloat16, 11, poison=poison)
     # queries sit in rows as wide as the fused qkv rows of the engine
     wide = torch.zeros(q.shape[0], (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device=DEV)
     wide[:, : nh * hd] = q
@@ -628,7 +639,7 @@ def test_attention_tcgen05_with_key_slices(nh, nkv, hd, ps, lens, rows, splits):
     c = core()
     for far in (None, 0, 33, -1):
         q, kp, vp, tables, ctx, refs = paged_case(lens, rows, nh, nkv, hd, ps, torch.bfloat16, 17,
-                                                  scale_key=far)
+                                                  scale_key=far, poison=(far == 33))
         wide = torch.zeros(q.shape[0], (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device=DEV)
         wide[:, : nh * hd] = q
         outs = []
@@ -681,6 +692,12 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
     assert flags & c.FLAG_WAIT_TIMEOUT
     assert "prompt attention: MMA issuer" in c.describe_flags(flags)
     assert "a device-side wait ran out" in c.describe_flags(flags)
+    # a wait of a matrix product is named the same way
+    err.zero_()
+    c.wait_probe(err, 30.0, c.TIMEOUT_SITES.index("product on SM pairs: epilogue"))
+    torch.cuda.synchronize()
+    assert "product on SM pairs: epilogue" in c.describe_flags(int(err.item()))
+    assert "prompt attention" not in c.describe_flags(int(err.item()))
     with pytest.raises(KernelError):
         c.wait_probe(err, 5000.0, 0)  # longer than a second is refused
     x = torch.randn(4, 64).to(DEV)

@@ -236,3 +236,41 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(dtype):
     runner.check_errors()
     got = torch.cat(rows)
     assert rel_err(got, plain_shared_schedule(W, tokens)) < (2e-5 if dtype == torch.float32 else 4e-2)
+
+
+def test_products_report_into_the_runtimes_error_word(monkeypatch):
+    """The tensor-core products report a wait that ran out in the device word
+    they are handed.  Every product of a part must be handed the word of the
+    part's Runtime (the one the engine reads after a step), not one of their
+    own: the calls are watched at the C boundary, for both kernels, with and
+    without the activation in the epilogue."""
+    from infernum_b200.ops import gemm_tc
+    from infernum_b200.parts import FEED_FORWARDS
+    from infernum_b200.parts.linear import Linear
+    rt = runtime(torch.bfloat16)
+    seen = {"few": [], "pair": []}
+    few, pair = gemm_tc.lib(), gemm_tc.pair_lib()
+    real_few, real_pair = few.ib_gemm_tc, pair.ib_gemm_pair
+
+    def spy_few(*args):
+        seen["few"].append(args[12])
+        return real_few(*args)
+
+    def spy_pair(*args):
+        seen["pair"].append(args[15])
+        return real_pair(*args)
+
+    monkeypatch.setattr(few, "ib_gemm_tc", spy_few)
+    monkeypatch.setattr(pair, "ib_gemm_pair", spy_pair)
+    lin = Linear(torch.randn(160, 96, device=DEV).to(torch.bfloat16), rt)
+    lin(torch.randn(5, 96, device=DEV).to(torch.bfloat16))          # few tokens
+    lin(torch.randn(768, 96, device=DEV).to(torch.bfloat16))        # a prompt: pairs of SMs
+    ffn = FEED_FORWARDS.get("swiglu")({"hidden_size": 96, "intermediate_size": 256, "prefix": "m."}, rt)
+    ffn.bind(weights_for(ffn, torch.bfloat16))
+    ffn.forward(torch.randn(3, 96, device=DEV).to(torch.bfloat16))    # activation in the epilogue, few tokens
+    ffn.forward(torch.randn(512, 96, device=DEV).to(torch.bfloat16))  # and on pairs of SMs
+    torch.cuda.synchronize()
+    word = rt.err.data_ptr()
+    assert len(seen["few"]) >= 3 and len(seen["pair"]) >= 2
+    assert set(seen["few"]) == {word} and set(seen["pair"]) == {word}
+    assert int(rt.err.item()) == 0
