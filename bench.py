@@ -17,7 +17,14 @@ line is printed:
   roofline   bytes a decode step must read (every weight once, the cache of
              the live requests) / its time, against the measured copy bandwidth
   points     decode tokens/s at batch 1 and at batch 64 (1,024-token prompts), and
-             at batch 8 near the end of an 8,192-token context
+             at batch 8 near the end of an 8,192-token context; and two runs
+             through the scheduler at other layer sizes, each with a model of its
+             own made after the headline runs: the Llama-3.2-1B sizes under a
+             mixed workload (64 requests, prompts of 16 to 4,096 tokens fed 512
+             at a time beside decoding requests, temperature 0.8), and the
+             Llama-2-13B sizes with a page pool of 0.8 of the need, so that
+             requests are preempted and recomputed (``pressure_13b_*``; some of
+             them, the preempted ones first, are run again alone and compared)
 
 Weights (15 GB) and cache are far larger than the 126 MB L2, so every timed
 step streams its inputs from HBM; no L2 flush is needed between steps.
@@ -278,6 +285,61 @@ def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3):
             "frac_of_burst": flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
 
 
+def scheduler_workloads(seed: int) -> dict:
+    """The mixed workload at the 1B layer sizes and the page-pressure workload at
+    the 13B layer sizes, through ``Engine`` (``infernum_b200.cli.bench``), as
+    flat entries for ``points``."""
+    import gc
+    from types import SimpleNamespace
+
+    import torch
+
+    from infernum_b200.cli import bench as cli
+
+    out = {}
+    base = dict(dtype="bf16", layers=None, seed=seed, block_size=16, requests=None, prompt_len=None,
+                new_tokens=None, num_blocks=None, no_warmup=False, n_gen=128)
+    args = SimpleNamespace(model="1b", workload="mixed", **base)
+    model = cli.load(args)
+    r = cli.run_mixed(model, args)
+    out.update({"mixed_1b_tok_s": round(r["total_tok_s"], 1), "mixed_1b_decode_tok_s": round(r["decode_tok_s"], 1),
+                "mixed_1b_prefill_tokens": r["prefill_tokens"], "mixed_1b_decode_tokens": r["decode_tokens"],
+                "mixed_1b_steps": r["steps"], "mixed_1b_budget_use": round(r["budget_use"], 3),
+                "mixed_1b_preemptions": r["preemptions"]})
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    args = SimpleNamespace(model="13b", workload="pressure", solo_checks=4, **base)
+    model = cli.load(args)
+    r = cli.run_pressure(model, args)
+    out.update({"pressure_13b_tok_s": round(r["total_tok_s"], 1), "pressure_13b_decode_tok_s": round(r["decode_tok_s"], 1),
+                "pressure_13b_layers": len(model.layers), "pressure_13b_num_blocks": r["num_blocks"],
+                "pressure_13b_blocks_for_all": r["blocks_for_all"], "pressure_13b_preemptions": r["preemptions"],
+                "pressure_13b_requests_preempted": r["requests_preempted"],
+                "pressure_13b_solo_checked": r["solo_checked"],
+                "pressure_13b_identical_to_solo": r["identical_to_solo"],
+                "pressure_13b_first_difference_at": ",".join(str(i) for i in r["first_difference_at"]),
+                # (bfloat16, random weights: a differing token must be a near-tie by the logits)
+                "pressure_13b_largest_gap_at_difference": max(r["logit_gap_at_first_difference"] + [0.0])})
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    # the same in true 32-bit, where a preempted request must reproduce its tokens exactly
+    # (four layers and eight requests: the 32-bit products run on the FMA units)
+    args = SimpleNamespace(model="13b", workload="pressure", solo_checks=4,
+                           **dict(base, dtype="f32", layers=4, requests=8))
+    model = cli.load(args)
+    r = cli.run_pressure(model, args)
+    out.update({"pressure_13b_f32_layers": 4, "pressure_13b_f32_requests": 8,
+                "pressure_13b_f32_preemptions": r["preemptions"],
+                "pressure_13b_f32_solo_checked": r["solo_checked"],
+                "pressure_13b_f32_identical_to_solo": r["identical_to_solo"]})
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -329,9 +391,11 @@ def main() -> int:
     clocks = ClockSampler(0)
     clocks.start()
     try:
-        # the prompt step first: it is bound by arithmetic and so by the SM clock, which sags
-        # under the power cap once the decode runs have heated the part; decode is bound by HBM
-        prefill = None if args.skip_extras else time_prefill(model, cfg, layers, 2048, args.page_size, peaks)
+        # The prompt step is bound by arithmetic and so by the SM clock, which sags under the
+        # power cap once the decode runs have heated the part (decode is bound by HBM): it is
+        # timed here, on the cool part, and again after the decode runs; the line carries the
+        # later, slower figure and names the earlier one beside it.
+        cool = None if args.skip_extras else time_prefill(model, cfg, layers, 2048, args.page_size, peaks)
         main_run = time_decode(model, args.batch, args.prompt_len, args.steps, warmup, args.page_size,
                                args.seed, clocks)
         e2e = time_e2e(model, args.batch, args.prompt_len, args.steps, warmup, args.page_size, args.seed + 1)
@@ -354,6 +418,19 @@ def main() -> int:
             points["decode_b8_ctx8k"] = round(r["tokens_per_s"], 1)
             points["decode_b8_ctx8k_hbm_frac"] = round(
                 r["bytes_per_step"] / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        prefill = None
+        if cool is not None:
+            prefill = time_prefill(model, cfg, layers, 2048, args.page_size, peaks)
+            prefill.update({"when": "after the decode runs", "ms_cool": cool["ms"], "frac_cool": cool["frac"],
+                            "value_cool": cool["value"]})
+        libraries = [os.path.basename(p) for p in loaded_libraries()]
+        if not args.skip_extras and not args.layers:
+            del model
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            points.update(scheduler_workloads(args.seed))
     finally:
         clocks.stop()
 
@@ -388,7 +465,7 @@ def main() -> int:
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                      "peaks": peaks["source"]},
         "points": points,
-        "kernel_libraries": [os.path.basename(p) for p in loaded_libraries()],
+        "kernel_libraries": libraries,
     }
     if prefill is not None:
         line["prefill"] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in prefill.items()}

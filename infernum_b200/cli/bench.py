@@ -74,6 +74,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--solo-checks", type=int, default=None,
+                    help="pressure: compare only so many requests with their run alone (preempted ones first)")
     ap.add_argument("--no-warmup", action="store_true",
                     help="mixed: time the first pass too (it records the decode graphs)")
     ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
@@ -163,8 +165,10 @@ def run_mixed(model, args) -> dict:
             "generated": sum(len(o) for o in outs), "seconds": dt,
             "total_tok_s": (sum(lens) + sum(len(o) for o in outs)) / dt,
             "decode_tok_s": sum(len(o) for o in outs) / dt, "steps": st.steps,
+            "prefill_tokens": st.prefill_tokens, "decode_tokens": st.decode_tokens,
             "tokens_per_step": (st.prefill_tokens + st.decode_tokens) / max(st.steps, 1),
-            "preemptions": st.preemptions}
+            "budget_use": (st.prefill_tokens + st.decode_tokens) / max(st.steps, 1) / (512 + n_req),
+            "host_seconds": st.step_seconds, "preemptions": st.preemptions}
 
 
 def run_pressure(model, args) -> dict:
@@ -186,26 +190,50 @@ def run_pressure(model, args) -> dict:
     tight = ib.Engine(model, ib.BatchConfig(num_blocks=blocks, **cfg))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    outs = tight.generate_batch(prompts, opts)
+    handles = [tight.submit(p, opts) for p in prompts]
+    tight.run_until_done(handles)
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    outs = [h.tokens for h in handles]
     preemptions = tight.stats.preemptions
+    preempted = [i for i, h in enumerate(handles) if h.seq.preemptions > 0]
+    st = tight.stats
     del tight
     torch.cuda.empty_cache()
-    # every request alone, with room: the yardstick
+    # requests alone, with room: the yardstick (those that were preempted first)
+    order = preempted + [i for i in range(n_req) if i not in preempted]
+    checks = order if getattr(args, "solo_checks", None) is None else order[: args.solo_checks]
     solo = ib.Engine(model, ib.BatchConfig(num_blocks=per_req + 2, **dict(cfg, max_batch_size=1)))
-    same, first_diff = 0, []
-    for p, o in zip(prompts, outs):
-        want = solo.generate(p, opts)
-        if want == o:
+    same, first_diff, gaps = 0, [], []
+    for i in checks:
+        want = solo.generate(prompts[i], opts)
+        if want == outs[i]:
             same += 1
-        else:
-            first_diff.append(next(i for i in range(len(o)) if o[i] != want[i]))
+            continue
+        k = next(k for k in range(len(want)) if outs[i][k] != want[k])
+        first_diff.append(k)
+        # how far apart the two tokens are by the engine's own logits at that step, as a
+        # fraction of the largest: rounding can only turn a near-tie
+        from ..engine.step import StepEntry
+
+        rc = solo.cache.admit(("gap", i))
+        seq, pos, logits = prompts[i] + want[:k], 0, None
+        while pos < len(seq):
+            n = min(2048, len(seq) - pos)
+            logits = solo.runner.step([StepEntry(rc, seq[pos: pos + n], [n - 1] if pos + n == len(seq) else [])])
+            pos += n
+        row = logits[0].float()
+        gaps.append(float((row[want[k]] - row[outs[i][k]]).abs() / row.abs().max()))
+        solo.cache.release(rc)
     return {"workload": "pressure", "requests": n_req, "num_blocks": blocks,
             "blocks_for_all": n_req * per_req, "preemptions": preemptions,
+            "requests_preempted": len(preempted), "prefill_tokens": st.prefill_tokens,
+            "decode_tokens": st.decode_tokens, "steps": st.steps,
             "generated": sum(len(o) for o in outs), "seconds": dt,
-            "decode_tok_s": sum(len(o) for o in outs) / dt, "identical_to_solo": same,
-            "first_difference_at": first_diff}
+            "total_tok_s": (st.prefill_tokens + st.decode_tokens) / dt,
+            "decode_tok_s": sum(len(o) for o in outs) / dt, "solo_checked": len(checks),
+            "identical_to_solo": same, "first_difference_at": first_diff,
+            "logit_gap_at_first_difference": [round(g, 4) for g in gaps]}
 
 
 def main(argv: Optional[List[str]] = None) -> int:

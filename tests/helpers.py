@@ -78,9 +78,12 @@ def random_tokens(n: int, vocab: int, seed: int) -> List[int]:
 class Plain:
     """The plain implementation over a model folder, logits cached by sequence."""
 
-    def __init__(self, folder: str):
-        self.cfg = plain_llama.read_config(folder)
-        self.weights = plain_llama.read_weights(folder)
+    def __init__(self, folder: Optional[str], config: Optional[dict] = None,
+                 weights: Optional[Dict[str, torch.Tensor]] = None):
+        """From a model folder, or from a config.json dict and CPU tensors by
+        checkpoint name."""
+        self.cfg = plain_llama.read_config(folder if folder is not None else config)
+        self.weights = plain_llama.read_weights(folder) if folder is not None else weights
         self._cache: Dict[tuple, torch.Tensor] = {}
 
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:

@@ -274,3 +274,21 @@ def test_products_report_into_the_runtimes_error_word(monkeypatch):
     assert len(seen["few"]) >= 3 and len(seen["pair"]) >= 2
     assert set(seen["few"]) == {word} and set(seen["pair"]) == {word}
     assert int(rt.err.item()) == 0
+
+
+def test_random_weights_are_the_same_on_the_device_and_in_a_written_folder(tmp_path):
+    """A model drawn on the GPU from a configuration and a seed and the folder
+    written for the same configuration and seed hold the same values bit for
+    bit, so what was measured on one can be checked with the plain
+    implementation on the other."""
+    from helpers import TINY_B
+    from infernum_b200.weights.random_init import model_specs_for, random_tensors, write_random_model
+    folder = write_random_model(str(tmp_path / "m"), TINY_B, seed=21)
+    stored = pl.read_weights(folder)
+    _, _, specs = model_specs_for(TINY_B)
+    drawn = random_tensors(specs, 21, DEV, torch.bfloat16)
+    assert set(stored) == set(drawn)
+    for name, t in drawn.items():
+        assert torch.equal(t.cpu(), stored[name]), name
+    other = random_tensors(specs, 22, DEV, torch.bfloat16)
+    assert not torch.equal(other["model.embed_tokens.weight"], drawn["model.embed_tokens.weight"])
