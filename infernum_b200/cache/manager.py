@@ -82,14 +82,19 @@ class CacheManager:
                  dtype: torch.dtype = torch.bfloat16, device=None):
         """``needs``: one item per schedule position with attributes
         ``paged`` (PagedCacheSpec or None), ``state`` (StateSpec or None) and
-        ``cache_of`` (an earlier position or None).  ``num_pages`` is the size
-        of every group's pool."""
+        ``cache_of`` (an earlier position or None).  ``num_pages`` sizes the
+        groups' pools: one number for all of them, a sequence with one number
+        per group (groups are numbered in the order in which the schedule first
+        needs them), or a function of the group's ``PagedCacheSpec`` - a group
+        whose window lets it give pages back early, or whose keys are small,
+        needs fewer or cheaper pages than one that keeps everything."""
         if page_size <= 0:
             raise CacheError("page_size must be positive")
         if max_requests <= 0:
             raise CacheError("max_requests must be positive")
         self.page_size = int(page_size)
-        self.num_pages = int(num_pages)
+        self._pages_arg = num_pages
+        self.group_pages: List[int] = []
         self.max_requests = int(max_requests)
         self.dtype = dtype
         self.device = device
@@ -103,7 +108,6 @@ class CacheManager:
         # num_pages, never handed out), belong to no request: rows that only pad
         # a batch to a fixed size write there.
         self.pad_slot = self.max_requests
-        self.pad_page = self.num_pages
 
         group_of_spec: Dict[PagedCacheSpec, int] = {}
         for need in needs:
@@ -117,11 +121,13 @@ class CacheManager:
                 if g is None:
                     g = len(self.groups)
                     group_of_spec[need.paged] = g
-                    self.groups.append(CacheGroup(need.paged, [], PagePool(self.num_pages)))
+                    self.group_pages.append(self._pages_of_group(g, need.paged))
+                    self.groups.append(CacheGroup(need.paged, [], PagePool(self.group_pages[g])))
                 self.groups[g].positions.append(need.position)
-                lc.group, lc.page_size, lc.num_pages = g, self.page_size, self.num_pages + 1
+                pages = self.group_pages[g]
+                lc.group, lc.page_size, lc.num_pages = g, self.page_size, pages + 1
                 if device is not None:
-                    shape = (self.num_pages + 1, need.paged.kv_heads, self.page_size, need.paged.head_dim)
+                    shape = (pages + 1, need.paged.kv_heads, self.page_size, need.paged.head_dim)
                     lc.k_pool = torch.zeros(shape, dtype=dtype, device=device)
                     lc.v_pool = torch.zeros(shape, dtype=dtype, device=device)
             if need.state is not None and need.cache_of is None:
@@ -131,13 +137,56 @@ class CacheManager:
                     self._state_tensors.append(lc.state)
             self.layer_caches.append(lc)
 
+        if not isinstance(self._pages_arg, int) and not callable(self._pages_arg) \
+                and len(self._pages_arg) != len(self.groups):
+            raise CacheError(f"num_pages names {len(self._pages_arg)} pools, the model has "
+                             f"{len(self.groups)} cache groups")
+
+    def _pages_of_group(self, g: int, spec: PagedCacheSpec) -> int:
+        arg = self._pages_arg
+        if callable(arg):
+            n = arg(spec)
+        elif isinstance(arg, int):
+            n = arg
+        else:
+            if g >= len(arg):
+                raise CacheError(f"num_pages names {len(arg)} pools, the model has more cache groups")
+            n = arg[g]
+        if int(n) <= 0:
+            raise CacheError(f"cache group {g}: a pool needs at least one page, got {n}")
+        return int(n)
+
     # ---- sizes --------------------------------------------------------------
     def pages_for(self, tokens: int) -> int:
         return (tokens + self.page_size - 1) // self.page_size
 
     @property
-    def max_blocks_per_request(self) -> int:
+    def num_pages(self) -> int:
+        """The size of the smallest pool (all pools, when one number sized them)."""
+        return min(self.group_pages) if self.group_pages else (
+            self._pages_arg if isinstance(self._pages_arg, int) else 0)
+
+    @property
+    def pad_page(self) -> int:
+        """The page behind the pool that padding rows write to, when every pool
+        has the same size (``pad_pages`` gives it per group)."""
         return self.num_pages
+
+    def peak_pages(self, total_tokens: int, step_tokens: int) -> List[int]:
+        """Per group, the most pages a request of ``total_tokens`` cached tokens
+        holds at any time when it is fed at most ``step_tokens`` a step: all of
+        its pages, or, in a group with a window, those the window and one step
+        reach (older ones are given back at every commit)."""
+        out = []
+        for g in self.groups:
+            need = self.pages_for(total_tokens)
+            if g.spec.window > 0:
+                need = min(need, self.pages_for(g.spec.window + step_tokens) + 1)
+            out.append(need)
+        return out
+
+    def could_ever_hold(self, total_tokens: int, step_tokens: int) -> bool:
+        return all(n <= p for n, p in zip(self.peak_pages(total_tokens, step_tokens), self.group_pages))
 
     def bytes_per_token(self) -> int:
         """Cache bytes one token occupies over all groups and members."""
@@ -156,7 +205,7 @@ class CacheManager:
 
     def pad_pages(self) -> List[int]:
         """Per group, the page that padding rows write to."""
-        return [self.pad_page] * len(self.groups)
+        return list(self.group_pages)
 
     # ---- a request's life ---------------------------------------------------
     def admit(self, request_id) -> RequestCache:

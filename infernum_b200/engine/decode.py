@@ -39,7 +39,6 @@ import torch
 from ..cache.manager import RequestCache
 from ..ops import core
 from ..errors import CacheError
-from ..ops.attention_fast import SM_COUNT_FALLBACK, choose_splits
 from .step import ModelRunner, StepContext
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
@@ -128,14 +127,14 @@ class DecodeRunner:
             ints = torch.zeros((4, size), dtype=torch.int32, device=dev)
             host_ints = torch.zeros((4, size), dtype=torch.int32).pin_memory()
             tables = torch.full((G, size, self.MB), -1, dtype=torch.int32, device=dev)
-            kv_heads = max([g.spec.kv_heads for g in self.cache.groups] + [1])
-            sm = self.rt.options.get("sm_count") or SM_COUNT_FALLBACK
             ctx = StepContext(
                 n_rows=size, n_entries=size, token_ids=ints[0], positions=ints[1], row_entry=arange[:size],
                 cu_rows=arange, q_start=ints[1], kv_len=ints[2], slot_ids=ints[3], logit_rows=arange[:size],
                 block_tables=[tables[g] for g in range(G)], host_cu_rows=list(range(size + 1)),
                 host_kv_len=[], max_rows_per_entry=1, max_kv_len=kv_cap, all_decode=True)
-            ctx.attention_mode = (2, choose_splits(size, kv_heads, kv_cap, sm))
+            # (how a mixer spreads these rows over its kernels is the mixer's to decide: it sees
+            # one row per entry and the longest cache the recorded step may meet, ``max_kv_len``,
+            # and keeps its plan in ``ctx.scratch``, which lives as long as the recording)
         else:
             # `size` decoded tokens (one row and one entry each), then one prompt portion of
             # `portion` rows as the last entry.  One flat buffer holds what changes from step

@@ -66,7 +66,7 @@ class BatchConfig:
     max_batch_size: int = 32
     max_prefill_tokens: int = 512
     block_size: int = 16
-    num_blocks: int = 1024
+    num_blocks: int = 1024  # pages of every cache group's pool, or a list with one number per group
     max_tokens_per_step: int = 2048
     max_model_len: Optional[int] = None  # default: the model's max_position_embeddings
     cuda_graphs: bool = True  # replay a recorded graph while the same requests decode
@@ -178,10 +178,10 @@ class Scheduler:
                 f"prompt ({len(prompt)}) + max_new_tokens ({options.max_new_tokens}) exceeds the "
                 f"longest sequence the engine takes ({self.max_model_len})")
         # the last generated token is never fed, so total - 1 tokens are cached at most
-        if self.cache.pages_for(total - 1) > self.cache.num_pages:
+        if not self.cache.could_ever_hold(total - 1, self.config.max_prefill_tokens):
             raise SchedulingError(
-                f"the request needs {self.cache.pages_for(total - 1)} pages, the pool has "
-                f"{self.cache.num_pages}: it could never run")
+                f"the request needs {self.cache.peak_pages(total - 1, self.config.max_prefill_tokens)} pages "
+                f"(per cache group), the pools have {self.cache.group_pages}: it could never run")
         seq = Sequence_(self._next_id, prompt, options)
         self._next_id += 1
         self.waiting.append(seq)

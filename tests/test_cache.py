@@ -152,3 +152,35 @@ def test_random_orders_keep_the_books(seed):
     cm.check_invariants()
     assert cm.free_pages() == [24, 24] and cm.num_free_slots == 5
     assert all(g.pool.reuses > 0 for g in cm.groups)
+
+
+def test_pools_sized_group_by_group():
+    """A group with a window gives pages back as the window passes them, so it
+    gets by with a pool of a few pages beside a group that keeps every key."""
+    needs = [need(0, FULL), need(1, WIN), need(2, FULL)]
+    cm = CacheManager(needs, page_size=4, num_pages=[40, 6], max_requests=2)
+    assert cm.group_pages == [40, 6] and cm.free_pages() == [40, 6] and cm.pad_pages() == [40, 6]
+    assert cm.layer_caches[0].num_pages == 41 and cm.layer_caches[1].num_pages == 7
+    # 150 tokens fed 8 at a time: the full group needs 38 pages, the windowed one at most
+    # pages_for(10 + 8) + 1 = 6 at any time
+    assert cm.peak_pages(150, 8) == [38, 6] and cm.could_ever_hold(150, 8)
+    assert not cm.could_ever_hold(150, 16) and not cm.could_ever_hold(170, 8)
+    rc = cm.admit("a")
+    fed = 0
+    while fed < 150:
+        n = min(8, 150 - fed)
+        cm.extend(rc, n)
+        assert cm.free_pages()[1] >= 0
+        cm.commit(rc, n)
+        fed += n
+        cm.check_invariants()
+    assert cm.free_pages()[0] == 40 - 38 and cm.free_pages()[1] >= 2
+    cm.release(rc)
+    assert cm.free_pages() == [40, 6]
+    # a function of the group's needs works too; a list of the wrong length is refused
+    by_need = CacheManager(needs, page_size=4, num_pages=lambda spec: 5 if spec.window else 30, max_requests=1)
+    assert by_need.group_pages == [30, 5]
+    with pytest.raises(CacheError, match="cache groups"):
+        CacheManager(needs, page_size=4, num_pages=[40, 6, 3], max_requests=2)
+    with pytest.raises(CacheError, match="cache groups"):
+        CacheManager(needs, page_size=4, num_pages=[40], max_requests=2)

@@ -33,14 +33,26 @@ def define_toy():
             self.w = weights[self.name].float()
 
         def forward(self, x, ctx, cache):
+            # What a mixer with state may rely on: the step's shape is known on the host
+            # (``host_cu_rows``, ``n_entries``, ``max_rows_per_entry``; fixed for a recorded
+            # step), the slots only on the device (``slot_ids``), because a recorded step is
+            # replayed for other requests.  Nothing here reads device memory on the host, so
+            # the engine can record it in a CUDA graph.
+            state, xf = cache.state, x.float()
+            if ctx.max_rows_per_entry == 1:  # one row per entry: all entries at once
+                slots = ctx.slot_ids.long()
+                s = state[slots] * self.decay + xf
+                state[slots] = s  # (rows that pad a batch all write the spare slot)
+                return (s @ self.w.T).to(x.dtype)
             out = torch.empty_like(x)
             cu = ctx.host_cu_rows
-            slots = ctx.slot_ids.tolist()
             for e in range(ctx.n_entries):  # rows of a request in order, state carried across steps
-                s = cache.state[slots[e]]
+                slot = ctx.slot_ids[e: e + 1].long()
+                s = state[slot][0]
                 for r in range(cu[e], cu[e + 1]):
-                    s.mul_(self.decay).add_(x[r].float())
+                    s = s * self.decay + xf[r]
                     out[r] = (self.w @ s).to(x.dtype)
+                state[slot] = s[None]
             return out
 
     def build_spec(cfg):
@@ -52,7 +64,7 @@ def define_toy():
             mixer = PartSpec("toy_running_mean", {"hidden_size": H, "decay": cfg["decay"], "prefix": p}) \
                 if i % 2 == 0 else PartSpec("attention", {
                     "hidden_size": H, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
-                    "prefix": p + "attn.",
+                    "prefix": p + "attn.", "window": cfg.get("window", 0) if i % 4 == 3 else 0,
                     "position": {"kind": "rotary", "params": {"head_dim": 16, "theta": 1e4}}})
             layers.append(LayerSpec("prenorm", name=p, parts={
                 "norm1": norm("n1"), "mixer": mixer, "norm2": norm("n2"),
@@ -123,6 +135,60 @@ def test_toy_mixer_with_state_steps_like_a_whole_run(dtype, tmp_path):
         scale = whole[k].abs().max()
         assert (whole[k] - cut[k]).abs().max() / scale < tol
     assert (whole["a"][:17] - whole["b"]).abs().max() > 1e-3  # the two requests are not mixed up
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_through_the_engine(dtype, tmp_path):
+    """The same toy architecture through ``Engine`` as a user runs it: decode
+    steps recorded as CUDA graphs and launched ahead, rows that pad a batch, a
+    request that arrives late, and page pools so small that a request is
+    preempted, loses its state slot and is computed again.  Four layers: state,
+    attention over all keys, state, attention with a window - so the cache has
+    two groups of pages, sized apart, beside the state slots.  Every request
+    gets the tokens of its run alone, and those are the tokens of one whole
+    pass over prompt and continuation."""
+    import infernum_b200 as ib
+    from infernum_b200.cache import CacheManager
+    from infernum_b200.engine.step import ModelRunner, StepEntry
+    define_toy()
+    cfg = dict(CFG, num_hidden_layers=4, window=12)
+    folder = ib.write_random_model(str(tmp_path / "toy4"), cfg, seed=5)
+    model = ib.load_model(folder, dtype=dtype)
+    needs = model.cache_needs()
+    assert [n.paged.window if n.paged else None for n in needs] == [None, 0, None, 12]
+    prompts = [[(7 * i + 3 * j) % 50 for j in range(n)] for i, n in enumerate((9, 21, 5, 14))]
+    n_new = 30
+    opts = ib.GenerateOptions(max_new_tokens=n_new, ignore_eos=True)
+    base = dict(max_batch_size=4, block_size=4, max_prefill_tokens=8, max_model_len=64)
+    solo = ib.Engine(model, ib.BatchConfig(num_blocks=[16, 16], cuda_graphs=False, **base))
+    alone = [solo.generate(p, opts) for p in prompts]
+    # the pool of the group that keeps every key holds 30 pages where the four requests need 43;
+    # the windowed group gets by with pages_for(12 + 8) + 1 = 6 a request
+    tight = ib.Engine(model, ib.BatchConfig(num_blocks=[30, 24], **base))
+    assert tight.cache.group_pages == [30, 24] and tight.decoder is not None
+    handles = [tight.submit(p, opts) for p in prompts[:3]]
+    for _ in range(6):
+        tight.step()
+    handles.append(tight.submit(prompts[3], opts))  # arrives while the others decode
+    tight.run_until_done(handles)
+    assert tight.stats.preemptions > 0 and tight.stats.ahead_launched > 0
+    assert any(s.graph is not None for s in tight.decoder._slots.values())
+    assert tight.cache.free_pages() == [30, 24] and tight.cache.num_free_slots == 4
+    for h, want in zip(handles, alone):
+        assert len(h.tokens) == n_new
+        if dtype == "float32":
+            assert h.tokens == want
+    if dtype == "float32":
+        # one whole pass over prompt and continuation selects the same tokens
+        cache = CacheManager(needs, page_size=4, num_pages=[16, 16], max_requests=1, dtype=model.rt.dtype, device=DEV)
+        runner = ModelRunner(model, cache)
+        for p, want in zip(prompts, alone):
+            rc = cache.admit("whole")
+            seq = p + want[:-1]
+            logits = runner.step([StepEntry(rc, seq, list(range(len(p) - 1, len(seq))))])
+            assert logits.argmax(dim=1).tolist() == want
+            cache.release(rc)
+        runner.check_errors()
 
 
 def define_toy_parts():
