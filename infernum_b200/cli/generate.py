@@ -10,8 +10,14 @@ The model folder defaults to $LLAMA_MODEL_PATH.  The architecture is chosen by
 (and always with ``--prompt-ids``) it is a list of token ids such as
 "1,15043,3186".  Like the reference it prints the decoding mode, the output as
 it is produced and "Generated N tokens in S s (R tokens/sec)" (generate.rs:180-240).
-Beyond the reference: ``--dtype`` (bfloat16 or float32) and the engine limits
-``--block-size``, ``--num-blocks``, ``--max-batch-size``, ``--max-prefill-tokens``.
+Beyond the reference: ``--dtype`` (bfloat16 or float32), the engine limits
+``--block-size``, ``--num-blocks``, ``--max-batch-size``, ``--max-prefill-tokens``,
+``--allow-unused-tensors``, and a random-weights mode that needs no checkpoint:
+
+    generate --config config.json --random-weights [--weights-seed 0] "5,6,7,8" -n 16 --greedy
+
+draws the weights on the GPU from the configuration file and a seed (the values
+``write_random_model`` would write to a folder for the same two).
 """
 
 from __future__ import annotations
@@ -49,6 +55,13 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--num-blocks", type=int, default=None)
     ap.add_argument("--max-batch-size", type=int, default=32)
     ap.add_argument("--max-prefill-tokens", type=int, default=512)
+    ap.add_argument("--config", default=None, metavar="FILE",
+                    help="a config.json to build the model from (with --random-weights)")
+    ap.add_argument("--random-weights", action="store_true",
+                    help="no checkpoint: draw the weights from --config and --weights-seed")
+    ap.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
+    ap.add_argument("--allow-unused-tensors", action="store_true",
+                    help="warn about tensors in the checkpoint that the model does not use instead of refusing")
     return ap
 
 
@@ -69,10 +82,20 @@ def _parse_ids(text: str) -> List[int]:
 
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
-    from .. import BatchConfig, Engine, GenerateOptions, SamplingParams, load_model
+    from .. import BatchConfig, Engine, GenerateOptions, SamplingParams, load_model, random_model
 
-    model = load_model(args.model, dtype=args.dtype)
-    tokenizer = None if args.prompt_ids else _load_tokenizer(args.model)
+    if args.random_weights != (args.config is not None):
+        print("--config FILE and --random-weights go together", file=sys.stderr)
+        return 2
+    if args.random_weights:
+        import json
+
+        with open(args.config, encoding="utf-8") as fh:
+            model = random_model(json.load(fh), seed=args.weights_seed, dtype=args.dtype)
+        tokenizer = None
+    else:
+        model = load_model(args.model, dtype=args.dtype, strict=not args.allow_unused_tensors)
+        tokenizer = None if args.prompt_ids else _load_tokenizer(args.model)
     if tokenizer is not None:
         ids = tokenizer.encode(args.prompt, add_special_tokens=False).ids
         if model.spec.bos_token_id is not None:

@@ -1,6 +1,7 @@
 """Times one kernel of the package at given sizes and reports what it moves or
 computes against the machine's measured peaks.  Meant for profiling: run it
-plain to get the number, or under ``ncu -k regex:<kernel> -c 3`` for counters.
+plain to get the number, or under ``ncu --clock-control none -k regex:<kernel> -c 3`` for
+counters (without that flag ncu locks the clocks of a GPU that others share).
 
     python -m infernum_b200.cli.kernel_bench attention-decode --batch 64 --kv-len 1100
     python -m infernum_b200.cli.kernel_bench attention-prefill --tokens 2048

@@ -16,6 +16,7 @@
 #define IB_ERR_BAD_ARG (-1)       // a size or pointer the kernel cannot take
 #define IB_ERR_UNSUPPORTED (-2)   // a configuration this build does not cover
 #define IB_ERR_TOO_LARGE (-3)     // beyond a stated maximum
+#define IB_ERR_NOALLOC_SETUP (-4) // ib_argmax_noalloc: the per-device look-up of its scratch array failed
 
 // Bits of the device-side error word that kernels may set (never trap).
 #define IB_FLAG_BAD_TOKEN 1u      // token id outside the vocabulary

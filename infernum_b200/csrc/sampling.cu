@@ -209,12 +209,14 @@ IB_EXPORT int ib_argmax(const float* logits, int ld, int n_rows, int V, int* out
 // The first call on a device looks the array's address up (in host code the
 // array's name is only a stand-in for the symbol, not a device address) and
 // remembers it per device; that first call should come before any stream
-// capture begins.  The function calls no cudaMalloc, cudaFree or other
-// allocating routine.  It has no counterpart in the reference.
+// capture begins.  Two host threads that make their first call on one device
+// at the same moment both do the look-up and store the same address, which
+// is harmless (the store is one aligned pointer).  The function calls no
+// cudaMalloc, cudaFree or other allocating routine.  It has no counterpart in
+// the reference.
 // ---------------------------------------------------------------------------
 #define IB_NOALLOC_MAX_ROWS 256
 #define IB_NOALLOC_MAX_DEVICES 64
-#define IB_ERR_NOALLOC_SETUP (-4)
 
 static __device__ __align__(256) unsigned char
     g_argmax_noalloc_scratch[IB_NOALLOC_MAX_ROWS * IB_ARGMAX_MAX_SLICES * 8];

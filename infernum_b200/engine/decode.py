@@ -8,7 +8,7 @@ those in fixed device buffers per *batch bucket* (the batch size rounded up to
 the bucket with rows that belong to no request (they write to a page and a
 state slot reserved for padding), and replays the graph recorded for that
 bucket.  Requests may come and go between steps without a new recording; a
-graph is recorded per (bucket, cache-length class, sampling or not), the first
+graph is recorded per (bucket, cache-length class, width of the sampling rows), the first
 time it is needed, after one eager step.
 
 Three ways to feed it:
@@ -87,7 +87,17 @@ class _Slot:
 
 
 class DecodeRunner:
+    # The recent tokens of a sampling row (for its repetition penalty) sit in a fixed buffer
+    # [rows, width]; the width is the largest window among the step's rows rounded up to a
+    # multiple of this, and part of the key a step is recorded under, so that a window of
+    # any length is seen whole.
     RECENT_WIDTH = 64
+
+    @classmethod
+    def recent_width(cls, windows) -> int:
+        """Buffer width for sampling rows whose repetition-penalty windows are ``windows``."""
+        w = max(list(windows) + [1])
+        return -(-w // cls.RECENT_WIDTH) * cls.RECENT_WIDTH
     # Buffers and graphs are kept for this many (bucket, cache-length class, sampling, feed,
     # portion) keys; beyond it the one unused for longest is dropped (a graph holds its own
     # activations: some hundred MB at large layer sizes).
@@ -166,8 +176,8 @@ class DecodeRunner:
             slot.sampled = torch.zeros(size, dtype=torch.int32, device=dev)
             slot.params = torch.zeros((size, f), dtype=torch.float32, device=dev)
             slot.host_params = torch.zeros((size, f), dtype=torch.float32).pin_memory()
-            slot.recent = torch.zeros((size, self.RECENT_WIDTH), dtype=torch.int32, device=dev)
-            slot.host_recent = torch.zeros((size, self.RECENT_WIDTH), dtype=torch.int32).pin_memory()
+            slot.recent = torch.zeros((size, int(sampling)), dtype=torch.int32, device=dev)
+            slot.host_recent = torch.zeros((size, int(sampling)), dtype=torch.int32).pin_memory()
             slot.mask = torch.zeros(size, dtype=torch.bool, device=dev)
             slot.host_mask = torch.zeros(size, dtype=torch.bool).pin_memory()
         self._slots[key] = slot
@@ -231,7 +241,7 @@ class DecodeRunner:
             slot.launches_per_step = core.LAUNCHES - before
             slot.eager_steps += 1
 
-    def _key(self, caches: Sequence[RequestCache], sampling: bool, feed: str, ahead: int = 1,
+    def _key(self, caches: Sequence[RequestCache], sampling: int, feed: str, ahead: int = 1,
              portion: Optional[Tuple[RequestCache, int]] = None) -> tuple:
         longest = max(rc.num_tokens for rc in caches) + ahead
         if portion is not None:
@@ -239,7 +249,7 @@ class DecodeRunner:
         kv_cap = 256
         while kv_cap < longest:
             kv_cap *= 2
-        return (bucket_for(len(caches)), kv_cap, bool(sampling), feed, portion[1] if portion else 0)
+        return (bucket_for(len(caches)), kv_cap, int(sampling), feed, portion[1] if portion else 0)
 
     def can_take(self, caches: Sequence[RequestCache],
                  portion: Optional[Tuple[RequestCache, int]] = None) -> bool:
@@ -254,14 +264,17 @@ class DecodeRunner:
         with the given input tokens.  ``sample``: (params, recent, mask) host
         tensors from ``pack_choices`` when some row samples.  Returns the
         selected token ids, int32 [len(caches)] on the device."""
-        out = self.launch(self.prepare(caches, sample is not None), caches, tokens, sample)
+        width = self.recent_width([sample[1].shape[1]]) if sample is not None else 0
+        out = self.launch(self.prepare(caches, width), caches, tokens, sample)
         self._reads.pop()  # the caller reads the device tensor itself
         return out
 
-    def prepare(self, caches: Sequence[RequestCache], sampling: bool,
+    def prepare(self, caches: Sequence[RequestCache], sampling: int,
                 portion: Optional[Tuple[RequestCache, int]] = None) -> _Slot:
         """The part of a step that does not need the input tokens: picks the
-        buffers, fills positions, slots and block tables.  It may run while the
+        buffers, fills positions, slots and block tables.  ``sampling``: 0 when
+        every row is greedy, else the width of the rows' recent-token buffer
+        (``recent_width``).  It may run while the
         step before is still on the GPU (its uploads are waited for first).
         ``portion``: (request, rows) of one prompt portion that rides along with
         the decoded tokens, continuing its request where the cache ends; such a
@@ -335,11 +348,13 @@ class DecodeRunner:
             slot.ints[0, :B].copy_(feed_from.selected[:B])
         if sample is not None:
             params, recent, mask = sample
+            if slot.recent is None or recent.shape[1] > slot.recent.shape[1]:
+                raise CacheError("decode step prepared without room for its rows' recent tokens")
             slot.host_params.zero_()
             slot.host_params[:, :3] = 1.0
             slot.host_params[:B] = params
             slot.host_recent.zero_()
-            slot.host_recent[:B, : recent.shape[1]] = recent[:, : self.RECENT_WIDTH]
+            slot.host_recent[:B, : recent.shape[1]] = recent
             slot.host_mask.zero_()
             slot.host_mask[:B] = mask
             slot.params.copy_(slot.host_params, non_blocking=True)

@@ -160,20 +160,21 @@ class Engine:
                 wanting = [p for p in plan.portions if p is not riding]
                 caches = [p.seq.cache for p in wanting]
                 choices = choices[: len(wanting)]
-                sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) \
-                    if any(c is not None for c in choices) else None
+                width = self._recent_width(choices)
+                sample = pack_choices(choices, width) if width else None
                 prc = riding.seq.cache
-                prepared = self.decoder.prepare(caches, sample is not None, portion=(prc, riding.count))
+                prepared = self.decoder.prepare(caches, width, portion=(prc, riding.count))
                 chosen = self.decoder.launch(prepared, caches, [p.seq.token_at(p.start) for p in wanting], sample,
                                              portion=(prc, riding.tokens))
                 self.h2d_bytes += 16 * len(wanting) + 8 * riding.count + 12
                 logits = self.decoder.last.logits
                 decode_only = True  # the result comes back the same way
             elif decode_only:
-                sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) \
-                    if any(c is not None for c in choices) else None
-                if prepared is None or prepared.prepared_for != tuple(rc.request_id for rc in caches):
-                    prepared = self.decoder.prepare(caches, sample is not None)
+                width = self._recent_width(choices)
+                sample = pack_choices(choices, width) if width else None
+                if prepared is None or prepared.prepared_for != tuple(rc.request_id for rc in caches) \
+                        or (prepared.recent.shape[1] if prepared.recent is not None else 0) != width:
+                    prepared = self.decoder.prepare(caches, width)
                 chosen = self.decoder.launch(prepared, caches,
                                              [p.seq.token_at(p.start) for p in plan.portions], sample)
                 self.h2d_bytes += 16 * len(plan.portions)
@@ -193,8 +194,9 @@ class Engine:
                 ahead = self.scheduler.plan_decode_ahead()
                 if ahead is not None:
                     nxt = [p.seq.cache for p in ahead.portions]
-                    samples = any(p.seq.options.sampling is not None for p in ahead.portions)
-                    ready = self.decoder.prepare(nxt, samples) if self.decoder.can_take(nxt) else None
+                    width = self._recent_width([p.seq.options.sampling and (p.seq.options.sampling, 0, ())
+                                                for p in ahead.portions])
+                    ready = self.decoder.prepare(nxt, width) if self.decoder.can_take(nxt) else None
                     launched = ready is not None and riding is None and self._launch_ahead(plan, ahead, ready, nxt)
                     self._ahead = (ahead, ready, launched)
             if chosen is not None:
@@ -253,10 +255,24 @@ class Engine:
                 return False
             # (the token of the step in flight is not appended yet: this will be the one after it)
             choices.append(None if sp is None else (sp, len(p.seq.generated_ids) + 1, ()))
-        sample = pack_choices(choices, DecodeRunner.RECENT_WIDTH) if any(c is not None for c in choices) else None
+        width = self._recent_width(choices)
+        sample = pack_choices(choices, width) if width else None
         self.decoder.launch(ready, caches, None, sample, feed_from=self.decoder.last)
         self.h2d_bytes += 12 * len(caches)
         return True
+
+    @staticmethod
+    def _recent_width(choices) -> int:
+        """0 when every row of ``choices`` is greedy; else the width of the recorded
+        step's recent-token buffer: the largest repetition-penalty window among the
+        rows that have a penalty, rounded up (``DecodeRunner.recent_width``).  The
+        window is a property of the request, so the width does not change while the
+        same requests decode."""
+        rows = [c[0] for c in choices if c]
+        if not rows:
+            return 0
+        return DecodeRunner.recent_width([sp.repetition_penalty_window for sp in rows
+                                          if sp.repetition_penalty != 1.0])
 
     GRAPH_PORTION_MIN = 64
 

@@ -41,16 +41,18 @@ def make_runtime(dtype, device="cuda:0", options: Optional[Dict[str, Any]] = Non
 
 
 def load_model(folder: str, dtype="bfloat16", device="cuda:0",
-               options: Optional[Dict[str, Any]] = None) -> Model:
+               options: Optional[Dict[str, Any]] = None, strict: bool = True) -> Model:
     """Reads ``folder/config.json``, picks the architecture by its
-    ``model_type``, and loads ``folder/*.safetensors`` by tensor name."""
+    ``model_type``, and loads ``folder/*.safetensors`` by tensor name.
+    ``strict=False`` turns tensors in the files that the model does not use from
+    an error into a warning."""
     rt = make_runtime(dtype, device, options)
     arch, cfg = resolve_config(read_config_json(folder))
     spec = arch.build_spec(cfg)
     with torch.cuda.device(rt.device):
         model = Model(spec, rt)
         model.config = cfg
-        weights = load_tensors(folder, model.weight_specs(), rt.dtype, rt.device, spec.ignorable)
+        weights = load_tensors(folder, model.weight_specs(), rt.dtype, rt.device, spec.ignorable, strict)
         model.bind(weights)
     return model
 

@@ -41,7 +41,8 @@ def describe_flags(flags: int) -> str:
     sites = [name for i, name in enumerate(TIMEOUT_SITES) if flags & (1 << (8 + i))]
     return "; ".join(what) + (" (" + ", ".join(sites) + ")" if sites else "")
 
-_ERR_NAMES = {-1: "bad argument", -2: "unsupported configuration", -3: "size beyond the kernel's maximum"}
+_ERR_NAMES = {-1: "bad argument", -2: "unsupported configuration", -3: "size beyond the kernel's maximum",
+              -4: "per-device set-up failed"}
 
 _lib = None
 

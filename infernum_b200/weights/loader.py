@@ -29,9 +29,11 @@ _INT_FILE_DTYPES = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uin
 
 
 def check_against_specs(specs: Mapping[str, WeightSpec], table: Mapping[str, TensorEntry],
-                        ignorable: Iterable[str] = ()) -> Dict[str, str]:
+                        ignorable: Iterable[str] = (), strict: bool = True) -> Dict[str, str]:
     """Returns name -> source name in the files; raises one WeightError that
-    lists everything that is wrong."""
+    lists everything that is wrong.  ``strict=False``: tensors nobody asked
+    for are named in a warning instead (the reference ignores them silently);
+    missing tensors, wrong shapes and unusable dtypes are errors either way."""
     missing, wrong_shape, wrong_dtype = [], [], []
     source: Dict[str, str] = {}
     for name, spec in specs.items():
@@ -52,6 +54,12 @@ def check_against_specs(specs: Mapping[str, WeightSpec], table: Mapping[str, Ten
         n for n in table
         if n not in used and n not in specs and not any(fnmatch.fnmatchcase(n, p) for p in patterns)
     )
+    if unexpected and not strict:
+        import warnings
+
+        warnings.warn(f"checkpoint holds {len(unexpected)} tensor(s) the model does not use: "
+                      + ", ".join(unexpected[:8]) + (" ..." if len(unexpected) > 8 else ""), stacklevel=3)
+        unexpected = []
     if missing or unexpected or wrong_shape or wrong_dtype:
         lines = ["checkpoint does not match the model:"]
         if missing:
@@ -76,9 +84,9 @@ def kept_dtype(spec: WeightSpec, file_dtype: torch.dtype, engine_dtype: torch.dt
 
 
 def load_tensors(folder: str, specs: Mapping[str, WeightSpec], engine_dtype: torch.dtype,
-                 device, ignorable: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
+                 device, ignorable: Iterable[str] = (), strict: bool = True) -> Dict[str, torch.Tensor]:
     table = open_model_folder(folder)
-    source = check_against_specs(specs, table, ignorable)
+    source = check_against_specs(specs, table, ignorable, strict)
     out: Dict[str, torch.Tensor] = {}
     for name, spec in specs.items():
         entry = table[source[name]]

@@ -139,6 +139,28 @@ def test_command_line_generate(folders):
     assert "Sampling: temperature=0.9, top_p=0.8, seed=7, repetition_penalty=1.3 (window=64)" in out2.stdout
 
 
+def test_command_line_generate_from_a_bare_configuration(tmp_path):
+    """``--config FILE --random-weights``: from a config.json and a seed to tokens
+    with no checkpoint; the weights are those ``write_random_model`` writes for the
+    same two, so the plain implementation can check the tokens."""
+    import json
+    from infernum_b200.weights.random_init import write_random_model
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(CONFIGS["B"]))
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "--config", str(cfg_path),
+                          "--random-weights", "--weights-seed", "9", "5,6,7,8,9", "-n", "5", "--greedy",
+                          "--dtype", "float32", "--block-size", "8"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("5,6,7,8,9")][0]
+    got = [int(t) for t in line.split()[1:]]
+    folder = write_random_model(str(tmp_path / "same"), CONFIGS["B"], 9)
+    want, _ = plain_greedy_with_margin(folder, [5, 6, 7, 8, 9], 5)
+    assert_same_up_to_ties(folder, [5, 6, 7, 8, 9], got, want, "float32")
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "--random-weights", "1,2"],
+                         capture_output=True, text=True, timeout=600)
+    assert bad.returncode == 2 and "go together" in bad.stderr
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_requests_come_and_go_under_recorded_decode_graphs(folders, dtype):
     """Requests of different lengths leave the batch one by one and a late one
@@ -402,3 +424,31 @@ def test_a_product_whose_wait_ran_out_surfaces_from_engine_step(folders):
             for _ in range(4):
                 engine.step()
         assert int(model.rt.err.item()) == 0  # reported once, then cleared
+
+
+def test_a_long_repetition_window_is_seen_whole_by_recorded_steps(folders):
+    """The recent tokens of a sampling row sit in a buffer of fixed width in a
+    recorded decode step.  A window longer than that buffer's smallest size (64)
+    must still be seen whole: an engine that records its steps and one that
+    launches them kernel by kernel select the same tokens, and the penalty over
+    tokens 65 to 100 back does change them."""
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype="float32")
+    prompt = random_tokens(20, 320, 808)
+    base = dict(max_batch_size=2, block_size=8, num_blocks=64)
+
+    def run(graphs, window):
+        engine = ib.Engine(model, ib.BatchConfig(cuda_graphs=graphs, **base))
+        sp = ib.SamplingParams(temperature=0.9, top_p=0.95, seed=4, repetition_penalty=1.8,
+                               repetition_penalty_window=window)
+        # a greedy request rides along, so that the batch has rows of both kinds
+        out = engine.generate_batch([prompt, prompt[:7]], [ib.GenerateOptions(max_new_tokens=150, sampling=sp),
+                                                           ib.GenerateOptions(max_new_tokens=150)])
+        return out, engine
+
+    (eager, eager_greedy), _ = run(False, 100)
+    (graph, graph_greedy), engine = run(True, 100)
+    assert any(k[2] == 128 for k in engine.decoder._slots)  # recorded with a buffer of 128 recent tokens
+    assert graph == eager and graph_greedy == eager_greedy
+    (short, _), _ = run(True, 64)
+    assert short != graph

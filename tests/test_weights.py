@@ -100,6 +100,27 @@ def test_one_error_lists_everything(tmp_path):
         assert word in text
 
 
+def test_unused_tensors_can_be_a_warning_instead(tmp_path):
+    """``strict=False``: a tensor nobody asked for is named in a warning (the
+    reference ignores it); a missing one is an error either way."""
+    folder = write_random_model(str(tmp_path / "m"), TINY_B, seed=1)
+    _, spec, specs = model_specs_for(TINY_B)
+    from safetensors.torch import load_file, save_file
+    tensors = load_file(os.path.join(folder, "model.safetensors"))
+    tensors["stray.tensor"] = torch.zeros(3)
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    with pytest.raises(WeightError):
+        check_against_specs(specs, open_model_folder(folder), spec.ignorable)
+    with pytest.warns(UserWarning, match="stray.tensor"):
+        src = check_against_specs(specs, open_model_folder(folder), spec.ignorable, strict=False)
+    assert set(src) == set(specs)
+    del tensors["model.norm.weight"]
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    with pytest.warns(UserWarning), pytest.raises(WeightError) as exc:
+        check_against_specs(specs, open_model_folder(folder), spec.ignorable, strict=False)
+    assert exc.value.missing == ["model.norm.weight"] and exc.value.unexpected == []
+
+
 def test_head_falls_back_to_the_embedding(tmp_path):
     folder = write_random_model(str(tmp_path / "m"), TINY_B, seed=1)
     from safetensors.torch import load_file, save_file
