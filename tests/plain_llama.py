@@ -4,10 +4,15 @@ tensors only.  It shares no code with the package under test: it parses
 config.json by itself and reads the checkpoint with the ``safetensors``
 library.
 
-This implementation rests on the formulas only: the reference is a Rust
-workspace and neither cargo nor rustc exists here, so its own model code
-cannot be compiled or imported to produce golden outputs.  Each function cites
-the reference file and lines it restates.
+The reference is a Rust workspace and neither cargo nor rustc exists here, so
+its model code cannot be compiled or imported as a whole.  Its CUDA kernels
+can: ``tests/golden/make_golden.py`` compiled the reference's unchanged ``.cu``
+files and ran their float32 variants once on a GPU - each part, and a whole
+forward pass of a tiny random model with the reference's kernels for everything
+but the matrix products - and ``tests/test_golden.py`` holds the functions
+below against those outputs.  What the reference does not have (llama3
+frequency scaling) rests on the formula alone.  Each function cites the
+reference file and lines it restates.
 
 Precision: weights are taken as stored (bfloat16 values widened exactly) and
 all arithmetic runs in ``dtype`` (float64 by default), except rotation angles,
