@@ -183,8 +183,38 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+// Two float32 in one 64-bit register, for the packed arithmetic of sm_100 (one
+// instruction, two results): the softmax warps are bound by the instructions
+// they issue, not by any arithmetic unit.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+// (d0, d1) = (a0, a1) * b + c, b and c packed pairs
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, unsigned long long b,
+                                     unsigned long long c) {
+    asm("{\n\t.reg .b64 ra, rd;\n\tmov.b64 ra, {%2, %3};\n\tfma.rn.f32x2 rd, ra, %4, %5;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}\n"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "l"(b), "l"(c));
+}
+// acc += (a0, a1), acc a packed pair
+__device__ __forceinline__ void add2(unsigned long long& acc, float a0, float a1) {
+    asm("{\n\t.reg .b64 ra;\n\tmov.b64 ra, {%1, %2};\n\tadd.rn.f32x2 %0, %0, ra;\n\t}\n"
+        : "+l"(acc) : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float sum2(unsigned long long v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo + hi;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // K-major operand tile with 128-byte rows and the 128-byte swizzle: groups of 8
@@ -428,17 +458,21 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
             // The maxima are kept in raw scores (the scale is positive); the scale and
             // the reference enter the exponent in one multiply-add.
             const int key0 = (t_off + t) * BN;
-            float m_new = m_run;
             if (key0 + BN - 1 > pos0 + r_begin || !valid) {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
-                    s[c] = (key0 + c <= my_pos) ? s[c] : -INFINITY;
-                    m_new = fmaxf(m_new, s[c]);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < BN; c += 2) m_new = fmaxf(m_new, fmaxf(s[c], s[c + 1]));
+                for (int c = 0; c < BN; ++c) s[c] = (key0 + c <= my_pos) ? s[c] : -INFINITY;
             }
+            // the tile's maximum: four chains of three-input maxima over 15 values each,
+            // then the chains, the running maximum and the four values left over
+            float ch[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                ch[q] = max3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
+#pragma unroll
+                for (int i = 3; i < 15; i += 2) ch[q] = max3(ch[q], s[16 * q + i], s[16 * q + i + 1]);
+            }
+            float m_new = max3(max3(m_run, ch[0], ch[1]), ch[2], ch[3]);
+            m_new = max3(max3(m_new, s[15], s[31]), s[47], s[63]);
             // The exponents refer to m_run, which follows the true maximum only when
             // that has risen by more than 2^8 in the exponent: softmax does not depend
             // on the reference, P stays below 256 (fine in bfloat16, the sum is 32-bit),
@@ -449,14 +483,19 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
                 m_run = m_new;
             }
             const float m_scaled = m_run == -INFINITY ? 0.f : m_run * p.scale_log2;
-            float sum0 = 0.f, sum1 = 0.f;
+            // exponent = score * scale - reference, two scores per instruction; the sums in
+            // four packed accumulators (eight chains of additions)
+            const unsigned long long scale2 = pack2(p.scale_log2, p.scale_log2);
+            const unsigned long long ref2 = pack2(-m_scaled, -m_scaled);
+            unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
             for (int c = 0; c < BN; c += 2) {
-                s[c] = fast_exp2(fmaf(s[c], p.scale_log2, -m_scaled));
-                s[c + 1] = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_scaled));
-                sum0 += s[c];
-                sum1 += s[c + 1];
+                fma2(s[c], s[c + 1], s[c], s[c + 1], scale2, ref2);
+                s[c] = fast_exp2(s[c]);
+                s[c + 1] = fast_exp2(s[c + 1]);
+                add2(acc[(c >> 1) & 3], s[c], s[c + 1]);
             }
+            const float sum0 = sum2(acc[0]) + sum2(acc[1]), sum1 = sum2(acc[2]) + sum2(acc[3]);
             l_run = l_run * corr + (sum0 + sum1);
             // The update of tile t - 1 began when the exponentials of this tile did and is
             // long complete; the wait is there to follow the barrier's phases, and for the

@@ -30,6 +30,9 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler",
               "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
+# More nvcc flags for every module, e.g. "-DNAME=1 -Xptxas -v" (they are part of a library's name)
+EXTRA_FLAGS = os.environ.get("INFERNUM_NVCC_FLAGS", "").split()
+
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
@@ -71,7 +74,7 @@ def build_dir() -> str:
 
 def _hash_module(sources: Sequence[str], defines: Sequence[str], nvcc: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + list(defines)).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + list(defines) + EXTRA_FLAGS).encode())
     try:
         h.update(subprocess.run([nvcc, "--version"], capture_output=True, check=True).stdout)
     except (OSError, subprocess.CalledProcessError):
@@ -132,7 +135,7 @@ def compile_module(name: str, sources: Sequence[str], defines: Sequence[str] = (
         for src in sources:
             obj = os.path.join(work, os.path.splitext(src)[0] + ".o")
             objs.append(obj)
-            cmds.append((src, [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *defines, "-I", CSRC_DIR, "-c",
+            cmds.append((src, [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *defines, *EXTRA_FLAGS, "-I", CSRC_DIR, "-c",
                                os.path.join(CSRC_DIR, src), "-o", obj]))
         _run_with_heartbeat(cmds, name)
         tmp_lib = os.path.join(work, "lib.so")
