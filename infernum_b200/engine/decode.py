@@ -11,6 +11,15 @@ bucket.  Requests may come and go between steps without a new recording; a
 graph is recorded per (bucket, cache-length class, width of the sampling rows), the first
 time it is needed, after one eager step.
 
+A step of decoded tokens and one prompt portion (the step that recurs while
+prompts are fed in portions, and every step of a prompt that is alone) is
+recorded the same way, per bucket of the portion's length (``portion_bucket``):
+the portion's rows are followed by rows of an entry that belongs to no request
+(it attends to, and writes, the page reserved for padding), so that portions of
+any length up to the bucket replay one recording.  What differs from step to
+step - which rows belong to the portion, where its last row is - is data in the
+device buffers, not shape.
+
 Three ways to feed it:
   * from the host (``Engine``): tokens, positions and lengths are copied from
     pinned memory every step, changed block-table rows too;
@@ -51,6 +60,14 @@ def bucket_for(n: int) -> int:
     return -(-n // 128) * 128
 
 
+def portion_bucket(n: int) -> int:
+    """Rows a recorded step holds for a prompt portion of ``n`` rows: multiples of
+    16 up to 64, of 64 up to 512, of 128 up to 1,024, of 256 beyond (the kernels
+    for prompts work on tiles of up to 256 rows, so the padding costs little)."""
+    step = 16 if n <= 64 else 64 if n <= 512 else 128 if n <= 1024 else 256
+    return -(-n // step) * step
+
+
 @dataclass
 class _Slot:
     """Buffers and graph of one (bucket, cache-length class, sampling, feed) key."""
@@ -66,7 +83,8 @@ class _Slot:
     host_np: object = None  # host_ints' memory as a numpy array (cheap to fill from lists)
     host_tables_np: object = None  # the same for host_tables
     rows_written: List[bool] = field(default_factory=list)  # a row that pads the bucket is written once
-    portion: int = 0  # rows of the prompt portion that rides along (0: decoded tokens only)
+    portion: int = 0  # rows held for the prompt portion that rides along (0: decoded tokens only)
+    portion_wants: bool = False  # the portion's last row is a logit row too (it ends its prompt)
     uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
     prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
     result: Optional[torch.Tensor] = None  # device [size + 1]: the selected tokens, then the error word
@@ -129,7 +147,7 @@ class DecodeRunner:
             if victim is None:
                 break
             del self._slots[victim]
-        size, kv_cap, sampling, _feed, portion = key
+        size, kv_cap, sampling, _feed, portion, portion_wants = key
         dev = self.rt.device
         G = len(self.cache.groups)
         arange = torch.arange(size + 1, dtype=torch.int32, device=dev)
@@ -146,42 +164,59 @@ class DecodeRunner:
             # one row per entry and the longest cache the recorded step may meet, ``max_kv_len``,
             # and keeps its plan in ``ctx.scratch``, which lives as long as the recording)
         else:
-            # `size` decoded tokens (one row and one entry each), then one prompt portion of
-            # `portion` rows as the last entry.  One flat buffer holds what changes from step
-            # to step: tokens | positions (a row each) | q_start | kv_len | slots (an entry each).
-            rows, entries = size + portion, size + 1
-            ints = torch.zeros(2 * rows + 3 * entries, dtype=torch.int32, device=dev)
-            host_ints = torch.zeros(2 * rows + 3 * entries, dtype=torch.int32).pin_memory()
+            # `size` decoded tokens (one row and one entry each), then the prompt portion's
+            # entry with up to `portion` rows, then an entry of the rows left over, which
+            # belongs to no request.  One flat buffer holds all that changes from step to
+            # step: tokens | positions | row_entry (a row each) | cu_rows (entries + 1) |
+            # q_start | kv_len | slots (an entry each) | logit rows (size + 1).
+            rows, entries = size + portion, size + 2
+            offs = self._portion_offsets(size, portion)
+            ints = torch.zeros(offs["end"], dtype=torch.int32, device=dev)
+            host_ints = torch.zeros(offs["end"], dtype=torch.int32).pin_memory()
             tables = torch.full((G, entries, self.MB), -1, dtype=torch.int32, device=dev)
-            row_entry = torch.cat([arange[:size], torch.full((portion,), size, dtype=torch.int32, device=dev)])
-            cu_rows = torch.cat([arange, torch.tensor([rows], dtype=torch.int32, device=dev)])
-            e0 = 2 * rows
+            view = lambda name, n: ints[offs[name]: offs[name] + n]  # noqa: E731
             ctx = StepContext(
-                n_rows=rows, n_entries=entries, token_ids=ints[:rows], positions=ints[rows: 2 * rows],
-                row_entry=row_entry, cu_rows=cu_rows, q_start=ints[e0: e0 + entries],
-                kv_len=ints[e0 + entries: e0 + 2 * entries], slot_ids=ints[e0 + 2 * entries: e0 + 3 * entries],
-                logit_rows=arange[:size], block_tables=[tables[g] for g in range(G)],
-                host_cu_rows=list(range(size + 1)) + [rows], host_kv_len=[], max_rows_per_entry=portion,
+                n_rows=rows, n_entries=entries, token_ids=view("tok", rows), positions=view("pos", rows),
+                row_entry=view("rowe", rows), cu_rows=view("cu", entries + 1), q_start=view("q0", entries),
+                kv_len=view("kv", entries), slot_ids=view("sl", entries),
+                logit_rows=view("logit", size + (1 if portion_wants else 0)),
+                block_tables=[tables[g] for g in range(G)],
+                # (for launch geometry: the portion at its longest, the entry behind it empty)
+                host_cu_rows=list(range(size + 1)) + [rows, rows], host_kv_len=[], max_rows_per_entry=portion,
                 max_kv_len=kv_cap, all_decode=False)
+        n_sel = size + (1 if portion and portion_wants else 0)   # rows whose token is selected
         slot = _Slot(size=size, ints=ints, host_ints=host_ints, tables=tables,
                      host_tables=torch.full(tuple(tables.shape), -1, dtype=torch.int32).pin_memory(),
-                     selected=torch.zeros(size, dtype=torch.int32, device=dev), ctx=ctx,
+                     selected=torch.zeros(n_sel, dtype=torch.int32, device=dev), ctx=ctx,
                      rows=[None] * tables.shape[1], rows_written=[False] * tables.shape[1], portion=portion)
+        slot.portion_wants = bool(portion and portion_wants)
         slot.host_np = slot.host_ints.numpy()
-        slot.result = torch.zeros(size + 1, dtype=torch.int32, device=dev)
-        slot.host_results = [torch.zeros(size + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        slot.result = torch.zeros(n_sel + 1, dtype=torch.int32, device=dev)
+        slot.host_results = [torch.zeros(n_sel + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         slot.result_events = [torch.cuda.Event(), torch.cuda.Event()]
         if sampling:
             f = core.SAMPLE_PARAM_FLOATS
-            slot.sampled = torch.zeros(size, dtype=torch.int32, device=dev)
-            slot.params = torch.zeros((size, f), dtype=torch.float32, device=dev)
-            slot.host_params = torch.zeros((size, f), dtype=torch.float32).pin_memory()
-            slot.recent = torch.zeros((size, int(sampling)), dtype=torch.int32, device=dev)
-            slot.host_recent = torch.zeros((size, int(sampling)), dtype=torch.int32).pin_memory()
-            slot.mask = torch.zeros(size, dtype=torch.bool, device=dev)
-            slot.host_mask = torch.zeros(size, dtype=torch.bool).pin_memory()
+            slot.sampled = torch.zeros(n_sel, dtype=torch.int32, device=dev)
+            slot.params = torch.zeros((n_sel, f), dtype=torch.float32, device=dev)
+            slot.host_params = torch.zeros((n_sel, f), dtype=torch.float32).pin_memory()
+            slot.recent = torch.zeros((n_sel, int(sampling)), dtype=torch.int32, device=dev)
+            slot.host_recent = torch.zeros((n_sel, int(sampling)), dtype=torch.int32).pin_memory()
+            slot.mask = torch.zeros(n_sel, dtype=torch.bool, device=dev)
+            slot.host_mask = torch.zeros(n_sel, dtype=torch.bool).pin_memory()
         self._slots[key] = slot
         return slot
+
+    @staticmethod
+    def _portion_offsets(size: int, portion: int) -> Dict[str, int]:
+        """Where the parts of a portion step's flat int32 buffer begin."""
+        rows, entries = size + portion, size + 2
+        offs, at = {}, 0
+        for name, n in (("tok", rows), ("pos", rows), ("rowe", rows), ("cu", entries + 1), ("q0", entries),
+                        ("kv", entries), ("sl", entries), ("logit", size + 1)):
+            offs[name] = at
+            at += n
+        offs["end"] = at
+        return offs
 
     def _fill_tables(self, slot: _Slot, caches: Sequence[RequestCache]) -> bool:
         """Brings the host mirror of the block tables up to date; True if it changed.
@@ -203,8 +238,13 @@ class DecodeRunner:
             changed = True
             tab[:, r, :] = -1
             if rc is None:
+                # a row that pads a batch sits at position 0; the entry behind a prompt portion
+                # has up to a bucket of rows: every page of its table is the page kept for padding
                 for g in range(len(self.cache.groups)):
-                    tab[g, r, 0] = pads[g]
+                    if slot.portion and r == len(slot.rows) - 1:
+                        tab[g, r, :] = pads[g]
+                    else:
+                        tab[g, r, 0] = pads[g]
                 continue
             for g, t in enumerate(rc.table_arrays()):
                 n = min(len(t), self.MB)
@@ -242,17 +282,18 @@ class DecodeRunner:
             slot.eager_steps += 1
 
     def _key(self, caches: Sequence[RequestCache], sampling: int, feed: str, ahead: int = 1,
-             portion: Optional[Tuple[RequestCache, int]] = None) -> tuple:
-        longest = max(rc.num_tokens for rc in caches) + ahead
+             portion: Optional[Tuple[RequestCache, int, bool]] = None) -> tuple:
+        longest = max([rc.num_tokens for rc in caches] + [0]) + ahead
         if portion is not None:
             longest = max(longest, portion[0].num_tokens + portion[1])
         kv_cap = 256
         while kv_cap < longest:
             kv_cap *= 2
-        return (bucket_for(len(caches)), kv_cap, int(sampling), feed, portion[1] if portion else 0)
+        return (bucket_for(len(caches)), kv_cap, int(sampling), feed,
+                portion_bucket(portion[1]) if portion else 0, bool(portion[2]) if portion else False)
 
     def can_take(self, caches: Sequence[RequestCache],
-                 portion: Optional[Tuple[RequestCache, int]] = None) -> bool:
+                 portion: Optional[Tuple[RequestCache, int, bool]] = None) -> bool:
         if portion is not None and self.cache.pages_for(portion[0].num_tokens + portion[1]) > self.MB:
             return False
         return all(self.cache.pages_for(rc.num_tokens + 1) <= self.MB for rc in caches)
@@ -276,35 +317,51 @@ class DecodeRunner:
         every row is greedy, else the width of the rows' recent-token buffer
         (``recent_width``).  It may run while the
         step before is still on the GPU (its uploads are waited for first).
-        ``portion``: (request, rows) of one prompt portion that rides along with
-        the decoded tokens, continuing its request where the cache ends; such a
-        step is recorded per (bucket, rows of the portion, cache-length class)."""
+        ``portion``: (request, rows, whether its last row's logits are wanted) of
+        one prompt portion that rides along with the decoded tokens (there may be
+        none), continuing its request where the cache ends; such a step is
+        recorded per (bucket, bucket of the portion's rows, cache-length class)."""
         B = len(caches)
         slot = self._slot(self._key(caches, sampling, "host", portion=portion))
         if slot.uploaded is not None:
             slot.uploaded.synchronize()  # the pinned mirrors are free to be written again
         pad = slot.size - B
         if portion is not None:
-            prc, P = portion
-            size, rows, entries = slot.size, slot.size + P, slot.size + 1
+            prc, n, _wants = portion
+            size, P = slot.size, slot.portion
+            rows, entries = size + P, size + 2
+            o = self._portion_offsets(size, P)
             hn = slot.host_np
-            pos, q0 = hn[rows: 2 * rows], hn[2 * rows: 2 * rows + entries]
-            kv, sl = hn[2 * rows + entries: 2 * rows + 2 * entries], hn[2 * rows + 2 * entries:]
+            pos, rowe = hn[o["pos"]: o["pos"] + rows], hn[o["rowe"]: o["rowe"] + rows]
+            cu, q0 = hn[o["cu"]: o["cu"] + entries + 1], hn[o["q0"]: o["q0"] + entries]
+            kv, sl = hn[o["kv"]: o["kv"] + entries], hn[o["sl"]: o["sl"] + entries]
             q0[:B] = [rc.num_tokens for rc in caches]
             sl[:B] = [rc.slot for rc in caches]
             if pad:
-                hn[B:size] = 0
+                hn[o["tok"] + B: o["tok"] + size] = 0
                 q0[B:size] = 0
                 sl[B:size] = self.cache.pad_slot
             pos[:size] = q0[:size]
             kv[:size] = q0[:size] + 1
+            rowe[:size] = range(size)
+            cu[: size + 1] = range(size + 1)
             start = prc.num_tokens
-            pos[size:] = range(start, start + P)
-            q0[size], kv[size], sl[size] = start, start + P, prc.slot
-            padded = list(caches) + [None] * pad + [prc]
+            # the portion's n rows, then the P - n rows of the entry that belongs to nobody
+            pos[size: size + n] = range(start, start + n)
+            pos[size + n:] = range(P - n)
+            rowe[size: size + n] = size
+            rowe[size + n:] = size + 1
+            cu[size + 1], cu[size + 2] = size + n, rows
+            q0[size], kv[size], sl[size] = start, start + n, prc.slot
+            q0[size + 1], kv[size + 1], sl[size + 1] = 0, P - n, self.cache.pad_slot
+            hn[o["tok"] + size + n: o["tok"] + rows] = 0
+            logit = hn[o["logit"]: o["logit"] + size + 1]
+            logit[:size] = range(size)
+            logit[size] = size + n - 1
+            padded = list(caches) + [None] * pad + [prc, None]
             if self._fill_tables(slot, padded):
                 slot.tables.copy_(slot.host_tables, non_blocking=True)
-            slot.prepared_for = tuple(rc.request_id for rc in caches) + (prc.request_id,)
+            slot.prepared_for = tuple(rc.request_id for rc in caches) + (prc.request_id, n)
             return slot
         hn = slot.host_np
         hn[1, :B] = [rc.num_tokens for rc in caches]
@@ -331,8 +388,8 @@ class DecodeRunner:
         The step's result starts on its way to the host at once; ``read_result``
         returns the results in the order of the launches."""
         B = len(caches)
-        expect = tuple(rc.request_id for rc in caches) + ((portion[0].request_id,) if portion else ())
-        if slot.prepared_for != expect or (slot.portion != (len(portion[1]) if portion else 0)):
+        expect = tuple(rc.request_id for rc in caches) + ((portion[0].request_id, len(portion[1])) if portion else ())
+        if slot.prepared_for != expect or bool(slot.portion) != (portion is not None):
             raise CacheError("decode step launched for other requests than it was prepared for")
         slot.prepared_for = None
         self.last = slot
@@ -340,7 +397,7 @@ class DecodeRunner:
             if feed_from is not None:
                 raise CacheError("a step with a prompt portion takes its tokens from the host")
             slot.host_np[:B] = tokens
-            slot.host_np[slot.size: slot.size + slot.portion] = portion[1]
+            slot.host_np[slot.size: slot.size + len(portion[1])] = portion[1]
         elif feed_from is None:
             slot.host_np[0, :B] = tokens
         slot.ints.copy_(slot.host_ints, non_blocking=True)
@@ -350,13 +407,19 @@ class DecodeRunner:
             params, recent, mask = sample
             if slot.recent is None or recent.shape[1] > slot.recent.shape[1]:
                 raise CacheError("decode step prepared without room for its rows' recent tokens")
+            # rows of `sample`: the decoded tokens, then (a portion that ends its prompt) its last row
+            n_dec = B
             slot.host_params.zero_()
             slot.host_params[:, :3] = 1.0
-            slot.host_params[:B] = params
+            slot.host_params[:n_dec] = params[:n_dec]
             slot.host_recent.zero_()
-            slot.host_recent[:B, : recent.shape[1]] = recent
+            slot.host_recent[:n_dec, : recent.shape[1]] = recent[:n_dec]
             slot.host_mask.zero_()
-            slot.host_mask[:B] = mask
+            slot.host_mask[:n_dec] = mask[:n_dec]
+            if params.shape[0] > n_dec:
+                slot.host_params[slot.size] = params[n_dec]
+                slot.host_recent[slot.size, : recent.shape[1]] = recent[n_dec]
+                slot.host_mask[slot.size] = mask[n_dec]
             slot.params.copy_(slot.host_params, non_blocking=True)
             slot.recent.copy_(slot.host_recent, non_blocking=True)
             slot.mask.copy_(slot.host_mask, non_blocking=True)
@@ -368,23 +431,25 @@ class DecodeRunner:
         slot.result_turn ^= 1
         slot.host_results[turn].copy_(slot.result, non_blocking=True)
         slot.result_events[turn].record()
-        self._reads.append((slot.host_results[turn], slot.result_events[turn], slot.size))
+        self._reads.append((slot.host_results[turn], slot.result_events[turn], slot.size,
+                            slot.selected.shape[0]))
         for rc in caches:
             self.cache.commit(rc, 1)
         if portion is not None:
-            self.cache.commit(portion[0], slot.portion)
+            self.cache.commit(portion[0], len(portion[1]))
         self.runner.steps_run += 1
-        self.runner.rows_run += B + slot.portion
+        self.runner.rows_run += B + (len(portion[1]) if portion is not None else 0)
         return slot.selected[:B]
 
-    def read_result(self, n: int) -> Tuple[List[int], int]:
-        """The tokens selected by the oldest launched step not read yet and the
-        error word after it, through pinned memory (this waits for that step, not
-        for one launched after it)."""
-        buf, event, size = self._reads.popleft()
+    def read_result(self, n: int, portion_too: bool = False) -> Tuple[List[int], int]:
+        """The tokens selected by the oldest launched step not read yet - for its
+        first ``n`` decoded tokens and, with ``portion_too``, for the last row of
+        its prompt portion - and the error word after it, through pinned memory
+        (this waits for that step, not for one launched after it)."""
+        buf, event, size, n_sel = self._reads.popleft()
         event.synchronize()
         host = buf.tolist()
-        return host[:n], host[size]
+        return host[:n] + ([host[size]] if portion_too else []), host[n_sel]
 
     # ---- fed from the device ---------------------------------------------------------------
     def pin(self, caches: Sequence[RequestCache], tokens: Sequence[int], steps: int) -> None:

@@ -156,17 +156,19 @@ class Engine:
             if in_flight:
                 chosen = True
             elif riding is not None:
-                # decoded tokens and one prompt portion: recorded per (bucket, rows of the portion)
-                wanting = [p for p in plan.portions if p is not riding]
-                caches = [p.seq.cache for p in wanting]
-                choices = choices[: len(wanting)]
+                # decoded tokens (there may be none) and one prompt portion: recorded per (bucket
+                # of the batch, bucket of the portion's rows)
+                decodes = [p for p in plan.portions if p is not riding]
+                caches = [p.seq.cache for p in decodes]
+                wanting = decodes + ([riding] if riding.wants_logits else [])
+                # (`choices` is in the order of `wanting`: the decoded tokens, then the portion's last row)
                 width = self._recent_width(choices)
                 sample = pack_choices(choices, width) if width else None
                 prc = riding.seq.cache
-                prepared = self.decoder.prepare(caches, width, portion=(prc, riding.count))
-                chosen = self.decoder.launch(prepared, caches, [p.seq.token_at(p.start) for p in wanting], sample,
+                prepared = self.decoder.prepare(caches, width, portion=(prc, riding.count, riding.wants_logits))
+                chosen = self.decoder.launch(prepared, caches, [p.seq.token_at(p.start) for p in decodes], sample,
                                              portion=(prc, riding.tokens))
-                self.h2d_bytes += 16 * len(wanting) + 8 * riding.count + 12
+                self.h2d_bytes += 4 * int(prepared.ints.numel())
                 logits = self.decoder.last.logits
                 decode_only = True  # the result comes back the same way
             elif decode_only:
@@ -201,7 +203,8 @@ class Engine:
                     self._ahead = (ahead, ready, launched)
             if chosen is not None:
                 if decode_only:
-                    picked, flags = self.decoder.read_result(len(wanting))
+                    with_portion = riding is not None and riding.wants_logits
+                    picked, flags = self.decoder.read_result(len(wanting) - (1 if with_portion else 0), with_portion)
                 else:
                     host = torch.cat([chosen, self.runner.rt.err]).cpu().tolist()
                     picked, flags = host[:-1], host[-1]
@@ -274,29 +277,31 @@ class Engine:
         return DecodeRunner.recent_width([sp.repetition_penalty_window for sp in rows
                                           if sp.repetition_penalty != 1.0])
 
-    GRAPH_PORTION_MIN = 64
+    GRAPH_PORTION_MIN = 16
 
     def _portion_beside_decodes(self, plan: StepPlan):
-        """The step's one prompt portion if the step is "decoded tokens, then one
-        portion that does not reach its prompt's end": such steps recur with the
-        same shape while a long prompt is fed in portions, so they are run from
-        recorded graphs like steps of decoded tokens alone.  The portion is cut by
-        a few rows where that makes the rows of the recorded step (decoded tokens
-        rounded up to their bucket, plus the portion) a multiple of the prompt
-        kernels' tile."""
-        if self.decoder is None or len(plan.portions) < 2:
+        """The step's one prompt portion if the step is "decoded tokens (or none),
+        then one prompt portion": such steps recur - while a long prompt is fed in
+        portions beside the decoding requests, and for every prompt that comes
+        alone - so they are run from recorded graphs like steps of decoded tokens
+        alone, one recording per bucket of the portion's length (a shorter portion
+        is followed by rows that belong to no request).  A portion that does not
+        end its prompt is cut by a few rows where that makes the rows of the
+        recorded step (decoded tokens rounded up to their bucket, plus the portion)
+        a multiple of the prompt kernels' tile."""
+        if self.decoder is None or not plan.portions:
             return None
         *decodes, last = plan.portions
-        if last.count < self.GRAPH_PORTION_MIN or last.wants_logits \
+        if last.count < self.GRAPH_PORTION_MIN or (last.count == 1 and last.wants_logits) \
                 or not all(p.count == 1 and p.wants_logits for p in decodes):
             return None
         m = self.config.token_multiple
-        if m > 0:
+        if m > 0 and not last.wants_logits:
             rows = bucket_for(len(decodes)) + last.count
             extra = rows % m
             if extra and extra * 16 <= rows and last.count - extra >= self.GRAPH_PORTION_MIN:
                 last.count -= extra  # its pages stay held for the next step
-        if not self.decoder.can_take([p.seq.cache for p in decodes], (last.seq.cache, last.count)):
+        if not self.decoder.can_take([p.seq.cache for p in decodes], (last.seq.cache, last.count, last.wants_logits)):
             return None
         return last
 

@@ -360,7 +360,9 @@ def test_steps_of_decoded_tokens_beside_one_prompt_portion_run_from_graphs(folde
     handles.append(engine.submit(long, long_opts))  # fed 64 tokens at a time beside three decoding requests
     engine.run_until_done(handles)
     mixed = [k for k, s in engine.decoder._slots.items() if k[4] > 0]
-    assert mixed and all(k[4] >= 56 for k in mixed)
+    # recorded per bucket of the portion's rows: 64 for the full portions, 48 for the last 38 tokens
+    # of the long prompt (whose last row's logits are wanted), 16 for the short prompts that came alone
+    assert mixed and {k[4] for k in mixed} <= {16, 48, 64} and any(k[5] for k in mixed)
     assert any(engine.decoder._slots[k].graph is not None for k in mixed)
     plain = Plain(folders["B"])
     for p, h, want in zip(short + [long], handles, alone):
@@ -452,3 +454,34 @@ def test_a_long_repetition_window_is_seen_whole_by_recorded_steps(folders):
     assert graph == eager and graph_greedy == eager_greedy
     (short, _), _ = run(True, 64)
     assert short != graph
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_of_any_length_run_from_recordings_per_bucket(folders, dtype):
+    """A prompt step - alone or beside decoding requests, ending its prompt or not - is
+    replayed from a recording made for the bucket of its length: the rows between the
+    portion's end and the bucket's belong to no request.  Prompts of many lengths, fed
+    whole or in portions, give the tokens of an engine that records nothing, and the
+    number of recordings stays small."""
+    import infernum_b200 as ib
+    model = ib.load_model(folders["B"], dtype=dtype)
+    base = dict(max_batch_size=4, block_size=8, num_blocks=160, max_prefill_tokens=48, max_tokens_per_step=64)
+    eager = ib.Engine(model, ib.BatchConfig(cuda_graphs=False, **base))
+    graphs = ib.Engine(model, ib.BatchConfig(**base))
+    plain = Plain(folders["B"])
+    lengths = [16, 17, 31, 32, 33, 47, 48, 49, 95, 96, 97, 130, 20, 40, 45]
+    prompts = [random_tokens(n, 320, 900 + n) for n in lengths]
+    sampled = ib.SamplingParams(temperature=0.8, top_p=0.9, seed=2)
+    opts = [ib.GenerateOptions(max_new_tokens=6, sampling=sampled if i % 4 == 1 else None) for i in range(len(prompts))]
+    # one by one (every step is a prompt alone), then all together (portions beside decoded tokens)
+    want = [eager.generate(p, o) for p, o in zip(prompts, opts)]
+    for p, o, w in zip(prompts, opts, want):
+        assert_same_up_to_ties(plain, p, graphs.generate(p, o), w, dtype, sampling=o.sampling)
+    together = graphs.generate_batch(prompts, opts)
+    for p, o, t, w in zip(prompts, opts, together, want):
+        assert_same_up_to_ties(plain, p, t, w, dtype, sampling=o.sampling)
+    keys = [k for k in graphs.decoder._slots if k[4] > 0]
+    assert keys and {k[4] for k in keys} <= {16, 32, 48} and len(keys) <= 24
+    assert sum(1 for k in keys if graphs.decoder._slots[k].graph is not None) >= 4
+    assert graphs.cache.free_pages() == [160] and graphs.cache.num_free_slots == 4
+    graphs.runner.check_errors()
