@@ -305,6 +305,9 @@ def scheduler_workloads(seed: int) -> dict:
     out.update({"mixed_1b_tok_s": round(r["total_tok_s"], 1), "mixed_1b_decode_tok_s": round(r["decode_tok_s"], 1),
                 "mixed_1b_prefill_tokens": r["prefill_tokens"], "mixed_1b_decode_tokens": r["decode_tokens"],
                 "mixed_1b_steps": r["steps"], "mixed_1b_budget_use": round(r["budget_use"], 3),
+                "mixed_1b_ms_per_step": round(r["ms_per_step"], 3),
+                "mixed_1b_host_ms_per_step": round(r["host_ms_per_step"], 3),
+                "mixed_1b_steps_replayed": r["steps_run"].get("replayed", 0),
                 "mixed_1b_preemptions": r["preemptions"]})
     del model
     gc.collect()

@@ -153,8 +153,12 @@ def run_mixed(model, args) -> dict:
                                sampling=ib.SamplingParams(temperature=0.8, top_p=1.0, seed=args.seed + i))
             for i in range(n_req)]
     if not args.no_warmup:
-        engine.generate_batch(prompts, opts)  # records the decode graphs of every batch bucket met
+        # a step's shape is recorded the second time it is met and replayed from the third on
+        for _ in range(2):
+            engine.generate_batch(prompts, opts)
         engine.stats = type(engine.stats)()
+    ran0 = dict(engine.decoder.counts) if engine.decoder is not None else {}
+    steps0 = engine.runner.steps_run
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = engine.generate_batch(prompts, opts)
@@ -168,7 +172,14 @@ def run_mixed(model, args) -> dict:
             "prefill_tokens": st.prefill_tokens, "decode_tokens": st.decode_tokens,
             "tokens_per_step": (st.prefill_tokens + st.decode_tokens) / max(st.steps, 1),
             "budget_use": (st.prefill_tokens + st.decode_tokens) / max(st.steps, 1) / (512 + n_req),
-            "host_seconds": st.step_seconds, "preemptions": st.preemptions}
+            # the host's own work per step against the step's whole time (the difference is spent
+            # waiting for the device: a step is bound by the device while the former is the smaller)
+            "host_ms_per_step": 1e3 * (st.step_seconds - st.wait_seconds) / max(st.steps, 1),
+            "ms_per_step": 1e3 * dt / max(st.steps, 1), "preemptions": st.preemptions,
+            # how the timed steps ran: replayed from a recording, recorded just then, or kernel by kernel
+            "steps_run": {**{k: v - ran0.get(k, 0) for k, v in (engine.decoder.counts if engine.decoder else {}).items()},
+                          "all": engine.runner.steps_run - steps0,
+                          "recordings_kept": len(engine.decoder._slots) if engine.decoder else 0}}
 
 
 def run_pressure(model, args) -> dict:

@@ -54,6 +54,8 @@ BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
 
 
 def bucket_for(n: int) -> int:
+    if n <= 0:
+        return 0  # (a prompt portion alone: no row for a decoded token)
     for b in BUCKETS:
         if n <= b:
             return b
@@ -62,9 +64,9 @@ def bucket_for(n: int) -> int:
 
 def portion_bucket(n: int) -> int:
     """Rows a recorded step holds for a prompt portion of ``n`` rows: multiples of
-    16 up to 64, of 64 up to 512, of 128 up to 1,024, of 256 beyond (the kernels
-    for prompts work on tiles of up to 256 rows, so the padding costs little)."""
-    step = 16 if n <= 64 else 64 if n <= 512 else 128 if n <= 1024 else 256
+    16 up to 64, of 64 beyond.  A portion cut at ``max_prefill_tokens`` fills its
+    bucket; only the last portion of a prompt leaves rows over, 32 on average."""
+    step = 16 if n <= 64 else 64
     return -(-n // step) * step
 
 
@@ -84,7 +86,6 @@ class _Slot:
     host_tables_np: object = None  # the same for host_tables
     rows_written: List[bool] = field(default_factory=list)  # a row that pads the bucket is written once
     portion: int = 0  # rows held for the prompt portion that rides along (0: decoded tokens only)
-    portion_wants: bool = False  # the portion's last row is a logit row too (it ends its prompt)
     uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
     prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
     result: Optional[torch.Tensor] = None  # device [size + 1]: the selected tokens, then the error word
@@ -118,8 +119,8 @@ class DecodeRunner:
         return -(-w // cls.RECENT_WIDTH) * cls.RECENT_WIDTH
     # Buffers and graphs are kept for this many (bucket, cache-length class, sampling, feed,
     # portion) keys; beyond it the one unused for longest is dropped (a graph holds its own
-    # activations: some hundred MB at large layer sizes).
-    MAX_RECORDED = 48
+    # activations: some 65 KB a row at the 8B layer sizes, 35 MB for a portion of 512).
+    MAX_RECORDED = 256
 
     def __init__(self, runner: ModelRunner, max_model_len: int, use_graph: bool = True):
         self.runner = runner
@@ -134,6 +135,8 @@ class DecodeRunner:
         self.last: Optional[_Slot] = None
         # results of launched steps on their way to the host, oldest first
         self._reads: collections.deque = collections.deque(maxlen=4)
+        # how the steps so far ran: kernel by kernel, recorded (and replayed at once), replayed
+        self.counts = {"eager": 0, "recorded": 0, "replayed": 0, "dropped": 0}
 
     # ---- buffers -------------------------------------------------------------------
     def _slot(self, key: tuple) -> _Slot:
@@ -147,7 +150,8 @@ class DecodeRunner:
             if victim is None:
                 break
             del self._slots[victim]
-        size, kv_cap, sampling, _feed, portion, portion_wants = key
+            self.counts["dropped"] += 1
+        size, kv_cap, sampling, _feed, portion = key
         dev = self.rt.device
         G = len(self.cache.groups)
         arange = torch.arange(size + 1, dtype=torch.int32, device=dev)
@@ -179,17 +183,18 @@ class DecodeRunner:
                 n_rows=rows, n_entries=entries, token_ids=view("tok", rows), positions=view("pos", rows),
                 row_entry=view("rowe", rows), cu_rows=view("cu", entries + 1), q_start=view("q0", entries),
                 kv_len=view("kv", entries), slot_ids=view("sl", entries),
-                logit_rows=view("logit", size + (1 if portion_wants else 0)),
+                # (the portion's last row is always a logit row: one row more through the head
+                # costs nothing, and a step whose portion ends its prompt needs no recording of its own)
+                logit_rows=view("logit", size + 1),
                 block_tables=[tables[g] for g in range(G)],
                 # (for launch geometry: the portion at its longest, the entry behind it empty)
                 host_cu_rows=list(range(size + 1)) + [rows, rows], host_kv_len=[], max_rows_per_entry=portion,
                 max_kv_len=kv_cap, all_decode=False)
-        n_sel = size + (1 if portion and portion_wants else 0)   # rows whose token is selected
+        n_sel = size + (1 if portion else 0)   # rows whose token is selected
         slot = _Slot(size=size, ints=ints, host_ints=host_ints, tables=tables,
                      host_tables=torch.full(tuple(tables.shape), -1, dtype=torch.int32).pin_memory(),
                      selected=torch.zeros(n_sel, dtype=torch.int32, device=dev), ctx=ctx,
                      rows=[None] * tables.shape[1], rows_written=[False] * tables.shape[1], portion=portion)
-        slot.portion_wants = bool(portion and portion_wants)
         slot.host_np = slot.host_ints.numpy()
         slot.result = torch.zeros(n_sel + 1, dtype=torch.int32, device=dev)
         slot.host_results = [torch.zeros(n_sel + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -268,6 +273,7 @@ class DecodeRunner:
     def _run(self, slot: _Slot, device_feed: bool) -> None:
         if slot.graph is not None:
             slot.graph.replay()
+            self.counts["replayed"] += 1
         elif self.use_graph and slot.eager_steps >= 1:
             torch.cuda.synchronize(self.rt.device)
             graph = torch.cuda.CUDAGraph()
@@ -275,7 +281,9 @@ class DecodeRunner:
                 self._body(slot, device_feed)
             slot.graph = graph
             graph.replay()
+            self.counts["recorded"] += 1
         else:
+            self.counts["eager"] += 1
             before = core.LAUNCHES
             self._body(slot, device_feed)
             slot.launches_per_step = core.LAUNCHES - before
@@ -286,11 +294,18 @@ class DecodeRunner:
         longest = max([rc.num_tokens for rc in caches] + [0]) + ahead
         if portion is not None:
             longest = max(longest, portion[0].num_tokens + portion[1])
+        # cache-length classes: powers of two for decoded tokens alone, of four beside a portion
+        # (their kernels' plans depend less on it, and the classes multiply the recordings)
         kv_cap = 256
         while kv_cap < longest:
-            kv_cap *= 2
-        return (bucket_for(len(caches)), kv_cap, int(sampling), feed,
-                portion_bucket(portion[1]) if portion else 0, bool(portion[2]) if portion else False)
+            kv_cap *= 4 if portion is not None else 2
+        # A portion that ends its prompt has any length: rounded up to its bucket.  One that does
+        # not was cut by the scheduler at ``max_prefill_tokens`` (less a few rows that make the
+        # step's rows a multiple of the prompt kernels' tile): kept as it is.
+        rows = 0
+        if portion is not None:
+            rows = portion_bucket(portion[1]) if portion[2] else -(-portion[1] // 8) * 8
+        return (bucket_for(len(caches)), kv_cap, int(sampling), feed, rows)
 
     def can_take(self, caches: Sequence[RequestCache],
                  portion: Optional[Tuple[RequestCache, int, bool]] = None) -> bool:

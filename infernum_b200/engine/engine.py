@@ -67,6 +67,7 @@ class EngineStats:
     preemptions: int = 0
     generated_tokens: int = 0
     step_seconds: float = 0.0
+    wait_seconds: float = 0.0  # of those, spent waiting for the device's results (the rest is the host's own work)
     ahead_used: int = 0    # decode steps that ran from a plan made while the step before them ran
     ahead_voided: int = 0  # such plans dropped because a request ended or arrived meanwhile
     ahead_launched: int = 0  # of the former, those launched before the step before them was read
@@ -202,12 +203,14 @@ class Engine:
                     launched = ready is not None and riding is None and self._launch_ahead(plan, ahead, ready, nxt)
                     self._ahead = (ahead, ready, launched)
             if chosen is not None:
+                t_wait = time.perf_counter()
                 if decode_only:
                     with_portion = riding is not None and riding.wants_logits
                     picked, flags = self.decoder.read_result(len(wanting) - (1 if with_portion else 0), with_portion)
                 else:
                     host = torch.cat([chosen, self.runner.rt.err]).cpu().tolist()
                     picked, flags = host[:-1], host[-1]
+                self.stats.wait_seconds += time.perf_counter() - t_wait
                 self.d2h_bytes += 4 * (len(picked) + 1)
                 if flags:
                     self.runner.check_errors()

@@ -361,8 +361,8 @@ def test_steps_of_decoded_tokens_beside_one_prompt_portion_run_from_graphs(folde
     engine.run_until_done(handles)
     mixed = [k for k, s in engine.decoder._slots.items() if k[4] > 0]
     # recorded per bucket of the portion's rows: 64 for the full portions, 48 for the last 38 tokens
-    # of the long prompt (whose last row's logits are wanted), 16 for the short prompts that came alone
-    assert mixed and {k[4] for k in mixed} <= {16, 48, 64} and any(k[5] for k in mixed)
+    # of the long prompt, 16 for the short prompts that came alone
+    assert mixed and {k[4] for k in mixed} <= {16, 48, 64}
     assert any(engine.decoder._slots[k].graph is not None for k in mixed)
     plain = Plain(folders["B"])
     for p, h, want in zip(short + [long], handles, alone):
