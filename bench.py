@@ -248,29 +248,44 @@ def time_e2e(model, batch, prompt_len, steps, warmup, page_size, seed, launch_ah
     return out
 
 
-def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3):
+def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3, recorded=False):
+    """One step over a whole prompt of ``T`` tokens, timed on the device.
+    ``recorded``: the way ``Engine`` runs a prompt that comes alone - replayed from
+    a recording made for the bucket of its length - with the host's own time for
+    the step beside it (a step is bound by the device while that is the smaller)."""
     import torch
 
     from infernum_b200.cache import CacheManager
+    from infernum_b200.engine.decode import DecodeRunner
     from infernum_b200.engine.step import ModelRunner, StepEntry
 
     cache = CacheManager(model.cache_needs(), page_size=page_size, num_pages=-(-T // page_size) + 2,
                          max_requests=1, dtype=model.rt.dtype, device=model.rt.device)
     runner = ModelRunner(model, cache, max_rows=T, max_entries=1)
+    session = DecodeRunner(runner, T + 8) if recorded else None
     g = torch.Generator().manual_seed(5)
-    times = []
-    for i in range(reps + 2):
+    times, host = [], []
+    for i in range(reps + (3 if recorded else 2)):
         prompt = torch.randint(0, model.spec.vocab_size, (T,), generator=g).tolist()
         rc = cache.admit(("prefill", i))
         cache.extend(rc, T)
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         start.record()
-        runner.step([StepEntry(rc, prompt, [T - 1])])
+        if recorded:
+            slot = session.prepare([], 0, portion=(rc, T, True))
+            session.launch(slot, [], [], None, portion=(rc, prompt))
+        else:
+            runner.step([StepEntry(rc, prompt, [T - 1])])
         end.record()
+        t1 = time.perf_counter()
         torch.cuda.synchronize()
-        if i >= 2:
+        if recorded:
+            session.read_result(0, True)
+        if i >= (3 if recorded else 2):
             times.append(start.elapsed_time(end))
+            host.append((t1 - t0) * 1e3)
         cache.release(rc)
     runner.check_errors()
     ms = sorted(times)[len(times) // 2]
@@ -278,7 +293,7 @@ def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3):
     peak = peaks["bf16_tflops_sustained"]
     del runner, cache
     torch.cuda.empty_cache()
-    return {"value": T * 1000.0 / ms, "tokens": T, "ms": ms,
+    return {"value": T * 1000.0 / ms, "tokens": T, "ms": ms, "host_ms": sorted(host)[len(host) // 2],
             "frac": flops / (ms * 1e-3) / (peak * 1e12), "tflops": flops / (ms * 1e-3) / 1e12,
             "peak_tflops": peak,
             # the same against the burst rate of the library product (a kernel timed in isolation)
@@ -421,6 +436,14 @@ def main() -> int:
             points["decode_b8_ctx8k"] = round(r["tokens_per_s"], 1)
             points["decode_b8_ctx8k_hbm_frac"] = round(
                 r["bytes_per_step"] / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        if not args.skip_extras:
+            # short prompts, the way the engine runs a prompt that comes alone: device time, the
+            # host's own time for the step, and the fraction of the sustained bf16 rate
+            for T in (256, 512):
+                r = time_prefill(model, cfg, layers, T, args.page_size, peaks, recorded=True)
+                points[f"prefill_{T}_ms"] = round(r["ms"], 3)
+                points[f"prefill_{T}_host_ms"] = round(r["host_ms"], 3)
+                points[f"prefill_{T}_frac"] = round(r["frac"], 4)
         prefill = None
         if cool is not None:
             prefill = time_prefill(model, cfg, layers, 2048, args.page_size, peaks)
