@@ -345,10 +345,10 @@ def scheduler_workloads(seed: int) -> dict:
     # the same in true 32-bit, where a preempted request must reproduce its tokens exactly
     # (four layers and eight requests: the 32-bit products run on the FMA units)
     args = SimpleNamespace(model="13b", workload="pressure", solo_checks=4,
-                           **dict(base, dtype="f32", layers=4, requests=8))
+                           **dict(base, dtype="f32", layers=4, requests=8, prompt_len=1024, new_tokens=256))
     model = cli.load(args)
     r = cli.run_pressure(model, args)
-    out.update({"pressure_13b_f32_layers": 4, "pressure_13b_f32_requests": 8,
+    out.update({"pressure_13b_f32_layers": 4, "pressure_13b_f32_requests": 8, "pressure_13b_f32_prompt_len": 1024,
                 "pressure_13b_f32_preemptions": r["preemptions"],
                 "pressure_13b_f32_solo_checked": r["solo_checked"],
                 "pressure_13b_f32_identical_to_solo": r["identical_to_solo"]})

@@ -230,7 +230,7 @@ def run_pressure(model, args) -> dict:
         rc = solo.cache.admit(("gap", i))
         seq, pos, logits = prompts[i] + want[:k], 0, None
         while pos < len(seq):
-            n = min(2048, len(seq) - pos)
+            n = min(512, solo.runner.max_rows, len(seq) - pos)
             logits = solo.runner.step([StepEntry(rc, seq[pos: pos + n], [n - 1] if pos + n == len(seq) else [])])
             pos += n
         row = logits[0].float()
