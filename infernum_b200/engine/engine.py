@@ -89,7 +89,7 @@ class Engine:
         self.sampler = Sampler(rt.device)
         self.stats = EngineStats()
         self._handles: Dict[int, RequestHandle] = {}
-        self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if cfg.cuda_graphs else None
+        self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if cfg.cuda_graphs and model.replayable else None
         # the next decode step, planned and prepared while the one before it ran
         # (plan, prepared buffers, whether it is on the GPU already)
         self._ahead: Optional[Tuple[StepPlan, object, bool]] = None

@@ -65,6 +65,11 @@ class Model:
             part.bind(weights)
         self.bound = True
 
+    @property
+    def replayable(self) -> bool:
+        """Whether every part can run from a recorded CUDA graph."""
+        return all(part.all_replayable() for part in self._all_parts())
+
     def cache_needs(self) -> List[CacheNeed]:
         needs = []
         for pos, item in enumerate(self.schedule):

@@ -136,10 +136,19 @@ class Part:
     """Base of all parts.  ``params`` are the part's own sizes and constants."""
 
     kind: str = ""
+    # Recurring steps are recorded as CUDA graphs and replayed with new
+    # contents in the step's device tensors.  A part whose ``forward`` cannot
+    # run that way (it branches on values it reads back from the device, or on
+    # host-side fields that differ between steps of one shape) sets this to
+    # False, and an engine with such a part runs every step eagerly.
+    replayable: bool = True
 
     def __init__(self, params: Dict[str, Any], rt: Runtime):
         self.params = dict(params)
         self.rt = rt
+
+    def all_replayable(self) -> bool:
+        return bool(self.replayable)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         """Checkpoint tensor name -> what it must look like."""
@@ -221,6 +230,9 @@ class Block(Part):
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in self.parts.values())
+
+    def all_replayable(self) -> bool:
+        return bool(self.replayable) and all(p.all_replayable() for p in self.parts.values())
 
     def forward(self, stream: "ResidualStream", ctx: Any, cache: Any) -> None:
         raise NotImplementedError

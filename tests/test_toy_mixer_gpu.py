@@ -215,7 +215,10 @@ def define_toy_parts():
     @register_feed_forward("toy_routed")
     class RoutedFFN(FeedForward):
         """Each token goes to the expert with the largest router logit (computed
-        in 32-bit); an expert is one matrix."""
+        in 32-bit); an expert is one matrix.  It asks the device which rows chose
+        which expert, so it cannot be replayed from a recording and says so."""
+
+        replayable = False
 
         def __init__(self, params, rt):
             super().__init__(params, rt)
@@ -324,3 +327,30 @@ def test_toy_position_encoding_and_routed_feed_forward():
     want = pl.rms_norm(h, Wd["fn"], 1e-5) @ Wd["head"].T
     assert (whole.double() - want).abs().max() / want.abs().max() < 5e-5
     assert len(set(choice.tolist())) > 1  # more than one expert was used
+
+
+def test_a_part_that_cannot_be_replayed_keeps_the_engine_eager():
+    """The routed feed-forward above reads its routing back on the host, so
+    it declares ``replayable = False``: an engine with it records no step and
+    still generates what one whole pass selects."""
+    import infernum_b200 as ib
+    from infernum_b200.cache import CacheManager
+    from infernum_b200.engine.step import ModelRunner, StepEntry
+    from infernum_b200.models.model import Model
+    from infernum_b200.ops import core
+    from infernum_b200.parts.base import Runtime
+    from infernum_b200.weights.random_init import random_tensors
+    define_toy_parts()
+    rt = Runtime(DEV, torch.float32, err=core.new_error_word(DEV))
+    model = Model(toy_parts_spec(), rt)
+    model.bind(random_tensors(model.weight_specs(), 4, DEV, torch.float32))
+    assert not model.replayable and model.layers[0].all_replayable() and not model.layers[1].all_replayable()
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=4, num_blocks=32, max_model_len=64))
+    assert engine.decoder is None
+    prompt = [3, 14, 15, 9, 2, 6]
+    got = engine.generate(prompt, ib.GenerateOptions(max_new_tokens=12, ignore_eos=True))
+    cache = CacheManager(model.cache_needs(), page_size=4, num_pages=16, max_requests=1, dtype=torch.float32, device=DEV)
+    rc = cache.admit("whole")
+    seq = prompt + got[:-1]
+    logits = ModelRunner(model, cache).step([StepEntry(rc, seq, list(range(len(prompt) - 1, len(seq))))])
+    assert logits.argmax(dim=1).tolist() == got
