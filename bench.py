@@ -274,15 +274,15 @@ def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3, recorded=False
         t0 = time.perf_counter()
         start.record()
         if recorded:
-            slot = session.prepare([], 0, portion=(rc, T, True))
-            session.launch(slot, [], [], None, portion=(rc, prompt))
+            slot = session.prepare([], 0, portions=[(rc, T, True)])
+            session.launch(slot, [], [], None, portions=[(rc, prompt, True)])
         else:
             runner.step([StepEntry(rc, prompt, [T - 1])])
         end.record()
         t1 = time.perf_counter()
         torch.cuda.synchronize()
         if recorded:
-            session.read_result(0, True)
+            session.read_result(0, [0])
         if i >= (3 if recorded else 2):
             times.append(start.elapsed_time(end))
             host.append((t1 - t0) * 1e3)

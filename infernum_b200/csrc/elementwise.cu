@@ -583,6 +583,29 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __res
 }
 
 // ---------------------------------------------------------------------------
+// Input tokens of a step that is launched while the step before it still runs:
+// row i takes the token that step selected for its row src[i]; a row with
+// src[i] < 0 keeps the token the host put there.  Launched the ordinary way,
+// behind the copy that brought `src`.
+// ---------------------------------------------------------------------------
+__global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
+                                   const int* __restrict__ selected, int n_selected, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int s = src[i];
+    if (s >= 0 && s < n_selected) tokens[i] = selected[s];
+}
+
+IB_EXPORT int ib_feed_tokens(int* tokens, const int* src, const int* selected, int n_selected, int n,
+                             void* stream) {
+    if (n <= 0) return IB_OK;
+    if (!tokens || !src || !selected || n_selected <= 0) return IB_ERR_BAD_ARG;
+    feed_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, src, selected, n_selected, n);
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
 // The first launch of every step.  The kernels of this package start under the
 // tail of their predecessor (programmatic dependent launch) and some read what
 // describes the step - positions, block tables, row offsets - before they wait

@@ -11,14 +11,16 @@ bucket.  Requests may come and go between steps without a new recording; a
 graph is recorded per (bucket, cache-length class, width of the sampling rows), the first
 time it is needed, after one eager step.
 
-A step of decoded tokens and one prompt portion (the step that recurs while
-prompts are fed in portions, and every step of a prompt that is alone) is
-recorded the same way, per bucket of the portion's length (``portion_bucket``):
-the portion's rows are followed by rows of an entry that belongs to no request
-(it attends to, and writes, the page reserved for padding), so that portions of
-any length up to the bucket replay one recording.  What differs from step to
-step - which rows belong to the portion, where its last row is - is data in the
-device buffers, not shape.
+A step of decoded tokens and a few prompt portions (the steps that recur while
+prompts are fed in portions - one portion, or the end of one prompt and the
+start of the next - and every step of a prompt that is alone) is recorded the
+same way, per bucket of the portions' rows together (``portion_bucket``): the
+recorded step has ``PORTION_ENTRIES`` entries for portions, of which a step may
+leave some empty, followed by an entry that belongs to no request and takes the
+rows left over (it attends to, and writes, the page reserved for padding), so
+that portions of any lengths up to the bucket replay one recording.  What
+differs from step to step - which rows belong to which portion, where their
+last rows are - is data in the device buffers, not shape.
 
 Three ways to feed it:
   * from the host (``Engine``): tokens, positions and lengths are copied from
@@ -75,7 +77,7 @@ class _Slot:
     """Buffers and graph of one (bucket, cache-length class, sampling, feed) key."""
 
     size: int
-    ints: torch.Tensor  # device [4, size]: tokens, positions, kv_len, slot ids
+    ints: torch.Tensor  # device [5, size]: tokens, positions, kv_len, slot ids, token sources
     host_ints: torch.Tensor  # pinned mirror
     tables: torch.Tensor  # device [groups, size, MB]
     host_tables: torch.Tensor  # pinned mirror
@@ -85,7 +87,7 @@ class _Slot:
     host_np: object = None  # host_ints' memory as a numpy array (cheap to fill from lists)
     host_tables_np: object = None  # the same for host_tables
     rows_written: List[bool] = field(default_factory=list)  # a row that pads the bucket is written once
-    portion: int = 0  # rows held for the prompt portion that rides along (0: decoded tokens only)
+    portion: int = 0  # rows held for the prompt portions that ride along (0: decoded tokens only)
     uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
     prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
     result: Optional[torch.Tensor] = None  # device [size + 1]: the selected tokens, then the error word
@@ -121,6 +123,8 @@ class DecodeRunner:
     # portion) keys; beyond it the one unused for longest is dropped (a graph holds its own
     # activations: some 65 KB a row at the 8B layer sizes, 35 MB for a portion of 512).
     MAX_RECORDED = 256
+    # Entries a recorded step holds for prompt portions (a step with more runs kernel by kernel).
+    PORTION_ENTRIES = 3
 
     def __init__(self, runner: ModelRunner, max_model_len: int, use_graph: bool = True):
         self.runner = runner
@@ -156,8 +160,11 @@ class DecodeRunner:
         G = len(self.cache.groups)
         arange = torch.arange(size + 1, dtype=torch.int32, device=dev)
         if portion == 0:
-            ints = torch.zeros((4, size), dtype=torch.int32, device=dev)
-            host_ints = torch.zeros((4, size), dtype=torch.int32).pin_memory()
+            # (row 4: for a step launched behind another, which of that step's selected tokens
+            # each row takes as its input; -1 for a token that comes from the host)
+            ints = torch.zeros((5, size), dtype=torch.int32, device=dev)
+            host_ints = torch.zeros((5, size), dtype=torch.int32).pin_memory()
+            host_ints[4] = -1
             tables = torch.full((G, size, self.MB), -1, dtype=torch.int32, device=dev)
             ctx = StepContext(
                 n_rows=size, n_entries=size, token_ids=ints[0], positions=ints[1], row_entry=arange[:size],
@@ -168,12 +175,14 @@ class DecodeRunner:
             # one row per entry and the longest cache the recorded step may meet, ``max_kv_len``,
             # and keeps its plan in ``ctx.scratch``, which lives as long as the recording)
         else:
-            # `size` decoded tokens (one row and one entry each), then the prompt portion's
-            # entry with up to `portion` rows, then an entry of the rows left over, which
-            # belongs to no request.  One flat buffer holds all that changes from step to
+            # `size` decoded tokens (one row and one entry each), then the entries of the prompt
+            # portions with up to `portion` rows together, then an entry of the rows left over,
+            # which belongs to no request.  One flat buffer holds all that changes from step to
             # step: tokens | positions | row_entry (a row each) | cu_rows (entries + 1) |
-            # q_start | kv_len | slots (an entry each) | logit rows (size + 1).
-            rows, entries = size + portion, size + 2
+            # q_start | kv_len | slots (an entry each) | logit rows (decoded rows and the last
+            # row of every portion) | token sources of the decoded rows (size; see above).
+            K = self.PORTION_ENTRIES
+            rows, entries = size + portion, size + K + 1
             offs = self._portion_offsets(size, portion)
             ints = torch.zeros(offs["end"], dtype=torch.int32, device=dev)
             host_ints = torch.zeros(offs["end"], dtype=torch.int32).pin_memory()
@@ -183,14 +192,14 @@ class DecodeRunner:
                 n_rows=rows, n_entries=entries, token_ids=view("tok", rows), positions=view("pos", rows),
                 row_entry=view("rowe", rows), cu_rows=view("cu", entries + 1), q_start=view("q0", entries),
                 kv_len=view("kv", entries), slot_ids=view("sl", entries),
-                # (the portion's last row is always a logit row: one row more through the head
+                # (a portion's last row is always a logit row: a row more through the head
                 # costs nothing, and a step whose portion ends its prompt needs no recording of its own)
-                logit_rows=view("logit", size + 1),
+                logit_rows=view("logit", size + K),
                 block_tables=[tables[g] for g in range(G)],
-                # (for launch geometry: the portion at its longest, the entry behind it empty)
-                host_cu_rows=list(range(size + 1)) + [rows, rows], host_kv_len=[], max_rows_per_entry=portion,
+                # (for launch geometry: one portion at its longest, the entries behind it empty)
+                host_cu_rows=list(range(size + 1)) + [rows] * (K + 1), host_kv_len=[], max_rows_per_entry=portion,
                 max_kv_len=kv_cap, all_decode=False)
-        n_sel = size + (1 if portion else 0)   # rows whose token is selected
+        n_sel = size + (self.PORTION_ENTRIES if portion else 0)   # rows whose token is selected
         slot = _Slot(size=size, ints=ints, host_ints=host_ints, tables=tables,
                      host_tables=torch.full(tuple(tables.shape), -1, dtype=torch.int32).pin_memory(),
                      selected=torch.zeros(n_sel, dtype=torch.int32, device=dev), ctx=ctx,
@@ -211,13 +220,13 @@ class DecodeRunner:
         self._slots[key] = slot
         return slot
 
-    @staticmethod
-    def _portion_offsets(size: int, portion: int) -> Dict[str, int]:
+    @classmethod
+    def _portion_offsets(cls, size: int, portion: int) -> Dict[str, int]:
         """Where the parts of a portion step's flat int32 buffer begin."""
-        rows, entries = size + portion, size + 2
+        rows, entries = size + portion, size + cls.PORTION_ENTRIES + 1
         offs, at = {}, 0
         for name, n in (("tok", rows), ("pos", rows), ("rowe", rows), ("cu", entries + 1), ("q0", entries),
-                        ("kv", entries), ("sl", entries), ("logit", size + 1)):
+                        ("kv", entries), ("sl", entries), ("logit", size + cls.PORTION_ENTRIES), ("src", size)):
             offs[name] = at
             at += n
         offs["end"] = at
@@ -290,26 +299,29 @@ class DecodeRunner:
             slot.eager_steps += 1
 
     def _key(self, caches: Sequence[RequestCache], sampling: int, feed: str, ahead: int = 1,
-             portion: Optional[Tuple[RequestCache, int, bool]] = None) -> tuple:
+             portions: Optional[Sequence[Tuple[RequestCache, int, bool]]] = None) -> tuple:
         longest = max([rc.num_tokens for rc in caches] + [0]) + ahead
-        if portion is not None:
-            longest = max(longest, portion[0].num_tokens + portion[1])
+        for prc, n, _wants in portions or ():
+            longest = max(longest, prc.num_tokens + n)
         # cache-length classes: powers of two for decoded tokens alone, of four beside a portion
         # (their kernels' plans depend less on it, and the classes multiply the recordings)
         kv_cap = 256
         while kv_cap < longest:
-            kv_cap *= 4 if portion is not None else 2
-        # A portion that ends its prompt has any length: rounded up to its bucket.  One that does
-        # not was cut by the scheduler at ``max_prefill_tokens`` (less a few rows that make the
-        # step's rows a multiple of the prompt kernels' tile): kept as it is.
+            kv_cap *= 4 if portions else 2
+        # Portions that end their prompts have any length: their rows together are rounded up
+        # to a bucket.  When the last one does not end its prompt, the scheduler cut it at
+        # ``max_prefill_tokens`` or at the step's budget (less a few rows that make the step's rows
+        # a multiple of the prompt kernels' tile): such totals recur and are kept as they are.
         rows = 0
-        if portion is not None:
-            rows = portion_bucket(portion[1]) if portion[2] else -(-portion[1] // 8) * 8
+        if portions:
+            total = sum(n for _rc, n, _wants in portions)
+            rows = portion_bucket(total) if portions[-1][2] else -(-total // 8) * 8
         return (bucket_for(len(caches)), kv_cap, int(sampling), feed, rows)
 
     def can_take(self, caches: Sequence[RequestCache],
-                 portion: Optional[Tuple[RequestCache, int, bool]] = None) -> bool:
-        if portion is not None and self.cache.pages_for(portion[0].num_tokens + portion[1]) > self.MB:
+                 portions: Optional[Sequence[Tuple[RequestCache, int, bool]]] = None) -> bool:
+        if portions is not None and (len(portions) > self.PORTION_ENTRIES or any(
+                self.cache.pages_for(prc.num_tokens + n) > self.MB for prc, n, _wants in portions)):
             return False
         return all(self.cache.pages_for(rc.num_tokens + 1) <= self.MB for rc in caches)
 
@@ -326,30 +338,31 @@ class DecodeRunner:
         return out
 
     def prepare(self, caches: Sequence[RequestCache], sampling: int,
-                portion: Optional[Tuple[RequestCache, int]] = None) -> _Slot:
+                portions: Optional[Sequence[Tuple[RequestCache, int, bool]]] = None) -> _Slot:
         """The part of a step that does not need the input tokens: picks the
         buffers, fills positions, slots and block tables.  ``sampling``: 0 when
         every row is greedy, else the width of the rows' recent-token buffer
         (``recent_width``).  It may run while the
         step before is still on the GPU (its uploads are waited for first).
-        ``portion``: (request, rows, whether its last row's logits are wanted) of
-        one prompt portion that rides along with the decoded tokens (there may be
-        none), continuing its request where the cache ends; such a step is
-        recorded per (bucket, bucket of the portion's rows, cache-length class)."""
+        ``portions``: (request, rows, whether its last row's logits are wanted) of
+        up to ``PORTION_ENTRIES`` prompt portions that ride along with the decoded
+        tokens (there may be none), each continuing its request where the cache
+        ends; such a step is recorded per (bucket, bucket of the portions' rows
+        together, cache-length class)."""
         B = len(caches)
-        slot = self._slot(self._key(caches, sampling, "host", portion=portion))
+        slot = self._slot(self._key(caches, sampling, "host", portions=portions))
         if slot.uploaded is not None:
             slot.uploaded.synchronize()  # the pinned mirrors are free to be written again
         pad = slot.size - B
-        if portion is not None:
-            prc, n, _wants = portion
-            size, P = slot.size, slot.portion
-            rows, entries = size + P, size + 2
+        if portions:
+            size, P, K = slot.size, slot.portion, self.PORTION_ENTRIES
+            rows, entries = size + P, size + K + 1
             o = self._portion_offsets(size, P)
             hn = slot.host_np
             pos, rowe = hn[o["pos"]: o["pos"] + rows], hn[o["rowe"]: o["rowe"] + rows]
             cu, q0 = hn[o["cu"]: o["cu"] + entries + 1], hn[o["q0"]: o["q0"] + entries]
             kv, sl = hn[o["kv"]: o["kv"] + entries], hn[o["sl"]: o["sl"] + entries]
+            logit = hn[o["logit"]: o["logit"] + size + K]
             q0[:B] = [rc.num_tokens for rc in caches]
             sl[:B] = [rc.slot for rc in caches]
             if pad:
@@ -360,23 +373,37 @@ class DecodeRunner:
             kv[:size] = q0[:size] + 1
             rowe[:size] = range(size)
             cu[: size + 1] = range(size + 1)
-            start = prc.num_tokens
-            # the portion's n rows, then the P - n rows of the entry that belongs to nobody
-            pos[size: size + n] = range(start, start + n)
-            pos[size + n:] = range(P - n)
-            rowe[size: size + n] = size
-            rowe[size + n:] = size + 1
-            cu[size + 1], cu[size + 2] = size + n, rows
-            q0[size], kv[size], sl[size] = start, start + n, prc.slot
-            q0[size + 1], kv[size + 1], sl[size + 1] = 0, P - n, self.cache.pad_slot
-            hn[o["tok"] + size + n: o["tok"] + rows] = 0
-            logit = hn[o["logit"]: o["logit"] + size + 1]
             logit[:size] = range(size)
-            logit[size] = size + n - 1
-            padded = list(caches) + [None] * pad + [prc, None]
+            # the portions' rows one after the other (an entry that is not used has none), then
+            # the rows left over, in the entry that belongs to nobody
+            at = size
+            for j in range(K):
+                e = size + j
+                if j < len(portions):
+                    prc, n, _wants = portions[j]
+                    start = prc.num_tokens
+                    pos[at: at + n] = range(start, start + n)
+                    rowe[at: at + n] = e
+                    q0[e], kv[e], sl[e] = start, start + n, prc.slot
+                    at += n
+                else:
+                    q0[e], kv[e], sl[e] = 0, 0, self.cache.pad_slot
+                cu[e + 1] = at
+                logit[e] = max(at - 1, size)
+            left = rows - at
+            if left < 0:
+                raise CacheError("more portion rows than the recorded step holds")
+            pos[at:] = range(left)
+            rowe[at:] = size + K
+            cu[size + K + 1] = rows
+            q0[size + K], kv[size + K], sl[size + K] = 0, left, self.cache.pad_slot
+            hn[o["tok"] + at: o["tok"] + rows] = 0
+            padded = list(caches) + [None] * pad + [prc for prc, _n, _w in portions] \
+                + [None] * (K - len(portions)) + [None]
             if self._fill_tables(slot, padded):
                 slot.tables.copy_(slot.host_tables, non_blocking=True)
-            slot.prepared_for = tuple(rc.request_id for rc in caches) + (prc.request_id, n)
+            slot.prepared_for = tuple(rc.request_id for rc in caches) + tuple(
+                (prc.request_id, n) for prc, n, _w in portions)
             return slot
         hn = slot.host_np
         hn[1, :B] = [rc.num_tokens for rc in caches]
@@ -393,36 +420,55 @@ class DecodeRunner:
 
     def launch(self, slot: _Slot, caches: Sequence[RequestCache], tokens: Optional[Sequence[int]],
                sample: Optional[tuple] = None,
-               portion: Optional[Tuple[RequestCache, Sequence[int]]] = None,
-               feed_from: Optional[_Slot] = None) -> torch.Tensor:
+               portions: Optional[Sequence[Tuple[RequestCache, Sequence[int], bool]]] = None,
+               feed_from: Optional[_Slot] = None,
+               feed_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Uploads the tokens (and sampling rows) and runs the prepared step.
-        ``portion``: (request, its tokens of this step) when the step was prepared with one.
-        ``feed_from``: instead of ``tokens``, the step takes what the step launched
-        before it (that slot's, which may be this one) selects, row for row: it can
-        be launched while that step still runs, before the host has seen its tokens.
+        ``portions``: (request, its tokens of this step, whether its last row's
+        token is wanted) for each portion the step was prepared with.
+        ``feed_from``: the step takes input tokens from what the step launched
+        before it (that slot's, which may be this one) selects, so it can be
+        launched while that step still runs, before the host has seen its tokens.
+        ``feed_rows`` says which: decoded row ``i`` takes entry ``feed_rows[i]`` of
+        that step's selection (its decoded rows in order, then the last rows of its
+        prompt portions), or, where that is negative, ``tokens[i]`` from the host;
+        without it the rows are those of the step before, in its order, and
+        ``tokens`` is not read.  A prompt portion's own tokens always come from the host.
+        ``sample``: rows for the decoded tokens in order, then for the portions
+        whose token is wanted.
         The step's result starts on its way to the host at once; ``read_result``
         returns the results in the order of the launches."""
         B = len(caches)
-        expect = tuple(rc.request_id for rc in caches) + ((portion[0].request_id, len(portion[1])) if portion else ())
-        if slot.prepared_for != expect or bool(slot.portion) != (portion is not None):
+        expect = tuple(rc.request_id for rc in caches) + tuple(
+            (prc.request_id, len(toks)) for prc, toks, _w in portions or ())
+        if slot.prepared_for != expect or bool(slot.portion) != bool(portions):
             raise CacheError("decode step launched for other requests than it was prepared for")
         slot.prepared_for = None
         self.last = slot
-        if portion is not None:
-            if feed_from is not None:
-                raise CacheError("a step with a prompt portion takes its tokens from the host")
-            slot.host_np[:B] = tokens
-            slot.host_np[slot.size: slot.size + len(portion[1])] = portion[1]
-        elif feed_from is None:
-            slot.host_np[0, :B] = tokens
-        slot.ints.copy_(slot.host_ints, non_blocking=True)
+        if feed_from is not None and feed_rows is None:
+            feed_rows, tokens = range(B), [0] * B
+        if portions:
+            hn = slot.host_np
+            at = self._portion_offsets(slot.size, slot.portion)["src"]
+            tok_rows, src_rows = hn[:slot.size], hn[at: at + slot.size]
+            row = slot.size
+            for _prc, toks, _w in portions:
+                hn[row: row + len(toks)] = toks
+                row += len(toks)
+        else:
+            tok_rows, src_rows = slot.host_np[0], slot.host_np[4]
+        tok_rows[:B] = tokens
+        src_rows[:] = -1
         if feed_from is not None:
-            slot.ints[0, :B].copy_(feed_from.selected[:B])
+            src_rows[:B] = feed_rows
+        slot.ints.copy_(slot.host_ints, non_blocking=True)
+        if feed_from is not None and B:
+            dev_src = slot.ints[at: at + slot.size] if portions else slot.ints[4]
+            core.feed_tokens(slot.ctx.token_ids[:slot.size], dev_src, feed_from.selected)
         if sample is not None:
             params, recent, mask = sample
             if slot.recent is None or recent.shape[1] > slot.recent.shape[1]:
                 raise CacheError("decode step prepared without room for its rows' recent tokens")
-            # rows of `sample`: the decoded tokens, then (a portion that ends its prompt) its last row
             n_dec = B
             slot.host_params.zero_()
             slot.host_params[:, :3] = 1.0
@@ -431,10 +477,13 @@ class DecodeRunner:
             slot.host_recent[:n_dec, : recent.shape[1]] = recent[:n_dec]
             slot.host_mask.zero_()
             slot.host_mask[:n_dec] = mask[:n_dec]
-            if params.shape[0] > n_dec:
-                slot.host_params[slot.size] = params[n_dec]
-                slot.host_recent[slot.size, : recent.shape[1]] = recent[n_dec]
-                slot.host_mask[slot.size] = mask[n_dec]
+            k = n_dec
+            for j, (_prc, _toks, wants) in enumerate(portions or ()):
+                if wants and k < params.shape[0]:
+                    slot.host_params[slot.size + j] = params[k]
+                    slot.host_recent[slot.size + j, : recent.shape[1]] = recent[k]
+                    slot.host_mask[slot.size + j] = mask[k]
+                    k += 1
             slot.params.copy_(slot.host_params, non_blocking=True)
             slot.recent.copy_(slot.host_recent, non_blocking=True)
             slot.mask.copy_(slot.host_mask, non_blocking=True)
@@ -450,21 +499,22 @@ class DecodeRunner:
                             slot.selected.shape[0]))
         for rc in caches:
             self.cache.commit(rc, 1)
-        if portion is not None:
-            self.cache.commit(portion[0], len(portion[1]))
+        for prc, toks, _w in portions or ():
+            self.cache.commit(prc, len(toks))
         self.runner.steps_run += 1
-        self.runner.rows_run += B + (len(portion[1]) if portion is not None else 0)
+        self.runner.rows_run += B + sum(len(toks) for _prc, toks, _w in portions or ())
         return slot.selected[:B]
 
-    def read_result(self, n: int, portion_too: bool = False) -> Tuple[List[int], int]:
+    def read_result(self, n: int, portions: Sequence[int] = ()) -> Tuple[List[int], int]:
         """The tokens selected by the oldest launched step not read yet - for its
-        first ``n`` decoded tokens and, with ``portion_too``, for the last row of
-        its prompt portion - and the error word after it, through pinned memory
-        (this waits for that step, not for one launched after it)."""
+        first ``n`` decoded tokens and for the last rows of the prompt portions
+        ``portions`` (their places among the step's portions) - and the error word
+        after them, through pinned memory (this waits for that step, not for one
+        launched after it)."""
         buf, event, size, n_sel = self._reads.popleft()
         event.synchronize()
         host = buf.tolist()
-        return host[:n] + ([host[size]] if portion_too else []), host[n_sel]
+        return host[:n] + [host[size + j] for j in portions], host[n_sel]
 
     # ---- fed from the device ---------------------------------------------------------------
     def pin(self, caches: Sequence[RequestCache], tokens: Sequence[int], steps: int) -> None:
@@ -480,6 +530,7 @@ class DecodeRunner:
         B = len(caches)
         hi = slot.host_ints
         hi.zero_()
+        hi[4] = -1
         hi[0, :B] = torch.tensor(list(tokens), dtype=torch.int32)
         hi[1, :B] = torch.tensor([rc.num_tokens for rc in caches], dtype=torch.int32)
         hi[3, :B] = torch.tensor([rc.slot for rc in caches], dtype=torch.int32)

@@ -92,7 +92,8 @@ class Engine:
         self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if cfg.cuda_graphs and model.replayable else None
         # the next decode step, planned and prepared while the one before it ran
         # (plan, prepared buffers, whether it is on the GPU already)
-        self._ahead: Optional[Tuple[StepPlan, object, bool]] = None
+        self._ahead: Optional[Tuple[StepPlan, object, bool, object]] = None
+        self._flight: Dict[int, int] = {}  # request id -> where the step launched last puts its token
         self.h2d_bytes = 0  # bytes of step inputs copied to the device so far
         self.d2h_bytes = 0  # bytes of step results read back so far
 
@@ -122,9 +123,9 @@ class Engine:
     def step(self) -> List[Tuple[RequestHandle, GenerationEvent]]:
         """One scheduling round and one model step; returns the new events."""
         t0 = time.perf_counter()
-        prepared, in_flight = None, False
+        prepared, in_flight, split = None, False, None
         if self._ahead is not None:
-            plan, prepared, in_flight = self._ahead
+            plan, prepared, in_flight, split = self._ahead
             self._ahead = None
             if in_flight:
                 # It runs already, on the tokens the step before it selected.  Requests that
@@ -132,7 +133,7 @@ class Engine:
                 # is dropped below; one that arrived waits for the next step.
                 self.stats.ahead_used += 1
                 self.stats.ahead_launched += 1
-            elif self.scheduler.ahead_still_holds(plan):
+            elif self.scheduler.plan_still_holds(plan):
                 self.stats.ahead_used += 1
             else:
                 self.stats.ahead_voided += 1
@@ -144,69 +145,56 @@ class Engine:
         self.stats.preemptions = self.scheduler.num_preemptions
         events: List[Tuple[RequestHandle, GenerationEvent]] = []
         if plan.portions:
-            wanting = [p for p in plan.portions if p.wants_logits]
-            choices = []
-            for p in wanting:
-                sp = p.seq.options.sampling
-                choices.append(None if sp is None else
-                               (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
-            caches = [p.seq.cache for p in plan.portions]
-            decode_only = in_flight or (self.decoder is not None and all(
-                p.count == 1 and p.wants_logits for p in plan.portions) and self.decoder.can_take(caches))
-            riding = None if decode_only else self._portion_beside_decodes(plan)
+            # A step of decoded tokens, alone or beside a few prompt portions, runs from a
+            # recording (`split`: its decoded rows and its portions); any other step runs
+            # kernel by kernel.
+            if not in_flight:
+                split = self._recorded_shape(plan)
+            if split is not None:
+                decodes, riding = split
+                wanting = decodes + [p for p in riding if p.wants_logits]
+            else:
+                wanting = [p for p in plan.portions if p.wants_logits]
             if in_flight:
                 chosen = True
-            elif riding is not None:
-                # decoded tokens (there may be none) and one prompt portion: recorded per (bucket
-                # of the batch, bucket of the portion's rows)
-                decodes = [p for p in plan.portions if p is not riding]
-                caches = [p.seq.cache for p in decodes]
-                wanting = decodes + ([riding] if riding.wants_logits else [])
-                # (`choices` is in the order of `wanting`: the decoded tokens, then the portion's last row)
-                width = self._recent_width(choices)
-                sample = pack_choices(choices, width) if width else None
-                prc = riding.seq.cache
-                prepared = self.decoder.prepare(caches, width, portion=(prc, riding.count, riding.wants_logits))
-                chosen = self.decoder.launch(prepared, caches, [p.seq.token_at(p.start) for p in decodes], sample,
-                                             portion=(prc, riding.tokens))
-                self.h2d_bytes += 4 * int(prepared.ints.numel())
-                logits = self.decoder.last.logits
-                decode_only = True  # the result comes back the same way
-            elif decode_only:
-                width = self._recent_width(choices)
-                sample = pack_choices(choices, width) if width else None
-                if prepared is None or prepared.prepared_for != tuple(rc.request_id for rc in caches) \
-                        or (prepared.recent.shape[1] if prepared.recent is not None else 0) != width:
-                    prepared = self.decoder.prepare(caches, width)
-                chosen = self.decoder.launch(prepared, caches,
-                                             [p.seq.token_at(p.start) for p in plan.portions], sample)
-                self.h2d_bytes += 16 * len(plan.portions)
-                logits = self.decoder.last.logits
             else:
-                entries = [StepEntry(p.seq.cache, p.tokens, [p.count - 1] if p.wants_logits else [])
-                           for p in plan.portions]
-                logits = self.runner.step(entries)
-                self.h2d_bytes += self.runner.last_upload_bytes
-                chosen = self.sampler.select(logits, choices) if logits is not None and wanting else None
+                choices = []
+                for p in wanting:
+                    sp = p.seq.options.sampling
+                    choices.append(None if sp is None else
+                                   (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
+                if split is not None:
+                    caches = [p.seq.cache for p in decodes]
+                    width = self._recent_width(choices)
+                    sample = pack_choices(choices, width) if width else None
+                    if riding or prepared is None or prepared.prepared_for != tuple(rc.request_id for rc in caches) \
+                            or (prepared.recent.shape[1] if prepared.recent is not None else 0) != width:
+                        prepared = self.decoder.prepare(
+                            caches, width, portions=[(p.seq.cache, p.count, p.wants_logits) for p in riding])
+                    chosen = self.decoder.launch(prepared, caches, [p.seq.token_at(p.start) for p in decodes], sample,
+                                                 portions=[(p.seq.cache, p.tokens, p.wants_logits) for p in riding])
+                    self._note_flight(decodes, riding)
+                    self.h2d_bytes += 4 * int(prepared.ints.numel()) if riding else 16 * len(decodes)
+                else:
+                    entries = [StepEntry(p.seq.cache, p.tokens, [p.count - 1] if p.wants_logits else [])
+                               for p in plan.portions]
+                    logits = self.runner.step(entries)
+                    self.h2d_bytes += self.runner.last_upload_bytes
+                    chosen = self.sampler.select(logits, choices) if logits is not None and wanting else None
             self.scheduler.commit(plan)
-            # (after a step launched ahead in which a request turned out to have ended, the
-            # next step comes from the scheduler, which takes that request's pages back)
-            if decode_only and not (in_flight and any(p.seq.finished for p in plan.portions)):
-                # While this step runs: plan the next one and fill in all of it but the
-                # tokens, so that little is left to do between the two steps.
-                ahead = self.scheduler.plan_decode_ahead()
+            if split is not None:
+                # While this step runs: schedule the next one as if every request had the token
+                # this step selects for it, and launch it behind this one, fed on the device;
+                # where that cannot be (a repetition penalty needs the token itself), fill in
+                # all of it but the tokens, so that little is left to do between the two steps.
+                ahead = self.scheduler.plan_ahead(plan)
                 if ahead is not None:
-                    nxt = [p.seq.cache for p in ahead.portions]
-                    width = self._recent_width([p.seq.options.sampling and (p.seq.options.sampling, 0, ())
-                                                for p in ahead.portions])
-                    ready = self.decoder.prepare(nxt, width) if self.decoder.can_take(nxt) else None
-                    launched = ready is not None and riding is None and self._launch_ahead(plan, ahead, ready, nxt)
-                    self._ahead = (ahead, ready, launched)
+                    self._ahead = (ahead,) + self._launch_ahead(ahead)
             if chosen is not None:
                 t_wait = time.perf_counter()
-                if decode_only:
-                    with_portion = riding is not None and riding.wants_logits
-                    picked, flags = self.decoder.read_result(len(wanting) - (1 if with_portion else 0), with_portion)
+                if split is not None:
+                    picked, flags = self.decoder.read_result(
+                        len(decodes), [j for j, p in enumerate(riding) if p.wants_logits])
                 else:
                     host = torch.cat([chosen, self.runner.rt.err]).cpu().tolist()
                     picked, flags = host[:-1], host[-1]
@@ -217,6 +205,7 @@ class Engine:
                 for p, tok in zip(wanting, picked):
                     handle = self._handles.get(p.seq.id)
                     if handle is None or p.seq.finished:
+                        p.seq.pending = 0
                         continue  # it ended while this step, launched ahead, ran
                     emitted = self.scheduler.append_token(p.seq, tok)
                     if emitted is not None:
@@ -243,29 +232,59 @@ class Engine:
         self.stats.step_seconds += time.perf_counter() - t0
         return events
 
-    def _launch_ahead(self, plan: StepPlan, ahead: StepPlan, ready, caches) -> bool:
-        """Launches the planned next decode step now, behind the one in flight, fed
-        on the device with the tokens that one selects: the host then reads a step's
+    def _note_flight(self, decodes, riding) -> None:
+        """Remembers where the step just launched puts each request's selected token
+        (its decoded rows in order, then the last rows of its prompt portions)."""
+        self._flight = {p.seq.id: i for i, p in enumerate(decodes)}
+        for j, p in enumerate(riding):
+            if p.wants_logits:
+                self._flight[p.seq.id] = self.decoder.last.size + j
+
+    def _launch_ahead(self, ahead: StepPlan):
+        """Launches the planned next step now, behind the one in flight, with the
+        tokens that one selects fed on the device: the host then reads a step's
         tokens while the next step runs, and the GPU does not wait for the host
-        between the two.  Possible when the rows are those of the step in flight,
-        in its order, and no row's sampling needs the tokens not yet seen (a
-        repetition penalty looks at the most recent ones)."""
-        if not self.config.launch_ahead or self.decoder.last is None or self.decoder.last.portion:
-            return False
-        if [p.seq.id for p in ahead.portions] != [p.seq.id for p in plan.portions]:
-            return False
-        choices = []
-        for p in ahead.portions:
+        between the two.  Possible for the steps that run from recordings
+        (decoded tokens, with or without prompt portions) when no row's sampling
+        needs the token not yet seen (a repetition penalty looks at the most
+        recent ones).  Returns (prepared buffers or None, whether it was launched,
+        the step's decoded rows and portions if it runs from a recording)."""
+        dec = self.decoder
+        split = self._recorded_shape(ahead)
+        if split is None:
+            return None, False, None
+        decodes, riding = split
+        caches = [p.seq.cache for p in decodes]
+        can_launch = self.config.launch_ahead and dec.last is not None and not any(p.seq.pending for p in riding)
+        choices, feed_rows, tokens = [], [], []
+        for p in decodes + [p for p in riding if p.wants_logits]:
             sp = p.seq.options.sampling
-            if sp is not None and sp.repetition_penalty != 1.0:
-                return False
-            # (the token of the step in flight is not appended yet: this will be the one after it)
-            choices.append(None if sp is None else (sp, len(p.seq.generated_ids) + 1, ()))
+            if sp is None:
+                choices.append(None)
+            elif p.seq.pending:
+                # (the token of the step in flight is not appended yet: this is the one after it)
+                can_launch = can_launch and sp.repetition_penalty == 1.0
+                choices.append((sp, len(p.seq.generated_ids) + 1, ()))
+            else:
+                choices.append((sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
+        for p in decodes:
+            if p.seq.pending:
+                feed_rows.append(self._flight.get(p.seq.id, -1))
+                tokens.append(0)
+                can_launch = can_launch and feed_rows[-1] >= 0
+            else:
+                feed_rows.append(-1)
+                tokens.append(p.seq.token_at(p.start))
         width = self._recent_width(choices)
+        if not can_launch:
+            return (dec.prepare(caches, width) if not riding else None), False, split
+        ready = dec.prepare(caches, width, portions=[(p.seq.cache, p.count, p.wants_logits) for p in riding])
         sample = pack_choices(choices, width) if width else None
-        self.decoder.launch(ready, caches, None, sample, feed_from=self.decoder.last)
-        self.h2d_bytes += 12 * len(caches)
-        return True
+        dec.launch(ready, caches, tokens, sample, feed_from=dec.last, feed_rows=feed_rows,
+                   portions=[(p.seq.cache, p.tokens, p.wants_logits) for p in riding])
+        self._note_flight(decodes, riding)
+        self.h2d_bytes += 4 * int(ready.ints.numel())
+        return ready, True, split
 
     @staticmethod
     def _recent_width(choices) -> int:
@@ -282,31 +301,36 @@ class Engine:
 
     GRAPH_PORTION_MIN = 16
 
-    def _portion_beside_decodes(self, plan: StepPlan):
-        """The step's one prompt portion if the step is "decoded tokens (or none),
-        then one prompt portion": such steps recur - while a long prompt is fed in
-        portions beside the decoding requests, and for every prompt that comes
-        alone - so they are run from recorded graphs like steps of decoded tokens
-        alone, one recording per bucket of the portion's length (a shorter portion
-        is followed by rows that belong to no request).  A portion that does not
-        end its prompt is cut by a few rows where that makes the rows of the
-        recorded step (decoded tokens rounded up to their bucket, plus the portion)
-        a multiple of the prompt kernels' tile."""
+    def _recorded_shape(self, plan: StepPlan):
+        """(decoded rows, prompt portions) if the step is one that runs from a
+        recording: decoded tokens - or none - beside at most a few prompt portions
+        (``DecodeRunner.PORTION_ENTRIES``).  Such steps recur: while long prompts
+        are fed in portions beside the decoding requests (one portion, or the end
+        of one prompt and the start of the next), and for every prompt that comes
+        alone.  They are recorded per bucket of the portions' rows together (rows
+        left over belong to no request).  A last portion that does not end its
+        prompt is cut by a few rows where that makes the rows of the recorded
+        step (decoded tokens rounded up to their bucket, plus the portions) a
+        multiple of the prompt kernels' tile.  None for any other step."""
         if self.decoder is None or not plan.portions:
             return None
-        *decodes, last = plan.portions
-        if last.count < self.GRAPH_PORTION_MIN or (last.count == 1 and last.wants_logits) \
-                or not all(p.count == 1 and p.wants_logits for p in decodes):
+        decodes = [p for p in plan.portions if p.count == 1 and p.wants_logits]
+        riding = [p for p in plan.portions if not (p.count == 1 and p.wants_logits)]
+        if not riding:
+            return (decodes, riding) if self.decoder.can_take([p.seq.cache for p in decodes]) else None
+        if len(riding) > self.decoder.PORTION_ENTRIES or sum(p.count for p in riding) < self.GRAPH_PORTION_MIN:
             return None
+        last = riding[-1]
         m = self.config.token_multiple
         if m > 0 and not last.wants_logits:
-            rows = bucket_for(len(decodes)) + last.count
+            rows = bucket_for(len(decodes)) + sum(p.count for p in riding)
             extra = rows % m
             if extra and extra * 16 <= rows and last.count - extra >= self.GRAPH_PORTION_MIN:
                 last.count -= extra  # its pages stay held for the next step
-        if not self.decoder.can_take([p.seq.cache for p in decodes], (last.seq.cache, last.count, last.wants_logits)):
+        if not self.decoder.can_take([p.seq.cache for p in decodes],
+                                     [(p.seq.cache, p.count, p.wants_logits) for p in riding]):
             return None
-        return last
+        return decodes, riding
 
     def run_until_done(self, handles: Optional[Sequence[RequestHandle]] = None) -> None:
         while self.has_work() and (handles is None or any(not h.finished for h in handles)):

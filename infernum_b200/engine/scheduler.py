@@ -101,14 +101,22 @@ class Sequence_:
     admitted_at: int = -1  # admission counter value, for "most recently admitted"
     preemptions: int = 0
     error: Optional[str] = None
+    # 1 while the token a step in flight selects for this request is not known yet: the
+    # request is scheduled as if it had it (its value is fed on the device)
+    pending: int = 0
 
     @property
     def tokens(self) -> List[int]:
+        """The tokens known so far (one in flight is not among them)."""
         return self.prompt_ids + self.generated_ids
 
     @property
-    def num_tokens(self) -> int:
+    def num_known(self) -> int:
         return len(self.prompt_ids) + len(self.generated_ids)
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_ids) + len(self.generated_ids) + self.pending
 
     def token_at(self, i: int) -> int:
         n = len(self.prompt_ids)
@@ -213,48 +221,47 @@ class Scheduler:
         self._trim_to_multiple(plan)
         return plan
 
-    def plan_decode_ahead(self) -> Optional[StepPlan]:
-        """The next step, planned before the tokens of the step in flight are known,
-        for the common case in which it is certain but for those tokens: nobody
-        waits, every running request decodes and stays below its length limit
-        whatever token it gets, and one more token fits each without taking
-        pages from anyone.  Returns None otherwise.  The plan holds no token
-        values (a portion reads them when asked); it is void if a request ends
-        (end-of-sequence, cancel) or arrives before it is used - the caller
-        checks that with ``ahead_still_holds`` - and the pages it reserved then
-        simply stay with their requests."""
-        if self.waiting:
-            return None
-        live = [s for s in self.running if not s.finished]
-        if not live or len(live) > self.config.max_tokens_per_step:
-            return None
-        for seq in live:
-            # its token of the step in flight is not appended yet: it will have
-            # len(generated_ids) + 1 tokens and must still be short of the limit
-            if seq.phase != Phase.DECODE or seq.cache is None \
-                    or len(seq.generated_ids) + 1 >= seq.options.max_new_tokens \
+    def plan_ahead(self, in_flight: StepPlan) -> Optional[StepPlan]:
+        """The step after ``in_flight``, scheduled while that one still runs and
+        before the tokens it selects are known.  What the scheduler decides
+        depends on how many tokens a request has, not on which, with two
+        exceptions: a request may end on the token in flight (end-of-sequence),
+        and one that reaches its length limit with it ends for certain.  The
+        second is known beforehand: then nothing is planned (None) and the
+        caller schedules after it has read the tokens.  The first is not: a
+        request that turns out to have ended has a row in the planned step that
+        was computed in vain; its pages go back at the next round, as always.
+
+        Every request that gets a token from ``in_flight`` is marked as having
+        one token more (``pending``); the round then runs as ``schedule`` does,
+        admissions and preemptions included.  The plan holds no token values:
+        the caller feeds the tokens in flight on the device, or waits for them
+        and checks the plan with ``plan_still_holds``.  Whatever was reserved or
+        admitted for a plan that is not used stays with its requests."""
+        coming = []
+        for p in in_flight.portions:
+            seq = p.seq
+            if not p.wants_logits or seq.finished or seq.cache is None:
+                continue
+            if len(seq.generated_ids) + 1 >= seq.options.max_new_tokens \
                     or seq.num_computed + 1 >= self.max_model_len:
                 return None
-        live.sort(key=lambda s: s.admitted_at)
-        plan = StepPlan()
-        for seq in live:
-            need = self._to_reserve(seq, 1)
-            if need:
-                if not self.cache.can_extend(seq.cache, need):
-                    return None  # what was reserved so far stays with its requests
-                self.cache.extend(seq.cache, need)
-            plan.portions.append(Portion(seq, seq.num_computed, 1, True))
-        return plan
+            coming.append(seq)
+        if not coming and not self.waiting and not any(s.phase == Phase.PREFILL for s in self.running):
+            return None
+        for seq in coming:
+            seq.pending = 1
+            seq.phase = Phase.DECODE
+        plan = self.schedule()
+        return plan if plan.portions else None
 
-    def ahead_still_holds(self, plan: StepPlan) -> bool:
-        """Whether a plan of ``plan_decode_ahead`` can run now that the tokens of
-        the step before it are appended."""
-        if self.waiting:
-            return False
-        live = [s for s in self.running if not s.finished]
-        return len(live) == len(plan.portions) and all(
-            not p.seq.finished and p.seq.cache is not None and p.seq.phase == Phase.DECODE
-            and p.start == p.seq.num_computed and p.seq.num_tokens == p.start + 1
+    def plan_still_holds(self, plan: StepPlan) -> bool:
+        """Whether a plan of ``plan_ahead`` that was not launched can run now that
+        the tokens of the step before it are appended: nobody in it has ended or
+        lost its pages, and every token it feeds is known."""
+        return bool(plan.portions) and all(
+            not p.seq.finished and p.seq.cache is not None and p.seq.pending == 0
+            and p.start == p.seq.num_computed and p.start + p.count <= p.seq.num_known
             for p in plan.portions)
 
     def _trim_to_multiple(self, plan: StepPlan) -> None:
@@ -309,6 +316,8 @@ class Scheduler:
             if seq.finished:  # cancelled while waiting
                 self.waiting.popleft()
                 continue
+            if seq.pending:  # preempted while its latest token is in flight: that token comes first
+                break
             first = min(seq.remaining, cfg.max_prefill_tokens, budget)
             if self._sliver(first, seq, plan):
                 break
@@ -380,6 +389,7 @@ class Scheduler:
         End-of-sequence is neither stored nor emitted; the token selected
         after the prompt counts as the first generated one
         (infernum-runtime/src/engine.rs:445-481, 286-288)."""
+        seq.pending = 0
         if seq.finished:
             return None
         opts = seq.options
@@ -387,7 +397,8 @@ class Scheduler:
             self._finish(seq, FinishReason.STOP)
             return None
         seq.generated_ids.append(int(token))
-        seq.phase = Phase.DECODE
+        if seq.phase != Phase.WAITING:  # (preempted while this token was in flight: it waits on)
+            seq.phase = Phase.DECODE
         if len(seq.generated_ids) >= opts.max_new_tokens:
             self._finish(seq, FinishReason.LENGTH)
         return int(token)

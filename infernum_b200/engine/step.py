@@ -43,7 +43,20 @@ class StepEntry:
 
 @dataclass
 class StepContext:
-    """Device-side description of a step, read by every part."""
+    """Device-side description of a step, read by every part.
+
+    The tensors are the truth: which rows belong to which entry (``row_entry``,
+    ``cu_rows``), where an entry's rows sit in its request (``q_start``,
+    ``positions``, ``kv_len``) and which state slot it has (``slot_ids``).  A
+    step that is replayed from a recording gets new contents in them each
+    time - other requests, portions of other lengths, rows at the end that
+    belong to no request - while the host-side fields below stay as they were
+    when the step was recorded.  Those describe the step's *shape* and serve
+    for launch geometry only: ``n_rows``, ``n_entries``; ``max_rows_per_entry``
+    and ``max_kv_len``, upper bounds; ``host_cu_rows``, which in a recorded step
+    gives every entry the most rows it may have (not the rows it has);
+    ``all_decode``, one row per entry.  ``scratch`` lives as long as the
+    recording: a part may keep a plan or a buffer there."""
 
     n_rows: int
     n_entries: int

@@ -77,7 +77,8 @@ def core_lib() -> ctypes.CDLL:
                                   _c_void_p, _c_void_p]
         lib.ib_decode_advance.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                           _c_void_p]
-        for fn in ("ib_decode_advance", "ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
+        lib.ib_feed_tokens.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p]
+        for fn in ("ib_decode_advance", "ib_feed_tokens", "ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
                    "ib_silu_mul", "ib_attention_plain", "ib_gemm_plain", "ib_argmax", "ib_sample"):
             getattr(lib, fn).restype = _c_int
         _lib = lib
@@ -369,6 +370,18 @@ def sample(logits: torch.Tensor, params: torch.Tensor, recent: Optional[torch.Te
     check(core_lib().ib_sample(logits.data_ptr(), logits.stride(0), R, V, params.data_ptr(),
                                _ptr(recent), recent_ld, out.data_ptr(), stream_ptr(logits)),
           "sample")
+
+
+def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, selected: torch.Tensor) -> None:
+    """tokens[i] = selected[src[i]] where src[i] >= 0 (other rows keep theirs): the
+    inputs of a step launched behind the step whose selection ``selected`` is."""
+    require_cuda(tokens, src, selected)
+    for t, name in ((tokens, "tokens"), (src, "src"), (selected, "selected")):
+        _int32(t, name)
+    if src.numel() < tokens.numel():
+        raise KernelError("feed_tokens: fewer sources than tokens")
+    check(core_lib().ib_feed_tokens(tokens.data_ptr(), src.data_ptr(), selected.data_ptr(), selected.numel(),
+                                    tokens.numel(), stream_ptr(tokens)), "feed_tokens")
 
 
 def decode_advance(tokens: torch.Tensor, selected: Optional[torch.Tensor], positions: torch.Tensor,

@@ -276,7 +276,7 @@ def test_a_cut_portion_that_would_have_ended_its_prompt_asks_for_no_logits():
     assert off.schedule().num_tokens == 520
 
 
-def test_the_next_decode_step_can_be_planned_before_its_tokens_are_known():
+def test_the_next_step_can_be_planned_before_its_tokens_are_known():
     sched, cache = make(num_blocks=64, block_size=4, max_batch=4, chunk=8, budget=16)
     opts = GenerateOptions(max_new_tokens=6, ignore_eos=True)
     a = sched.add_request([5, 6, 7], opts)
@@ -285,90 +285,155 @@ def test_the_next_decode_step_can_be_planned_before_its_tokens_are_known():
     # a decode step in flight: scheduled and committed, its tokens not yet appended
     plan = sched.schedule()
     sched.commit(plan, commit_cache=True)
-    ahead = sched.plan_decode_ahead()
+    ahead = sched.plan_ahead(plan)
     assert ahead is not None and [p.seq for p in ahead.portions] == [a, b]
     assert [(p.start, p.count, p.wants_logits) for p in ahead.portions] == \
         [(a.num_computed, 1, True), (b.num_computed, 1, True)]
+    assert a.pending == 1 and a.num_tokens == a.num_known + 1
+    assert not sched.plan_still_holds(ahead)  # it feeds tokens nobody has seen yet
     for p in plan.portions:
         sched.append_token(p.seq, fake_token(p.seq))
-    assert sched.ahead_still_holds(ahead)
+    assert a.pending == 0 and sched.plan_still_holds(ahead)
     assert [p.tokens for p in ahead.portions] == [[a.generated_ids[-1]], [b.generated_ids[-1]]]
     cache.check_invariants()
-    # a request that arrives, or one that ends, voids the plan
+    # a request that arrives joins a later step; one that ends voids the plan
     sched.add_request([1, 2, 3], opts)
-    assert not sched.ahead_still_holds(ahead)
+    assert sched.plan_still_holds(ahead)
+    sched.cancel(b)
+    assert not sched.plan_still_holds(ahead)
     drain(sched, cache)
     assert a.generated_ids == solo_tokens([5, 6, 7], 6)
 
 
-def test_no_plan_ahead_when_a_request_is_about_to_reach_its_limit_or_pages_are_short():
+def test_planning_ahead_admits_portions_and_knows_the_limits():
+    """The step planned ahead is a whole scheduling round: a prompt that ends in
+    the step in flight decodes in the next, the next portion of a long prompt
+    and a waiting request ride along.  A request whose token in flight is its
+    last is known to end, so nothing is planned until that token is read."""
+    sched, cache = make(num_blocks=64, block_size=4, max_batch=3, chunk=8, budget=16)
+    opts = GenerateOptions(max_new_tokens=5, ignore_eos=True)
+    a = sched.add_request([5, 6, 7], opts)
+    b = sched.add_request(list(range(3, 23)), opts)       # 20 tokens: portions of 8, 8, 4
+    plan = sched.schedule()                                 # a whole, b's first portion
+    sched.commit(plan, commit_cache=True)
+    c = sched.add_request([9, 9], opts)
+    ahead = sched.plan_ahead(plan)
+    assert [(p.seq, p.start, p.count, p.wants_logits) for p in ahead.portions] == \
+        [(a, 3, 1, True), (b, 8, 8, False), (c, 0, 2, True)]
+    assert a.phase == Phase.DECODE and a.pending == 1 and b.pending == 0
+    cache.check_invariants()
+    for p in plan.portions:
+        if p.wants_logits:
+            sched.append_token(p.seq, fake_token(p.seq))
+    assert sched.plan_still_holds(ahead)
+    drain(sched, cache)
+    assert a.generated_ids == solo_tokens([5, 6, 7], 5) and len(b.generated_ids) == 5
+    # the limit
     sched, cache = make(num_blocks=64, block_size=4)
     a = sched.add_request([5, 6, 7], GenerateOptions(max_new_tokens=2, ignore_eos=True))
     run_step(sched, cache)
     plan = sched.schedule()
     sched.commit(plan, commit_cache=True)
-    assert sched.plan_decode_ahead() is None  # the token in flight is its last
+    assert sched.plan_ahead(plan) is None and a.pending == 0  # the token in flight is its last
     for p in plan.portions:
         sched.append_token(p.seq, fake_token(p.seq))
     assert a.finished
-    # pages: two requests that fill the pool exactly cannot both grow
+
+
+def test_planning_ahead_takes_pages_like_any_round():
+    """Two requests fill the pool; the round planned ahead needs a page more, so
+    the younger request is preempted while its token is still in flight.  The
+    token is kept when it arrives, the request waits (it is not let back in
+    before that), is computed again and ends with the tokens it gets alone."""
     sched, cache = make(num_blocks=4, block_size=4)
     opts = GenerateOptions(max_new_tokens=8, ignore_eos=True)
-    sched.add_request([1] * 7, opts)
-    sched.add_request([2] * 7, opts)
+    a = sched.add_request([1] * 7, opts)
+    b = sched.add_request([2] * 7, opts)
     run_step(sched, cache)           # 7 tokens each: two pages each, the pool is full
     plan = sched.schedule()          # token 8 fits the pages held
     sched.commit(plan, commit_cache=True)
-    assert sched.plan_decode_ahead() is None  # token 9 would need a fifth page
+    ahead = sched.plan_ahead(plan)   # token 9 needs a fifth page
+    assert [p.seq for p in ahead.portions] == [a] and ahead.preempted == [b]
+    assert b.phase == Phase.WAITING and b.pending == 1 and b.cache is None
     cache.check_invariants()
+    for p in plan.portions:
+        sched.append_token(p.seq, fake_token(p.seq))
+    assert b.phase == Phase.WAITING and b.pending == 0 and len(b.generated_ids) == 2
+    assert sched.plan_still_holds(ahead)
+    drain(sched, cache)
+    assert a.generated_ids == solo_tokens([1] * 7, 8) and b.generated_ids == solo_tokens([2] * 7, 8)
+    assert cache.free_pages() == [4]
 
 
 def test_planning_ahead_under_random_arrivals_ends_and_tight_pages():
-    """The engine's way of driving the scheduler - plan the next decode step while
-    one is in flight, use the plan if it still holds - under random prompt
-    lengths, arrivals between steps, end-of-sequence tokens and so few pages
-    that requests are preempted: every request gets the tokens it gets alone,
-    no page is lost, and plans made ahead are both used and voided."""
+    """The engine's way of driving the scheduler - schedule the next step while
+    one is in flight, as if its tokens were there; run it at once if it only
+    needs them on the device, else when they have come and the plan still
+    holds - under random prompt lengths, arrivals between steps,
+    end-of-sequence tokens and so few pages that requests are preempted: every
+    request gets the tokens it gets alone, no page is lost, and plans made
+    ahead are launched, used later and voided."""
     import random
     rng = random.Random(11)
     sched, cache = make(num_blocks=48, block_size=4, max_batch=5, chunk=9, budget=20, max_len=200)
-    pending = [([rng.randrange(3, 90) for _ in range(rng.randint(1, 40))], rng.randint(1, 25)) for _ in range(30)]
+    todo = [([rng.randrange(3, 90) for _ in range(rng.randint(1, 40))], rng.randint(1, 25)) for _ in range(40)]
     expect, seqs = [], []
-    used = voided = 0
-    ahead = None
+    launched = used = voided = 0
+    ahead = None  # (plan, launched)
     steps = 0
-    while pending or sched.has_work():
+
+    def land(plan):
+        for p in plan.portions:
+            if p.wants_logits:
+                if p.seq.finished:
+                    p.seq.pending = 0  # (computed in vain)
+                else:
+                    sched.append_token(p.seq, fake_token(p.seq))
+
+    while todo or sched.has_work() or ahead is not None:
         steps += 1
         assert steps < 5000
-        if pending and rng.random() < 0.3:
-            p, n = pending.pop()
+        if todo and rng.random() < 0.3:
+            p, n = todo.pop()
             want = solo_tokens(p, n)
             eos = want[len(want) // 2] if (len(want) > 3 and rng.random() < 0.4) else None
             seqs.append(sched.add_request(p, GenerateOptions(max_new_tokens=n, eos_token_id=eos)))
             expect.append(want if eos is None else want[: want.index(eos)])
-        plan = None
+        plan, in_flight = None, False
         if ahead is not None:
-            if sched.ahead_still_holds(ahead):
-                plan, used = ahead, used + 1
-            else:
-                voided += 1
+            plan, in_flight = ahead
             ahead = None
+            if in_flight:
+                launched += 1
+            elif sched.plan_still_holds(plan):
+                used += 1
+            else:
+                plan, voided = None, voided + 1
         if plan is None:
             plan = sched.schedule()
         cache.check_invariants()
-        for p in plan.portions:
-            assert p.tokens == p.seq.tokens[p.seq.num_computed: p.seq.num_computed + p.count]
+        if not in_flight:
+            for p in plan.portions:  # run from the host: every token is known
+                assert p.tokens == p.seq.tokens[p.seq.num_computed: p.seq.num_computed + p.count]
+        if not plan.portions:
+            continue
         sched.commit(plan, commit_cache=True)
-        if plan.portions and all(p.count == 1 and p.wants_logits for p in plan.portions):
-            ahead = sched.plan_decode_ahead()  # before the tokens of `plan` are appended
-            cache.check_invariants()
-        for p in plan.portions:
-            if p.wants_logits:
-                sched.append_token(p.seq, fake_token(p.seq))
+        nxt = sched.plan_ahead(plan)
+        cache.check_invariants()
+        if nxt is not None:
+            # launched at once when it is decoded tokens beside at most one portion whose
+            # tokens are known (what the engine runs from recordings); else kept for later
+            many = [p for p in nxt.portions if p.count > 1 or not p.wants_logits]
+            now = len(many) <= 1 and all(not p.seq.pending for p in many) and rng.random() < 0.8
+            if now:
+                for p in nxt.portions:  # a token in flight is fed on the device, the others are known
+                    assert p.seq.pending == (1 if p.start + p.count > p.seq.num_known else 0)
+            ahead = (nxt, now)
+        land(plan)  # the tokens of `plan` arrive
     sched.schedule()
     cache.check_invariants()
     assert [s.generated_ids for s in seqs] == expect
-    assert cache.free_pages() == [48] and used > 5 and voided > 3
+    assert cache.free_pages() == [48] and launched > 20 and used > 3 and voided > 0, (launched, used, voided)
 
 
 def test_leftover_budget_is_not_spent_on_a_sliver_of_a_prompt():

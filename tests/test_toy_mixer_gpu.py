@@ -33,11 +33,13 @@ def define_toy():
             self.w = weights[self.name].float()
 
         def forward(self, x, ctx, cache):
-            # What a mixer with state may rely on: the step's shape is known on the host
-            # (``host_cu_rows``, ``n_entries``, ``max_rows_per_entry``; fixed for a recorded
-            # step), the slots only on the device (``slot_ids``), because a recorded step is
-            # replayed for other requests.  Nothing here reads device memory on the host, so
-            # the engine can record it in a CUDA graph.
+            # What a mixer with state may rely on: how many rows and entries the step has is
+            # known on the host and fixed for a recorded step; which row belongs to which entry
+            # (``row_entry``) and which entry to which slot (``slot_ids``) is known on the device
+            # only, because a recorded step is replayed for other requests, for portions of
+            # other lengths, and with rows at its end that belong to no request (their entry's
+            # slot is the spare one).  Nothing here reads device memory on the host, so the
+            # engine can record it in a CUDA graph.
             state, xf = cache.state, x.float()
             if ctx.max_rows_per_entry == 1:  # one row per entry: all entries at once
                 slots = ctx.slot_ids.long()
@@ -45,14 +47,12 @@ def define_toy():
                 state[slots] = s  # (rows that pad a batch all write the spare slot)
                 return (s @ self.w.T).to(x.dtype)
             out = torch.empty_like(x)
-            cu = ctx.host_cu_rows
-            for e in range(ctx.n_entries):  # rows of a request in order, state carried across steps
-                slot = ctx.slot_ids[e: e + 1].long()
-                s = state[slot][0]
-                for r in range(cu[e], cu[e + 1]):
-                    s = s * self.decay + xf[r]
-                    out[r] = (self.w @ s).to(x.dtype)
-                state[slot] = s[None]
+            slot_of_row = ctx.slot_ids.long()[ctx.row_entry.long()]
+            for r in range(x.shape[0]):  # rows of a request come in order, its state is carried along
+                slot = slot_of_row[r: r + 1]
+                s = state[slot] * self.decay + xf[r: r + 1]
+                state[slot] = s
+                out[r: r + 1] = (s @ self.w.T).to(x.dtype)
             return out
 
     def build_spec(cfg):
