@@ -135,6 +135,13 @@ class Sequence_:
         return self.num_tokens - self.num_computed
 
     @property
+    def ends_in_flight(self) -> bool:
+        """The token in flight is the last one this request may have: whatever it
+        is, the request ends when it arrives, and takes no part in a step
+        planned before that."""
+        return bool(self.pending) and len(self.generated_ids) + self.pending >= self.options.max_new_tokens
+
+    @property
     def finished(self) -> bool:
         return self.phase == Phase.FINISHED
 
@@ -203,12 +210,14 @@ class Scheduler:
         return bool(self.waiting) or any(not s.finished for s in self.running)
 
     # ---- one scheduling round --------------------------------------------------
-    def schedule(self) -> StepPlan:
+    def schedule(self, ahead: bool = False) -> StepPlan:
         plan = StepPlan()
         self._reap()
         while True:
             self._fill(plan)
-            if plan.portions or not self.running:
+            if plan.portions or not self.running or ahead:
+                # (a round planned ahead in which nothing fits is left to the round that
+                # knows the tokens in flight: a request may be about to end and make room)
                 break
             # Nothing fits although requests are running: make room.
             victim = self._most_recent(exclude=None)
@@ -227,10 +236,10 @@ class Scheduler:
         depends on how many tokens a request has, not on which, with two
         exceptions: a request may end on the token in flight (end-of-sequence),
         and one that reaches its length limit with it ends for certain.  The
-        second is known beforehand: then nothing is planned (None) and the
-        caller schedules after it has read the tokens.  The first is not: a
-        request that turns out to have ended has a row in the planned step that
-        was computed in vain; its pages go back at the next round, as always.
+        second is known beforehand: such a request gets no row in the planned
+        step (its pages go back when its token has arrived).  The first is not:
+        a request that turns out to have ended has a row in the planned step
+        that was computed in vain; its pages go back at the next round, as always.
 
         Every request that gets a token from ``in_flight`` is marked as having
         one token more (``pending``); the round then runs as ``schedule`` does,
@@ -243,16 +252,16 @@ class Scheduler:
             seq = p.seq
             if not p.wants_logits or seq.finished or seq.cache is None:
                 continue
-            if len(seq.generated_ids) + 1 >= seq.options.max_new_tokens \
-                    or seq.num_computed + 1 >= self.max_model_len:
+            if seq.num_computed + 1 >= self.max_model_len:
                 return None
             coming.append(seq)
-        if not coming and not self.waiting and not any(s.phase == Phase.PREFILL for s in self.running):
-            return None
+        if not self.waiting and not any(s.phase == Phase.PREFILL for s in self.running) and all(
+                len(s.generated_ids) + 1 >= s.options.max_new_tokens for s in coming):
+            return None  # nothing would be left to run
         for seq in coming:
             seq.pending = 1
             seq.phase = Phase.DECODE
-        plan = self.schedule()
+        plan = self.schedule(ahead=True)
         return plan if plan.portions else None
 
     def plan_still_holds(self, plan: StepPlan) -> bool:
@@ -286,7 +295,7 @@ class Scheduler:
         scheduled = set()
         # 1. decoding requests, oldest first; preempt the youngest for pages
         for seq in sorted(self.running, key=lambda s: s.admitted_at):
-            if seq.finished or seq.phase != Phase.DECODE or seq.cache is None:
+            if seq.finished or seq.phase != Phase.DECODE or seq.cache is None or seq.ends_in_flight:
                 continue
             if budget <= 0:
                 break

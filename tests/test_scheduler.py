@@ -328,16 +328,36 @@ def test_planning_ahead_admits_portions_and_knows_the_limits():
     assert sched.plan_still_holds(ahead)
     drain(sched, cache)
     assert a.generated_ids == solo_tokens([5, 6, 7], 5) and len(b.generated_ids) == 5
-    # the limit
-    sched, cache = make(num_blocks=64, block_size=4)
+    # the limit: a request whose token in flight is its last has no row in the step planned ahead;
+    # alone, nothing is planned; its slot is free for the next request only when the token has come
+    sched, cache = make(num_blocks=64, block_size=4, max_batch=2)
     a = sched.add_request([5, 6, 7], GenerateOptions(max_new_tokens=2, ignore_eos=True))
     run_step(sched, cache)
     plan = sched.schedule()
     sched.commit(plan, commit_cache=True)
-    assert sched.plan_ahead(plan) is None and a.pending == 0  # the token in flight is its last
+    assert sched.plan_ahead(plan) is None and not a.finished
+    b = sched.add_request([8, 9, 10, 11], GenerateOptions(max_new_tokens=3, ignore_eos=True))
+    c = sched.add_request([1, 2], GenerateOptions(max_new_tokens=3, ignore_eos=True))
+    ahead = sched.plan_ahead(plan)
+    assert [p.seq for p in ahead.portions] == [b] and a.ends_in_flight and c.phase == Phase.WAITING
     for p in plan.portions:
         sched.append_token(p.seq, fake_token(p.seq))
-    assert a.finished
+    assert a.finished and a.finish_reason == FinishReason.LENGTH and sched.plan_still_holds(ahead)
+    drain(sched, cache)
+    assert b.generated_ids == solo_tokens([8, 9, 10, 11], 3) and c.generated_ids == solo_tokens([1, 2], 3)
+    # one slot only: the request that waits cannot come in before the token in flight has
+    # arrived, and the one that is about to end is neither preempted nor failed for it
+    sched, cache = make(num_blocks=64, block_size=4, max_batch=1)
+    a = sched.add_request([5, 6, 7], GenerateOptions(max_new_tokens=2, ignore_eos=True))
+    b = sched.add_request([8, 9], GenerateOptions(max_new_tokens=2, ignore_eos=True))
+    run_step(sched, cache)
+    plan = sched.schedule()
+    sched.commit(plan, commit_cache=True)
+    assert sched.plan_ahead(plan) is None and not a.finished and a.cache is not None
+    for p in plan.portions:
+        sched.append_token(p.seq, fake_token(p.seq))
+    drain(sched, cache)
+    assert a.finish_reason == b.finish_reason == FinishReason.LENGTH and b.generated_ids == solo_tokens([8, 9], 2)
 
 
 def test_planning_ahead_takes_pages_like_any_round():
