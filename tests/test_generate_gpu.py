@@ -550,3 +550,62 @@ def test_steps_with_portions_are_launched_behind_the_step_in_flight(folders, dty
         if dtype == "float32" and k != 3:
             assert g.tokens == w.tokens
     engine.runner.check_errors()
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_traffic_through_the_pipeline_equals_runs_alone(folders, seed):
+    """Requests of random lengths and limits arrive at random moments; some stop
+    on an end-of-sequence token, some are sampled (with and without a repetition
+    penalty), some are cancelled, and the pages are so few that requests are
+    preempted - while steps are scheduled and launched ahead of the tokens in
+    flight.  In 32-bit every request gets, token for token, what it gets alone
+    from an engine that records nothing and launches nothing ahead; no page or
+    slot is lost."""
+    import random
+    import infernum_b200 as ib
+    rng = random.Random(seed)
+    model = ib.load_model(folders["B"], dtype="float32")
+    base = dict(max_batch_size=5, block_size=8, max_prefill_tokens=24, max_tokens_per_step=40, max_model_len=200)
+    solo = ib.Engine(model, ib.BatchConfig(num_blocks=64, cuda_graphs=False, launch_ahead=False, **base))
+    engine = ib.Engine(model, ib.BatchConfig(num_blocks=44, **base))
+    todo = []
+    for i in range(26):
+        prompt = random_tokens(rng.randint(1, 110), 320, 1000 * seed + i)
+        kind = rng.random()
+        sampling = None
+        if kind < 0.25:
+            sampling = ib.SamplingParams(temperature=0.9, top_p=0.9, seed=i)
+        elif kind < 0.4:
+            sampling = ib.SamplingParams(temperature=0.8, top_p=0.95, seed=i, repetition_penalty=1.2,
+                                         repetition_penalty_window=16)
+        n_new = rng.randint(1, 22)
+        want = solo.generate(prompt, ib.GenerateOptions(max_new_tokens=n_new, sampling=sampling))
+        eos = want[len(want) // 2] if len(want) > 3 and rng.random() < 0.3 else None
+        if eos is not None:
+            want = want[: want.index(eos)]
+        todo.append((prompt, ib.GenerateOptions(max_new_tokens=n_new, sampling=sampling, eos_token_id=eos), want))
+    live, done, cancelled = [], [], 0
+    steps = 0
+    while todo or engine.has_work():
+        steps += 1
+        assert steps < 3000
+        if todo and rng.random() < 0.35:
+            prompt, opts, want = todo.pop()
+            live.append((engine.submit(prompt, opts), want))
+        if live and rng.random() < 0.02:
+            h, want = live[rng.randrange(len(live))]
+            if not h.finished:
+                engine.cancel(h)
+                cancelled += 1
+        engine.step()
+    engine.run_until_done()
+    for h, want in live:
+        if h.finish_reason == ib.FinishReason.CANCELLED:
+            assert h.tokens == want[: len(h.tokens)]
+        else:
+            assert h.tokens == want, (h.id, h.finish_reason)
+    st = engine.stats
+    assert st.preemptions > 0 and st.ahead_launched > 30 and engine.decoder.counts["replayed"] > 30
+    assert not engine.decoder._reads
+    assert engine.cache.free_pages() == [44] and engine.cache.num_free_slots == 5
+    engine.runner.check_errors()
