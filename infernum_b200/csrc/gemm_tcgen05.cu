@@ -177,25 +177,10 @@ struct GemmParams {
     int kblocks_per_split;
     int out_f32;
     int swiglu;           // 1: W rows are 64 gates then their 64 ups per tile; out is [T, N/2]
-    // Row factor of an RMSNorm whose input rows came without it.  X holds, per token, the
-    // norm's input times the norm's weights; the factor rsqrt(mean(h^2) + eps) is a scalar
-    // per token and commutes with the product, so it is applied to the accumulator.  The
-    // sum of squares of token t is the sum over i < scale_tiles of scale_sumsq[i * scale_ld + t].
-    const float* scale_sumsq;
-    int scale_tiles, scale_ld;
-    float scale_inv_h, scale_eps;
-    // Residual add and the preparation of the norm that follows, in place of a store of the
-    // product: h = residual[t, n] + product (float32, written back), out[t, n] = bf16(h * gamma[n]),
-    // sumsq_out[n_tile * sumsq_ld + t] = sum of h^2 over this tile's 128 columns.
-    float* residual;
-    int ld_res;
-    const bf16* gamma;
-    float* sumsq_out;
-    int sumsq_ld;
 };
 
 template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
     constexpr int STAGES = num_stages(BN);
@@ -211,8 +196,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     __shared__ __align__(8) unsigned long long accum_bar;
     __shared__ unsigned tmem_base_slot;
     __shared__ unsigned gave_up;
-    __shared__ float row_factor[BN];   // per token of this tile (scale_sumsq)
-    __shared__ float sq_part[4][BN];   // per epilogue warp and token: its 32 columns' sum of h^2
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -311,26 +294,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         const int row = quad * 32 + lane;          // weight row within the tile
         const int n = n_tile * BM + row;
         pdl_wait();  // nothing is stored before the kernels ahead of this one are done
-        if (p.scale_sumsq) {
-            // the tokens' row factors, worked out while the products run
-            if (row < BN) {
-                const int t = t_tile * BN + row;
-                float sum = 0.f;
-                if (t < p.T) {
-                    // (eight loads in flight at a time; the parts are added in their order)
-                    for (int i0 = 0; i0 < p.scale_tiles; i0 += 8) {
-                        float part[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            part[j] = i0 + j < p.scale_tiles ? p.scale_sumsq[(size_t)(i0 + j) * p.scale_ld + t] : 0.f;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) sum += part[j];
-                    }
-                }
-                row_factor[row] = rsqrtf(sum * p.scale_inv_h + p.scale_eps);
-            }
-            epilogue_bar_sync();
-        }
         bool ok = mbar_wait(&accum_bar, 0);
         if (!ok && lane == 0) {
             atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_GEMM_EPILOGUE));
@@ -339,7 +302,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         tc_fence_after();
         const unsigned taddr = tmem_base + ((unsigned)(quad * 32) << 16);
         const int t0 = t_tile * BN;
-        const float gam = (p.residual && n < p.N) ? __bfloat162float(p.gamma[n]) : 0.f;
         if (p.swiglu) {
             // Rows 0..63 of the tile are gates, rows 64..127 their ups (splits == 1).
             // The up lanes park their values in shared memory (the stages are free:
@@ -368,9 +330,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     for (int j = 0; j < 16; ++j) {
                         const int t = t0 + c + j;
                         if (t < p.T) {
-                            const float f = p.scale_sumsq ? row_factor[c + j] : 1.f;
-                            const float g = __uint_as_float(v[j]) * f;
-                            const float u = xch[(c + j) * 64 + row] * f;
+                            const float g = __uint_as_float(v[j]);
+                            const float u = xch[(c + j) * 64 + row];
                             ((bf16*)p.out)[(size_t)t * p.ldo + col] =
                                 __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
                         }
@@ -382,42 +343,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
                 for (int c = 0; c < BN; c += 16) {
                     unsigned v[16];
-                    float res_v[16];
-                    if (p.residual) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            res_v[j] = (t0 + c + j < p.T && n < p.N) ? p.residual[(size_t)(t0 + c + j) * p.ld_res + n] : 0.f;
-                    }
                     tmem_ld16(taddr + c, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = t0 + c + j;
-                        float f = __uint_as_float(v[j]);
-                        if (p.scale_sumsq) f *= row_factor[c + j];
-                        float sq = 0.f;
                         if (t < p.T && n < p.N) {
-                            if (p.residual) {
-                                const float h = res_v[j] + f;
-                                p.residual[(size_t)t * p.ld_res + n] = h;
-                                sq = h * h;
-                                f = h * gam;
-                            }
+                            const float f = __uint_as_float(v[j]);
                             if (p.out_f32) ((float*)p.out)[(size_t)t * p.ldo + n] = f;
                             else ((bf16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(f);
                         }
-                        if (p.residual) {
-                            sq = warp_sum(sq);
-                            if (lane == 0) sq_part[quad][c + j] = sq;
-                        }
                     }
                 }
-            }
-            if (p.residual) {
-                epilogue_bar_sync();
-                if (row < BN && t0 + row < p.T)
-                    p.sumsq_out[(size_t)n_tile * p.sumsq_ld + t0 + row] =
-                        (sq_part[0][row] + sq_part[1][row]) + (sq_part[2][row] + sq_part[3][row]);
             }
         } else {
             // my slice's partial tile into my own shared memory: [col][row].
@@ -451,54 +388,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
             const int cols_per = (BN + p.splits - 1) / p.splits;
             const int c_begin = (int)rank * cols_per;
             const int c_end = min(BN, c_begin + cols_per);
-            const float gam = (p.residual && n < p.N) ? __bfloat162float(p.gamma[n]) : 0.f;
-            for (int c0 = c_begin; c0 < c_end; c0 += 8) {
-                // the residual's values of up to eight tokens are fetched together, ahead of their use
-                float res_v[8];
-                if (p.residual) {
+            for (int c = c_begin; c < c_end; ++c) {
+                const int t = t0 + c;
+                if (t >= p.T) break;
+                // all loads first (they are independent), then the sum in slice order
+                float part[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        res_v[j] = (c0 + j < c_end && t0 + c0 + j < p.T && n < p.N)
-                                       ? p.residual[(size_t)(t0 + c0 + j) * p.ld_res + n] : 0.f;
+                for (int sidx = 0; sidx < 8; ++sidx)
+                    part[sidx] = sidx < p.splits ? ld_peer_smem(red + c * BM + row, (unsigned)sidx) : 0.f;
+                float acc = 0.f;
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) acc += part[sidx];
+                if (n < p.N) {
+                    if (p.out_f32) ((float*)p.out)[(size_t)t * p.ldo + n] = acc;
+                    else ((bf16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(acc);
                 }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int c = c0 + j;
-                    const int t = t0 + c;
-                    if (c >= c_end || t >= p.T) continue;  // (the same for the whole warp)
-                    // all loads first (they are independent), then the sum in slice order
-                    float part[8];
-#pragma unroll
-                    for (int sidx = 0; sidx < 8; ++sidx)
-                        part[sidx] = sidx < p.splits ? ld_peer_smem(red + c * BM + row, (unsigned)sidx) : 0.f;
-                    float acc = 0.f;
-#pragma unroll
-                    for (int sidx = 0; sidx < 8; ++sidx) acc += part[sidx];
-                    if (p.scale_sumsq) acc *= row_factor[c];
-                    float sq = 0.f;
-                    if (n < p.N) {
-                        if (p.residual) {
-                            const float h = res_v[j] + acc;
-                            p.residual[(size_t)t * p.ld_res + n] = h;
-                            sq = h * h;
-                            acc = h * gam;
-                        }
-                        if (p.out_f32) ((float*)p.out)[(size_t)t * p.ldo + n] = acc;
-                        else ((bf16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(acc);
-                    }
-                    if (p.residual) {
-                        sq = warp_sum(sq);
-                        if (lane == 0) sq_part[quad][c] = sq;
-                    }
-                }
-            }
-            if (p.residual) {
-                // this CTA's share of the tokens: the four warps' sums, in a fixed order
-                epilogue_bar_sync();
-                const int c = c_begin + row;
-                if (c < c_end && t0 + c < p.T)
-                    p.sumsq_out[(size_t)n_tile * p.sumsq_ld + t0 + c] =
-                        (sq_part[0][c] + sq_part[1][c]) + (sq_part[2][c] + sq_part[3][c]);
             }
         }
         cluster_sync_all();  // nobody leaves while a peer may still read its tile
@@ -595,47 +499,10 @@ IB_EXPORT int ib_gemm_tc_token_tile(int T) {
 // CTAs of a cluster.  swiglu = 1: W holds, per
 // 128 rows, 64 gate rows followed by their 64 up rows; out is [T, N / 2] bf16 with
 // out[t, 64 b + r] = silu(x . W[128 b + r]) * (x . W[128 b + 64 + r]); K is not split.
-//
-// ib_gemm_tc_fused adds two things around the same product, for the steps of a
-// decoder layer that an RMSNorm separates:
-//   scale_sumsq != null: the rows of X lack the row factor of their norm (they are the norm's
-//     input times its weights); the factor rsqrt(sum_i scale_sumsq[i * scale_ld + t] / hidden +
-//     eps) multiplies the product of token t (before SiLU x up, when swiglu = 1);
-//   residual != null: the product is added to residual[T, N] (float32, in place); out gets
-//     bf16(residual * gamma) - the next norm's input times its weights - and
-//     sumsq_out[n_tile * sumsq_ld + t] the sum of squares of this tile's 128 columns, so that the
-//     product after this one can be given the row factor the same way.  Not with swiglu.
-static int gemm_tc_impl(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
-                        int out_f32, int T, int N, int K, int splits, int swiglu,
-                        const float* scale_sumsq, int scale_tiles, int scale_ld, int scale_hidden,
-                        float scale_eps, float* residual, int ld_res, const void* gamma,
-                        float* sumsq_out, int sumsq_ld, unsigned* err, void* stream);
-
 IB_EXPORT int ib_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
                          int out_f32, int T, int N, int K, int splits, int swiglu, unsigned* err,
                          void* stream) {
-    return gemm_tc_impl(x, ldx, w, ldw, out, ldo, out_f32, T, N, K, splits, swiglu, nullptr, 0, 0, 0, 0.f,
-                        nullptr, 0, nullptr, nullptr, 0, err, stream);
-}
-
-IB_EXPORT int ib_gemm_tc_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
-                               int out_f32, int T, int N, int K, int splits, int swiglu,
-                               const float* scale_sumsq, int scale_tiles, int scale_ld, int scale_hidden,
-                               float scale_eps, float* residual, int ld_res, const void* gamma,
-                               float* sumsq_out, int sumsq_ld, unsigned* err, void* stream) {
-    return gemm_tc_impl(x, ldx, w, ldw, out, ldo, out_f32, T, N, K, splits, swiglu, scale_sumsq, scale_tiles,
-                        scale_ld, scale_hidden, scale_eps, residual, ld_res, gamma, sumsq_out, sumsq_ld, err,
-                        stream);
-}
-
-static int gemm_tc_impl(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
-                        int out_f32, int T, int N, int K, int splits, int swiglu,
-                        const float* scale_sumsq, int scale_tiles, int scale_ld, int scale_hidden,
-                        float scale_eps, float* residual, int ld_res, const void* gamma,
-                        float* sumsq_out, int sumsq_ld, unsigned* err, void* stream) {
     if (T <= 0 || N <= 0) return IB_OK;
-    if (scale_sumsq && (scale_tiles <= 0 || scale_ld < T || scale_hidden <= 0)) return IB_ERR_BAD_ARG;
-    if (residual && (swiglu || out_f32 || !gamma || !sumsq_out || ld_res < N || sumsq_ld < T)) return IB_ERR_BAD_ARG;
     if (!x || !w || !out || !err || K <= 0) return IB_ERR_BAD_ARG;
     // TMA: 16-byte aligned bases and row strides
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx % 8) || (ldw % 8) || ldx < K || ldw < K ||
@@ -660,16 +527,6 @@ static int gemm_tc_impl(const void* x, int ldx, const void* w, int ldw, void* ou
     p.splits = (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;  // no empty slice
     p.out_f32 = out_f32;
     p.swiglu = swiglu ? 1 : 0;
-    p.scale_sumsq = scale_sumsq;
-    p.scale_tiles = scale_tiles;
-    p.scale_ld = scale_ld;
-    p.scale_inv_h = scale_sumsq ? 1.f / (float)scale_hidden : 0.f;
-    p.scale_eps = scale_eps;
-    p.residual = residual;
-    p.ld_res = ld_res;
-    p.gamma = (const bf16*)gamma;
-    p.sumsq_out = sumsq_out;
-    p.sumsq_ld = sumsq_ld;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, ldw, BM);
     if (rc != IB_OK) return rc;

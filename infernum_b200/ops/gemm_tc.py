@@ -20,7 +20,6 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..csrc.build import load_module
-from ..errors import KernelError
 from . import core
 
 _c_int, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_void_p, ctypes.c_longlong
@@ -36,10 +35,7 @@ PAIR_TILE_OVERHEAD = 66
 # Which products the kernel takes: "all", "none", or a largest token count.
 POLICY = {"mode": os.environ.get("INFERNUM_GEMM", "auto"), "max_tokens": 64, "pair_max_padding": 1.13,
           "pair_min_tokens_plain": 600, "pair_group_bytes": 64 << 20, "pair_group_max_tiles": 16,
-          "sm_count": 148,
-          # steps of few rows: the residual add and the norm between two products run in the
-          # products' own kernels (INFERNUM_FUSE_NORMS=0: in a kernel of their own)
-          "fuse_norms": os.environ.get("INFERNUM_FUSE_NORMS", "1") != "0"}
+          "sm_count": 148}
 
 
 def pair_suits(T: int, fused_activation: bool = False) -> bool:
@@ -63,11 +59,6 @@ def lib() -> ctypes.CDLL:
         l.ib_gemm_tc.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
         l.ib_gemm_tc.restype = _c_int
-        l.ib_gemm_tc_fused.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
-                                       _c_int, _c_int, _c_int, _c_int, _c_int,
-                                       _c_void_p, _c_int, _c_int, _c_int, ctypes.c_float,
-                                       _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p]
-        l.ib_gemm_tc_fused.restype = _c_int
         l.ib_gemm_tc_token_tile.argtypes = [_c_int]
         l.ib_gemm_tc_token_tile.restype = _c_int
         if torch.cuda.is_available():
@@ -127,90 +118,20 @@ def eligible(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
-            err: Optional[torch.Tensor] = None, swiglu: bool = False, scale=None,
-            add_norm: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> None:
+            err: Optional[torch.Tensor] = None, swiglu: bool = False) -> None:
     """Runs the tcgen05 kernel; raises KernelError if the operands do not fit it.
     ``swiglu``: ``w`` holds, per 128 rows, 64 gate rows then their 64 up rows, and
-    ``out`` [T, N/2] receives silu(gate) * up (at most 64 tokens).
-    ``scale``: a ``ScaledRows`` whose ``values`` are ``x``: its row factor is
-    applied to the product.  ``add_norm`` = (residual [T, N] float32, gamma [N],
-    sumsq [tiles, >= T] float32): the product is added to ``residual`` in place,
-    ``out`` gets ``residual * gamma`` and ``sumsq`` the rows' sums of squares in
-    parts of 128 columns (what a ``ScaledRows`` holds)."""
+    ``out`` [T, N/2] receives silu(gate) * up (at most 64 tokens)."""
     core.require_cuda(x, w, out)
     T, K = x.shape
     N = w.shape[0]
     if splits is None:
         splits = choose_splits(T, N, K, POLICY["sm_count"])
-    err_ptr = (err if err is not None else _error_word(x.device)).data_ptr()
-    if scale is None and add_norm is None:
-        code = lib().ib_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
-                                out.stride(0), 1 if out.dtype == torch.float32 else 0, T, N, K, splits,
-                                1 if swiglu else 0, err_ptr, core.stream_ptr(x))
-        core.check(code, "gemm_tc")
-        return
-    s_ptr, s_tiles, s_ld, s_hidden, s_eps = None, 0, 0, 0, 0.0
-    if scale is not None:
-        core.require_cuda(scale.sumsq)
-        if scale.sumsq.dtype != torch.float32 or scale.sumsq.stride(1) != 1 or scale.values.shape[0] != T:
-            raise KernelError("gemm_tc: the rows' sums of squares must be float32 [tiles, >= rows]")
-        s_ptr, s_tiles, s_ld = scale.sumsq.data_ptr(), scale.tiles, scale.sumsq.stride(0)
-        s_hidden, s_eps = scale.hidden, scale.eps
-    r_ptr, r_ld, g_ptr, q_ptr, q_ld = None, 0, None, None, 0
-    if add_norm is not None:
-        residual, gamma, sumsq = add_norm
-        core.require_cuda(residual, gamma, sumsq)
-        if (residual.dtype != torch.float32 or tuple(residual.shape) != (T, N) or residual.stride(1) != 1
-                or gamma.dtype != torch.bfloat16 or gamma.numel() != N or not gamma.is_contiguous()
-                or sumsq.dtype != torch.float32 or sumsq.shape[0] < -(-N // BM) or sumsq.shape[1] < T
-                or sumsq.stride(1) != 1 or out.dtype != torch.bfloat16):
-            raise KernelError("gemm_tc: residual, norm weights or sums of squares do not fit the product")
-        r_ptr, r_ld, g_ptr = residual.data_ptr(), residual.stride(0), gamma.data_ptr()
-        q_ptr, q_ld = sumsq.data_ptr(), sumsq.stride(0)
-    code = lib().ib_gemm_tc_fused(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
-                                  out.stride(0), 1 if out.dtype == torch.float32 else 0, T, N, K, splits,
-                                  1 if swiglu else 0, s_ptr, s_tiles, s_ld, s_hidden, float(s_eps),
-                                  r_ptr, r_ld, g_ptr, q_ptr, q_ld, err_ptr, core.stream_ptr(x))
+    code = lib().ib_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                            out.stride(0), 1 if out.dtype == torch.float32 else 0, T, N, K, splits,
+                            1 if swiglu else 0, (err if err is not None else _error_word(x.device)).data_ptr(),
+                            core.stream_ptr(x))
     core.check(code, "gemm_tc")
-
-
-def _few_rows(T: int) -> bool:
-    return POLICY["mode"] not in ("none", "cublas", "library") and POLICY["fuse_norms"] and T <= POLICY["max_tokens"]
-
-
-def add_norm_route(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float,
-                   err: Optional[torch.Tensor] = None):
-    """``residual += x . w^T`` and the preparation of the RMSNorm (weights
-    ``gamma``) that follows, in the product's kernel, for steps of few rows:
-    returns the norm's rows without their row factor (``ScaledRows``), or None
-    when the operands or the policy do not allow it (nothing is done then)."""
-    from ..parts.base import ScaledRows
-
-    T, N = x.shape[0], w.shape[0]
-    if not _few_rows(T) or T == 0 or gamma.dtype != torch.bfloat16 or residual.dtype != torch.float32 \
-            or tuple(residual.shape) != (T, N) or residual.stride(1) != 1 or N % 8:
-        return None
-    values = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
-    if not eligible(x, w, values) or not gamma.is_contiguous():
-        return None
-    tiles = -(-N // BM)
-    sumsq = torch.empty((tiles, -(-T // 4) * 4), dtype=torch.float32, device=x.device)
-    gemm_tc(x, w, values, err=err, add_norm=(residual, gamma, sumsq))
-    return ScaledRows(values, sumsq, tiles, N, eps)
-
-
-def scaled_route(rows, w: torch.Tensor, out_dtype: torch.dtype, err: Optional[torch.Tensor] = None):
-    """``rows . w^T`` with the rows' factor applied to the product (few rows
-    only); the result, or None when the kernel cannot take it."""
-    x = rows.values
-    T, N = x.shape[0], w.shape[0]
-    if not _few_rows(T) or T == 0:
-        return None
-    out = torch.empty((T, N), dtype=out_dtype, device=x.device)
-    if not eligible(x, w, out):
-        return None
-    gemm_tc(x, w, out, err=err, scale=rows)
-    return out
 
 
 @functools.lru_cache(maxsize=256)
@@ -306,24 +227,17 @@ def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor
     the policy and the operands allow; ``out`` is [T, I].  Up to 64 tokens go to
     the kernel that streams the weights once (decode), prompts to the kernel on
     pairs of SMs when their length suits its tiles (``pair_suits``)."""
-    from ..parts.base import ScaledRows
-
     mode = POLICY["mode"]
     if mode in ("none", "cublas", "library"):
         return False
     if w_interleaved.shape[0] % 128 or out.dtype != torch.bfloat16:
         return False
-    scale = x if isinstance(x, ScaledRows) else None
-    if scale is not None:
-        x = scale.values
     if not eligible(x, w_interleaved, out) or out.stride(0) % 8 or out.data_ptr() % 16:
         return False
     T = x.shape[0]
     if T <= min(POLICY["max_tokens"], 64):
-        gemm_tc(x, w_interleaved, out, splits=1, swiglu=True, err=err, scale=scale)
+        gemm_tc(x, w_interleaved, out, splits=1, swiglu=True, err=err)
         return True
-    if scale is not None:
-        return False  # (rows without their factor exist for few rows only)
     if pair_suits(T, fused_activation=True):
         gemm_pair(x, w_interleaved, out, swiglu=True, err=err)
         return True

@@ -29,7 +29,7 @@ import torch
 from ..errors import ConfigError
 from ..ops import attention as attn_ops
 from ..ops import core
-from .base import MIXERS, POSITION_ENCODINGS, DeferredProduct, Mixer, PagedCacheSpec, Runtime, WeightSpec
+from .base import MIXERS, POSITION_ENCODINGS, Mixer, PagedCacheSpec, Runtime, WeightSpec
 from .linear import Linear
 from .rope import RotaryEmbedding
 
@@ -85,10 +85,6 @@ class Attention(Mixer):
 
     # ---- the step -----------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
-        return self.forward_deferred(x, ctx, cache).materialize()
-
-    def forward_deferred(self, x, ctx, cache) -> DeferredProduct:
-        """``x`` may be ``ScaledRows``; the output product is left to the caller."""
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = self.qkv(x)  # [N, (nh + 2 nkv) hd], or [N, nh hd] when the cache is shared
         tables = ctx.block_tables[cache.group]
@@ -110,4 +106,4 @@ class Attention(Mixer):
         out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
         attn_ops.paged_attention(qkv, cache.k_pool, cache.v_pool, out, ctx, tables, nh,
                                  self.scale, self.window, self.rt)
-        return self.o.defer(out)
+        return self.o(out)

@@ -164,12 +164,7 @@ class Part:
 
 class Norm(Part):
     """``forward(stream)`` folds the stream's pending delta into its residual
-    and returns the normed rows in the activation dtype.  A norm that sets
-    ``can_leave_row_factor`` also takes ``scaled_ok=True`` and may then return
-    ``ScaledRows`` (its rows without the row factor) for a consumer that has
-    ``forward_deferred``."""
-
-    can_leave_row_factor = False
+    and returns the normed rows in the activation dtype."""
 
     def forward(self, stream: "ResidualStream", row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
@@ -203,14 +198,9 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
         raise NotImplementedError
 
-    # Optional: ``forward_deferred(x, ctx, cache)`` - the same, but ``x`` may be ``ScaledRows``
-    # and the result may be a ``DeferredProduct``: a mixer whose first and last operations are
-    # products can leave the norms around it to those products' kernels.
-
 
 class FeedForward(Part):
-    """Per-token transformation.  ``forward(x, ctx)`` -> [N, hidden].
-    Optional ``forward_deferred(x, ctx)`` as for a mixer."""
+    """Per-token transformation.  ``forward(x, ctx)`` -> [N, hidden]."""
 
     def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
         raise NotImplementedError
@@ -248,72 +238,26 @@ class Block(Part):
         raise NotImplementedError
 
 
-class DeferredProduct:
-    """``x . W^T`` not computed yet: the last product of a mixer or a
-    feed-forward, handed to the residual stream as it is.  The norm that
-    follows may then run it as one kernel with the residual add and its own
-    preparation (``RMSNorm.forward``); anybody else calls ``materialize``."""
-
-    def __init__(self, linear, x: torch.Tensor):
-        self.linear = linear
-        self.x = x
-
-    def materialize(self) -> torch.Tensor:
-        return self.linear(self.x)
-
-
-class ScaledRows:
-    """Rows of an RMSNorm's output that still lack the norm's row factor:
-    ``values[t] = h[t] * weight`` in the activation dtype, and the sum of
-    ``h[t]^2`` in ``tiles`` parts, ``sumsq[i, t]``.  The factor
-    ``rsqrt(sum_i sumsq[i, t] / hidden + eps)`` is one number per row and
-    commutes with a matrix product, so a product that takes these rows applies
-    it to its result (``Linear.__call__``); anybody else calls ``materialize``."""
-
-    def __init__(self, values: torch.Tensor, sumsq: torch.Tensor, tiles: int, hidden: int, eps: float):
-        self.values, self.sumsq, self.tiles, self.hidden, self.eps = values, sumsq, tiles, hidden, eps
-
-    @property
-    def shape(self):
-        return self.values.shape
-
-    @property
-    def dtype(self):
-        return self.values.dtype
-
-    def materialize(self) -> torch.Tensor:
-        n = self.values.shape[0]
-        factor = torch.rsqrt(self.sumsq[: self.tiles, :n].sum(dim=0) / self.hidden + self.eps)
-        return (self.values.float() * factor[:, None]).to(self.values.dtype)
-
-
 class ResidualStream:
     """The hidden state between parts: a float32 residual [N, hidden] and, at
     most, one pending delta in the activation dtype that the next norm (or
     ``flush``) adds to it.  Keeping the sum in 32-bit and fusing the add into
-    the norm kernel saves one pass over the rows per sub-layer.  The pending
-    delta may be a product that is still to be computed (``DeferredProduct``)."""
+    the norm kernel saves one pass over the rows per sub-layer."""
 
     def __init__(self, residual: torch.Tensor):
         self.residual = residual
-        self.pending = None  # a tensor or a DeferredProduct
+        self.pending: Optional[torch.Tensor] = None
 
-    def push(self, delta) -> None:
+    def push(self, delta: torch.Tensor) -> None:
         if self.pending is not None:
             self.flush()
         self.pending = delta
-
-    def take_pending(self) -> Optional[torch.Tensor]:
-        """The pending delta as a tensor (a deferred product is computed now)."""
-        if isinstance(self.pending, DeferredProduct):
-            self.pending = self.pending.materialize()
-        return self.pending
 
     def flush(self) -> None:
         if self.pending is not None:
             from ..ops import core
 
-            core.residual_add(self.residual, self.take_pending())
+            core.residual_add(self.residual, self.pending)
             self.pending = None
 
 

@@ -25,17 +25,5 @@ class PreNormBlock(Block):
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         p = self.parts
-        self._sublayer(stream, p["norm1"], p["mixer"], ctx, cache)
-        self._sublayer(stream, p["norm2"], p["ffn"], ctx)
-
-    @staticmethod
-    def _sublayer(stream: ResidualStream, norm, part, *args) -> None:
-        """``stream += part(norm(stream))``.  Where the part can take rows without
-        their row factor and hand back its last product undone
-        (``forward_deferred``) and the norm can work that way, the norms'
-        kernels disappear into the products around them for steps of few rows."""
-        deferred = getattr(part, "forward_deferred", None)
-        if deferred is not None and norm.can_leave_row_factor:
-            stream.push(deferred(norm.forward(stream, scaled_ok=True), *args))
-        else:
-            stream.push(part.forward(norm.forward(stream), *args))
+        stream.push(p["mixer"].forward(p["norm1"].forward(stream), ctx, cache))
+        stream.push(p["ffn"].forward(p["norm2"].forward(stream), ctx))

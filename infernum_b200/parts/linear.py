@@ -22,7 +22,6 @@ import torch
 
 from ..errors import KernelError
 from ..ops import core
-from .base import DeferredProduct, ScaledRows
 
 # Optional hand-written bf16 GEMM routes: callables (x, w, out, err) -> bool that
 # return True when they took the product.  Filled by ops modules at import.
@@ -81,19 +80,5 @@ class Linear:
     def nbytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def __call__(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """``x . W^T``.  ``x`` may be ``ScaledRows`` (a norm's rows without their
-        row factor): the package's kernel for few rows applies the factor to the
-        product; otherwise the rows are completed first."""
-        if isinstance(x, ScaledRows):
-            from ..ops import gemm_tc
-
-            out = gemm_tc.scaled_route(x, self.weight, out_dtype or x.dtype, self.err)
-            if out is not None:
-                return out
-            x = x.materialize()
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return matmul_nt(x, self.weight, out_dtype, err=self.err)
-
-    def defer(self, x: torch.Tensor) -> DeferredProduct:
-        """The product as something still to be done (see ``DeferredProduct``)."""
-        return DeferredProduct(self, x)

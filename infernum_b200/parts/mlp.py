@@ -20,7 +20,7 @@ import torch
 
 from ..errors import ConfigError
 from ..ops import core
-from .base import FEED_FORWARDS, DeferredProduct, FeedForward, Runtime, WeightSpec
+from .base import FEED_FORWARDS, FeedForward, Runtime, WeightSpec
 from .linear import Linear
 
 
@@ -61,11 +61,7 @@ class SwiGLU(FeedForward):
         return self.gate_up.nbytes + self.down.nbytes
 
     def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:
-        return self.forward_deferred(x, ctx).materialize()
-
-    def forward_deferred(self, x, ctx=None) -> DeferredProduct:
-        """``x`` may be ``ScaledRows``; the down product is left to the caller."""
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=self.gate_up.weight.device)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         fused = False
         if self.block == 64 and x.dtype == torch.bfloat16 and self.gate_up.weight.dtype == torch.bfloat16:
             from ..ops import gemm_tc
@@ -73,4 +69,4 @@ class SwiGLU(FeedForward):
             fused = gemm_tc.swiglu_route(x, self.gate_up.weight, act, self.gate_up.err)
         if not fused:
             core.silu_mul(self.gate_up(x), act, block=self.block)
-        return self.down.defer(act)
+        return self.down(act)

@@ -13,7 +13,7 @@ from typing import Dict, Optional
 import torch
 
 from ..ops import core
-from .base import NORMS, DeferredProduct, Norm, ResidualStream, Runtime, WeightSpec
+from .base import NORMS, Norm, ResidualStream, Runtime, WeightSpec
 
 
 @NORMS.register("rmsnorm")
@@ -34,27 +34,11 @@ class RMSNorm(Norm):
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    can_leave_row_factor = True
-
-    def forward(self, stream: ResidualStream, row_idx: Optional[torch.Tensor] = None, scaled_ok: bool = False):
-        """The normed rows.  With ``scaled_ok``, where the pending delta is a
-        product still to be computed and its kernel can do it: one kernel runs
-        that product, adds it to the residual and writes the rows times this
-        norm's weights, with their sums of squares beside them (``ScaledRows``);
-        the product that takes those rows applies the row factor."""
+    def forward(self, stream: ResidualStream, row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
         residual = stream.residual
-        if scaled_ok and row_idx is None and isinstance(stream.pending, DeferredProduct):
-            from ..ops import gemm_tc
-
-            pend = stream.pending
-            rows = gemm_tc.add_norm_route(pend.x, pend.linear.weight, residual, self.weight, self.eps, pend.linear.err)
-            if rows is not None:
-                stream.pending = None
-                return rows
-        pending = stream.take_pending()
         n_out = residual.shape[0] if row_idx is None else row_idx.numel()
         out = torch.empty((n_out, self.hidden_size), dtype=self.rt.dtype, device=residual.device)
-        core.add_rmsnorm(residual, pending, self.weight, self.eps, out, row_idx=row_idx,
+        core.add_rmsnorm(residual, stream.pending, self.weight, self.eps, out, row_idx=row_idx,
                          write_residual=row_idx is None)
         if row_idx is None:
             stream.pending = None

@@ -472,53 +472,6 @@ def test_gemm_tcgen05_takes_strided_rows_and_refuses_what_tma_cannot_fetch():
     assert not gemm_tc.eligible(big[:, 1:257], w, out)  # base not 16-byte aligned
 
 
-@pytest.mark.parametrize("T, N, K, splits", [(1, 128, 64, 1), (8, 80, 256, 1), (8, 4096, 1024, 4), (33, 200, 520, 2),
-                                             (64, 1000, 2048, 8), (16, 384, 4096, 8)])
-def test_gemm_tcgen05_with_the_norms_around_it(T, N, K, splits):
-    """The two fused forms of the product for few rows.  One adds the product to
-    a float32 residual and prepares the RMSNorm that follows: rows times the
-    norm's weights, and the rows' sums of squares in parts of 128 columns.  The
-    other takes such rows and applies their row factor to its product.  Held
-    against the same steps done one by one in 64-bit."""
-    from infernum_b200.ops import gemm_tc
-    from infernum_b200.parts.base import ScaledRows
-    g = torch.Generator().manual_seed(T * 77 + N)
-    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
-    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
-    res = torch.randn(T, N, generator=g)
-    gamma = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16)
-    eps = 1e-5
-    tiles = -(-N // 128)
-    residual = res.clone().to(DEV)
-    values = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    sumsq = torch.full((tiles, T + 3), float("nan"), dtype=torch.float32, device=DEV)
-    gemm_tc.gemm_tc(x.to(DEV), w.to(DEV), values, splits=splits, add_norm=(residual, gamma.to(DEV), sumsq))
-    assert gemm_tc.error_flags(DEV) == 0
-    h = res.double() + x.double() @ w.double().T
-    assert rel_err(residual, h) < 2e-6
-    assert rel_err(values, h * gamma.double()) < 5e-3
-    assert rel_err(sumsq[:, :T].sum(dim=0), (h * h).sum(dim=1)) < 1e-5
-    assert torch.isnan(sumsq[:, T:]).all()  # nothing is written beyond the rows
-    # the rows' factor on the next product: rows . W2^T * rsqrt(mean(h^2) + eps), plain and with SiLU x up
-    rows = ScaledRows(values, sumsq, tiles, N, eps)
-    factor = torch.rsqrt((h * h).mean(dim=1) + eps)
-    normed = values.double().cpu() * factor[:, None]
-    assert rel_err(rows.materialize(), normed) < 5e-3
-    M = 256
-    w2 = (torch.randn(M, N, generator=g) * 0.1).to(torch.bfloat16)
-    for out_dtype in (torch.bfloat16, torch.float32):
-        for sp in (1, 2):
-            out = torch.full((T, M), float("nan"), dtype=out_dtype, device=DEV)
-            gemm_tc.gemm_tc(values, w2.to(DEV), out, splits=sp, scale=rows)
-            assert rel_err(out, normed @ w2.double().T) < (5e-3 if out_dtype == torch.bfloat16 else 1e-5)
-    act = torch.full((T, M // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
-    gemm_tc.gemm_tc(values, w2.to(DEV), act, splits=1, swiglu=True, scale=rows)
-    gu = (normed @ w2.double().T).view(T, M // 128, 2, 64)
-    want = (gu[:, :, 0] / (1 + torch.exp(-gu[:, :, 0])) * gu[:, :, 1]).reshape(T, M // 2)
-    assert rel_err(act, want) < 6e-3
-    assert gemm_tc.error_flags(DEV) == 0
-
-
 @pytest.mark.parametrize("T, I, K", [(1, 128, 64), (8, 256, 512), (33, 192, 200), (64, 1024, 1024)])
 def test_gemm_tcgen05_with_swiglu_epilogue(T, I, K):
     """Weight rows interleaved 64 gates / 64 ups per tile; the epilogue stores silu(gate) * up."""
