@@ -1,6 +1,8 @@
 """The engine at layer sizes of the 8B class (hidden 4096, 32 heads over 8 kv
 heads of size 128, intermediate 14336, llama3 rope scaling; two layers and a
-32k vocabulary to keep it quick) against the plain implementation, in float32
+32k vocabulary to keep it quick) and of the 1B class (hidden 2048, 32 heads
+over 8 kv heads of size 64, intermediate 8192, tied embeddings, three layers)
+against the plain implementation, in float32
 and in bfloat16, under every way of cutting the work: whole prompts, portions
 of 512 and less, most of a prompt in one step and its last 32 tokens one by
 one, and four requests mixed.  This is where the tensor-core products, the
@@ -16,13 +18,23 @@ from helpers import TOL, random_tokens
 
 pytestmark = pytest.mark.gpu
 
-CFG = {
-    "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32,
-    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 32000,
-    "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
-                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
-    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+CFGS = {
+    "8b": {
+        "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 32000,
+        "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+    },
+    "1b": {
+        "model_type": "llama", "num_hidden_layers": 3, "hidden_size": 2048, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 32000,
+        "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192,
+    },
 }
 SEED = 7
 SEQS = {"a": random_tokens(700, 32000, 1), "b": random_tokens(130, 32000, 2),
@@ -56,27 +68,27 @@ def run(model, seqs, plan, page_size=16):
     return rows
 
 
-@pytest.fixture(scope="module")
-def plain_rows():
-    """The plain implementation's logits at the picked places, over the very
-    tensors the engine's models are made of (drawn once on the device; the
-    random generator is all that is shared)."""
+@pytest.fixture(scope="module", params=["8b", "1b"])
+def world(request):
+    """For one of the shapes: the plain implementation's logits at the picked
+    places, over the very tensors the engine's models are made of (drawn once
+    on the device; the random generator is all that is shared), and the
+    engine's models in both precisions."""
+    import infernum_b200 as ib
     from infernum_b200.weights.random_init import model_specs_for, random_tensors
-    _, _, specs = model_specs_for(CFG)
+    config = CFGS[request.param]
+    _, _, specs = model_specs_for(config)
     weights = {k: v.cpu() for k, v in random_tensors(specs, SEED, "cuda:0", torch.bfloat16).items()}
-    cfg = pl.read_config(CFG)
+    cfg = pl.read_config(config)
     rows = {}
     for rid, seq in SEQS.items():
         logits = pl.forward(cfg, weights, seq)
         for pos in PICKS[rid]:
             rows[(rid, pos)] = logits[pos].clone()
-    return rows
-
-
-@pytest.fixture(scope="module")
-def models():
-    import infernum_b200 as ib
-    return {d: ib.random_model(CFG, seed=SEED, dtype=d) for d in ("float32", "bfloat16")}
+    models = {d: ib.random_model(config, seed=SEED, dtype=d) for d in ("float32", "bfloat16")}
+    yield request.param, models, rows
+    del models
+    torch.cuda.empty_cache()
 
 
 def plans():
@@ -100,7 +112,8 @@ def plans():
 
 @pytest.mark.parametrize("cut", ["whole", "portions", "tail", "mixed"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_8b_class_layers_against_plain(models, plain_rows, dtype, cut):
+def test_real_layer_sizes_against_plain(world, dtype, cut):
+    shape, models, plain_rows = world
     plan = plans()[cut]
     seqs = SEQS if cut in ("whole", "mixed") else {"a": SEQS["a"]}
     rows = run(models[dtype], seqs, plan)
@@ -109,7 +122,7 @@ def test_8b_class_layers_against_plain(models, plain_rows, dtype, cut):
         ref = plain_rows[key]
         assert torch.isfinite(row).all(), f"{cut}: request {key[0]} position {key[1]}: not finite"
         err = float((row - ref).abs().max() / ref.abs().max())
-        assert err < TOL[dtype], f"{dtype} {cut}: request {key[0]} position {key[1]}: relative error {err:.3e}"
+        assert err < TOL[dtype], f"{shape} {dtype} {cut}: request {key[0]} position {key[1]}: relative error {err:.3e}"
         compared += 1
     assert compared >= {"whole": 44, "portions": 39, "tail": 39, "mixed": 40}[cut]
     if cut in ("tail", "mixed"):
