@@ -323,6 +323,7 @@ def scheduler_workloads(seed: int) -> dict:
                 "mixed_1b_ms_per_step": round(r["ms_per_step"], 3),
                 "mixed_1b_host_ms_per_step": round(r["host_ms_per_step"], 3),
                 "mixed_1b_steps_replayed": r["steps_run"].get("replayed", 0),
+                "mixed_1b_steps_launched_ahead": r.get("steps_launched_ahead", 0),
                 "mixed_1b_preemptions": r["preemptions"]})
     del model
     gc.collect()

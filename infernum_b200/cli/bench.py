@@ -176,6 +176,8 @@ def run_mixed(model, args) -> dict:
             # waiting for the device: a step is bound by the device while the former is the smaller)
             "host_ms_per_step": 1e3 * (st.step_seconds - st.wait_seconds) / max(st.steps, 1),
             "ms_per_step": 1e3 * dt / max(st.steps, 1), "preemptions": st.preemptions,
+            # steps launched behind the step in flight, before its tokens were read
+            "steps_launched_ahead": st.ahead_launched,
             # how the timed steps ran: replayed from a recording, recorded just then, or kernel by kernel
             "steps_run": {**{k: v - ran0.get(k, 0) for k, v in (engine.decoder.counts if engine.decoder else {}).items()},
                           "all": engine.runner.steps_run - steps0,
