@@ -177,11 +177,14 @@ def pack_params(c, rows):
     return p.to(DEV)
 
 
-@pytest.mark.parametrize("V", [50, 1000, 5003])
-def test_sample_against_plain(V):
+@pytest.mark.parametrize("V, R", [(50, 24), (1000, 24), (5003, 24), (33000, 12), (128256, 6), (128256, 80),
+                                  (200003, 6), (270001, 3)])
+def test_sample_against_plain(V, R):
+    """Rows of every width: one CTA a row, a row over 2, 4 and 8 CTAs of a
+    cluster (few rows: 16 candidate thresholds a pass; many rows: 4), and
+    beyond 262,144 tokens the kernel that reads its row once per pass."""
     c = core()
     rng = random.Random(V)
-    R = 24
     logits = torch.randn(R, V) * 3
     rows, recents = [], torch.zeros(R, 8, dtype=torch.int32)
     for i in range(R):
