@@ -268,6 +268,33 @@ struct SampleParams {
     int pad;
 };
 
+// The repetition penalty over a row's recent tokens, by all threads of a CTA: a
+// token that occurs k times is penalised k times (logit > 0 ? logit / r : logit * r
+// never changes the sign, so the order of the occurrences does not matter); the
+// thread that holds a token's first occurrence applies them all.
+__device__ __forceinline__ void apply_penalty(float* __restrict__ x, int V, const int* __restrict__ rt,
+                                              int n_recent, float penalty) {
+    for (int i = threadIdx.x; i < n_recent; i += blockDim.x) {
+        const int t = rt[i];
+        if (t < 0 || t >= V) continue;
+        int k = 0;
+        bool first = true;
+        for (int j = 0; j < n_recent; ++j) {
+            if (rt[j] == t) {
+                if (j < i) {
+                    first = false;
+                    break;
+                }
+                ++k;
+            }
+        }
+        if (!first) continue;
+        float v = x[t];
+        for (int q = 0; q < k; ++q) v = v > 0.f ? v / penalty : v * penalty;
+        x[t] = v;
+    }
+}
+
 __global__ void sample_kernel(float* __restrict__ logits, int ld, int V,
                               const SampleParams* __restrict__ params,
                               const int* __restrict__ recent, int recent_ld,
@@ -280,17 +307,8 @@ __global__ void sample_kernel(float* __restrict__ logits, int ld, int V,
     const SampleParams pr = params[row];
     const int nt = blockDim.x;
 
-    // 1. repetition penalty, in place, once per occurrence, in list order.
-    if (threadIdx.x == 0 && pr.penalty != 1.f) {
-        const int* rt = recent + (size_t)row * recent_ld;
-        for (int i = 0; i < pr.n_recent; ++i) {
-            const int t = rt[i];
-            if (t >= 0 && t < V) {
-                const float v = x[t];
-                x[t] = v > 0.f ? v / pr.penalty : v * pr.penalty;
-            }
-        }
-    }
+    // 1. repetition penalty, in place, once per occurrence.
+    if (pr.penalty != 1.f) apply_penalty(x, V, recent + (size_t)row * recent_ld, pr.n_recent, pr.penalty);
     __syncthreads();
 
     // 2. softmax statistics of logits / temperature.
@@ -465,17 +483,10 @@ sample_cluster_kernel(float* __restrict__ logits, int ld, int V, const SamplePar
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int turn = 0;
 
-    // 1. repetition penalty, in place, once per occurrence, in list order (one thread of the cluster).
+    // 1. repetition penalty, in place, once per occurrence (one CTA of the cluster).
     if (pr.penalty != 1.f) {
-        if (rank == 0 && threadIdx.x == 0) {
-            const int* rt = recent + (size_t)row * recent_ld;
-            for (int i = 0; i < pr.n_recent; ++i) {
-                const int t = rt[i];
-                if (t >= 0 && t < V) {
-                    const float v = x[t];
-                    x[t] = v > 0.f ? v / pr.penalty : v * pr.penalty;
-                }
-            }
+        if (rank == 0) {
+            apply_penalty(x, V, recent + (size_t)row * recent_ld, pr.n_recent, pr.penalty);
             __threadfence();
         }
         sc_cluster_sync();
