@@ -588,19 +588,31 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __res
 // src[i] < 0 keeps the token the host put there.  Launched the ordinary way,
 // behind the copy that brought `src`.
 // ---------------------------------------------------------------------------
+// The same token also goes into the row's list of recent tokens (for its
+// repetition penalty) at place recent_pos[i], where that is not negative.
 __global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
-                                   const int* __restrict__ selected, int n_selected, int n) {
+                                   const int* __restrict__ selected, int n_selected, int n,
+                                   int* __restrict__ recent, int recent_ld,
+                                   const int* __restrict__ recent_pos) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int s = src[i];
-    if (s >= 0 && s < n_selected) tokens[i] = selected[s];
+    if (s < 0 || s >= n_selected) return;
+    const int tok = selected[s];
+    tokens[i] = tok;
+    if (recent && recent_pos) {
+        const int at = recent_pos[i];
+        if (at >= 0 && at < recent_ld) recent[(size_t)i * recent_ld + at] = tok;
+    }
 }
 
 IB_EXPORT int ib_feed_tokens(int* tokens, const int* src, const int* selected, int n_selected, int n,
-                             void* stream) {
+                             int* recent, int recent_ld, const int* recent_pos, void* stream) {
     if (n <= 0) return IB_OK;
     if (!tokens || !src || !selected || n_selected <= 0) return IB_ERR_BAD_ARG;
-    feed_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, src, selected, n_selected, n);
+    if (recent && (!recent_pos || recent_ld <= 0)) return IB_ERR_BAD_ARG;
+    feed_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, src, selected, n_selected, n,
+                                                                           recent, recent_ld, recent_pos);
     IB_LAUNCH_CHECK();
     return IB_OK;
 }

@@ -77,7 +77,7 @@ class _Slot:
     """Buffers and graph of one (bucket, cache-length class, sampling, feed) key."""
 
     size: int
-    ints: torch.Tensor  # device [5, size]: tokens, positions, kv_len, slot ids, token sources
+    ints: torch.Tensor  # device [6, size]: tokens, positions, kv_len, slot ids, token sources, recent places
     host_ints: torch.Tensor  # pinned mirror
     tables: torch.Tensor  # device [groups, size, MB]
     host_tables: torch.Tensor  # pinned mirror
@@ -161,10 +161,11 @@ class DecodeRunner:
         arange = torch.arange(size + 1, dtype=torch.int32, device=dev)
         if portion == 0:
             # (row 4: for a step launched behind another, which of that step's selected tokens
-            # each row takes as its input; -1 for a token that comes from the host)
-            ints = torch.zeros((5, size), dtype=torch.int32, device=dev)
-            host_ints = torch.zeros((5, size), dtype=torch.int32).pin_memory()
-            host_ints[4] = -1
+            # each row takes as its input; -1 for a token that comes from the host.  Row 5: where
+            # in the row's recent tokens that token goes too, or -1)
+            ints = torch.zeros((6, size), dtype=torch.int32, device=dev)
+            host_ints = torch.zeros((6, size), dtype=torch.int32).pin_memory()
+            host_ints[4:] = -1
             tables = torch.full((G, size, self.MB), -1, dtype=torch.int32, device=dev)
             ctx = StepContext(
                 n_rows=size, n_entries=size, token_ids=ints[0], positions=ints[1], row_entry=arange[:size],
@@ -226,7 +227,7 @@ class DecodeRunner:
         rows, entries = size + portion, size + cls.PORTION_ENTRIES + 1
         offs, at = {}, 0
         for name, n in (("tok", rows), ("pos", rows), ("rowe", rows), ("cu", entries + 1), ("q0", entries),
-                        ("kv", entries), ("sl", entries), ("logit", size + cls.PORTION_ENTRIES), ("src", size)):
+                        ("kv", entries), ("sl", entries), ("logit", size + cls.PORTION_ENTRIES), ("src", size), ("rpos", size)):
             offs[name] = at
             at += n
         offs["end"] = at
@@ -422,7 +423,8 @@ class DecodeRunner:
                sample: Optional[tuple] = None,
                portions: Optional[Sequence[Tuple[RequestCache, Sequence[int], bool]]] = None,
                feed_from: Optional[_Slot] = None,
-               feed_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+               feed_rows: Optional[Sequence[int]] = None,
+               feed_recent: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Uploads the tokens (and sampling rows) and runs the prepared step.
         ``portions``: (request, its tokens of this step, whether its last row's
         token is wanted) for each portion the step was prepared with.
@@ -434,6 +436,8 @@ class DecodeRunner:
         prompt portions), or, where that is negative, ``tokens[i]`` from the host;
         without it the rows are those of the step before, in its order, and
         ``tokens`` is not read.  A prompt portion's own tokens always come from the host.
+        ``feed_recent[i]``: the place in row ``i``'s recent tokens (``sample``) that the fed
+        token takes too, for a row whose repetition penalty must see it; negative for none.
         ``sample``: rows for the decoded tokens in order, then for the portions
         whose token is wanted.
         The step's result starts on its way to the host at once; ``read_result``
@@ -449,22 +453,23 @@ class DecodeRunner:
             feed_rows, tokens = range(B), [0] * B
         if portions:
             hn = slot.host_np
-            at = self._portion_offsets(slot.size, slot.portion)["src"]
-            tok_rows, src_rows = hn[:slot.size], hn[at: at + slot.size]
+            offs = self._portion_offsets(slot.size, slot.portion)
+            at, rat = offs["src"], offs["rpos"]
+            tok_rows, src_rows, rpos_rows = hn[:slot.size], hn[at: at + slot.size], hn[rat: rat + slot.size]
             row = slot.size
             for _prc, toks, _w in portions:
                 hn[row: row + len(toks)] = toks
                 row += len(toks)
         else:
-            tok_rows, src_rows = slot.host_np[0], slot.host_np[4]
+            tok_rows, src_rows, rpos_rows = slot.host_np[0], slot.host_np[4], slot.host_np[5]
         tok_rows[:B] = tokens
         src_rows[:] = -1
+        rpos_rows[:] = -1
         if feed_from is not None:
             src_rows[:B] = feed_rows
+            if feed_recent is not None:
+                rpos_rows[:B] = feed_recent
         slot.ints.copy_(slot.host_ints, non_blocking=True)
-        if feed_from is not None and B:
-            dev_src = slot.ints[at: at + slot.size] if portions else slot.ints[4]
-            core.feed_tokens(slot.ctx.token_ids[:slot.size], dev_src, feed_from.selected)
         if sample is not None:
             params, recent, mask = sample
             if slot.recent is None or recent.shape[1] > slot.recent.shape[1]:
@@ -487,6 +492,14 @@ class DecodeRunner:
             slot.params.copy_(slot.host_params, non_blocking=True)
             slot.recent.copy_(slot.host_recent, non_blocking=True)
             slot.mask.copy_(slot.host_mask, non_blocking=True)
+        if feed_from is not None and B:
+            # (behind the uploads: the fed tokens go into the input rows and, where a row's
+            # repetition penalty looks at them, into its recent tokens)
+            dev_src = slot.ints[at: at + slot.size] if portions else slot.ints[4]
+            dev_rpos = slot.ints[rat: rat + slot.size] if portions else slot.ints[5]
+            with_recent = feed_recent is not None and sample is not None and slot.recent is not None
+            core.feed_tokens(slot.ctx.token_ids[:slot.size], dev_src, feed_from.selected,
+                             slot.recent if with_recent else None, dev_rpos if with_recent else None)
         if slot.uploaded is None:
             slot.uploaded = torch.cuda.Event()
         slot.uploaded.record()
@@ -530,7 +543,7 @@ class DecodeRunner:
         B = len(caches)
         hi = slot.host_ints
         hi.zero_()
-        hi[4] = -1
+        hi[4:] = -1
         hi[0, :B] = torch.tensor(list(tokens), dtype=torch.int32)
         hi[1, :B] = torch.tensor([rc.num_tokens for rc in caches], dtype=torch.int32)
         hi[3, :B] = torch.tensor([rc.slot for rc in caches], dtype=torch.int32)

@@ -185,8 +185,8 @@ class Engine:
             if split is not None:
                 # While this step runs: schedule the next one as if every request had the token
                 # this step selects for it, and launch it behind this one, fed on the device;
-                # where that cannot be (a repetition penalty needs the token itself), fill in
-                # all of it but the tokens, so that little is left to do between the two steps.
+                # where that cannot be (it is a step that runs kernel by kernel, or launching
+                # ahead is switched off), it is kept and run when the tokens have come.
                 ahead = self.scheduler.plan_ahead(plan)
                 if ahead is not None:
                     self._ahead = (ahead,) + self._launch_ahead(ahead)
@@ -245,9 +245,8 @@ class Engine:
         tokens that one selects fed on the device: the host then reads a step's
         tokens while the next step runs, and the GPU does not wait for the host
         between the two.  Possible for the steps that run from recordings
-        (decoded tokens, with or without prompt portions) when no row's sampling
-        needs the token not yet seen (a repetition penalty looks at the most
-        recent ones).  Returns (prepared buffers or None, whether it was launched,
+        (decoded tokens, with or without prompt portions); a row whose repetition
+        penalty looks at the token not yet seen gets it on the device too.  Returns (prepared buffers or None, whether it was launched,
         the step's decoded rows and portions if it runs from a recording)."""
         dec = self.decoder
         split = self._recorded_shape(ahead)
@@ -256,17 +255,25 @@ class Engine:
         decodes, riding = split
         caches = [p.seq.cache for p in decodes]
         can_launch = self.config.launch_ahead and dec.last is not None and not any(p.seq.pending for p in riding)
-        choices, feed_rows, tokens = [], [], []
+        choices, feed_rows, feed_recent, tokens = [], [], [], []
         for p in decodes + [p for p in riding if p.wants_logits]:
             sp = p.seq.options.sampling
+            place = -1
             if sp is None:
                 choices.append(None)
             elif p.seq.pending:
-                # (the token of the step in flight is not appended yet: this is the one after it)
-                can_launch = can_launch and sp.repetition_penalty == 1.0
-                choices.append((sp, len(p.seq.generated_ids) + 1, ()))
+                # (the token of the step in flight is not appended yet: this is the one after it;
+                # a repetition penalty looks at that token too, so it is given a place at the end
+                # of the row's recent tokens, which the device fills in)
+                rec = ()
+                if sp.repetition_penalty != 1.0:
+                    rec = list(recent_window(p.seq.tokens + [0], sp))
+                    place = len(rec) - 1
+                choices.append((sp, len(p.seq.generated_ids) + 1, rec))
             else:
                 choices.append((sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
+            if len(feed_recent) < len(decodes):
+                feed_recent.append(place)
         for p in decodes:
             if p.seq.pending:
                 feed_rows.append(self._flight.get(p.seq.id, -1))
@@ -280,7 +287,7 @@ class Engine:
             return (dec.prepare(caches, width) if not riding else None), False, split
         ready = dec.prepare(caches, width, portions=[(p.seq.cache, p.count, p.wants_logits) for p in riding])
         sample = pack_choices(choices, width) if width else None
-        dec.launch(ready, caches, tokens, sample, feed_from=dec.last, feed_rows=feed_rows,
+        dec.launch(ready, caches, tokens, sample, feed_from=dec.last, feed_rows=feed_rows, feed_recent=feed_recent,
                    portions=[(p.seq.cache, p.tokens, p.wants_logits) for p in riding])
         self._note_flight(decodes, riding)
         self.h2d_bytes += 4 * int(ready.ints.numel())

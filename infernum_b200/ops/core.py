@@ -77,7 +77,8 @@ def core_lib() -> ctypes.CDLL:
                                   _c_void_p, _c_void_p]
         lib.ib_decode_advance.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                           _c_void_p]
-        lib.ib_feed_tokens.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p]
+        lib.ib_feed_tokens.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
+                                       _c_void_p]
         for fn in ("ib_decode_advance", "ib_feed_tokens", "ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
                    "ib_silu_mul", "ib_attention_plain", "ib_gemm_plain", "ib_argmax", "ib_sample"):
             getattr(lib, fn).restype = _c_int
@@ -372,16 +373,25 @@ def sample(logits: torch.Tensor, params: torch.Tensor, recent: Optional[torch.Te
           "sample")
 
 
-def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, selected: torch.Tensor) -> None:
+def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, selected: torch.Tensor,
+                recent: Optional[torch.Tensor] = None, recent_pos: Optional[torch.Tensor] = None) -> None:
     """tokens[i] = selected[src[i]] where src[i] >= 0 (other rows keep theirs): the
-    inputs of a step launched behind the step whose selection ``selected`` is."""
-    require_cuda(tokens, src, selected)
-    for t, name in ((tokens, "tokens"), (src, "src"), (selected, "selected")):
+    inputs of a step launched behind the step whose selection ``selected`` is.
+    With ``recent`` [rows, width] and ``recent_pos`` [rows], the same token is
+    also written to ``recent[i, recent_pos[i]]`` where that place is not
+    negative (the row's recent tokens, for its repetition penalty)."""
+    require_cuda(tokens, src, selected, recent, recent_pos)
+    for t, name in ((tokens, "tokens"), (src, "src"), (selected, "selected"), (recent, "recent"),
+                    (recent_pos, "recent_pos")):
         _int32(t, name)
     if src.numel() < tokens.numel():
         raise KernelError("feed_tokens: fewer sources than tokens")
+    if recent is not None and (recent_pos is None or recent.dim() != 2 or recent.shape[0] < tokens.numel()
+                               or recent_pos.numel() < tokens.numel()):
+        raise KernelError("feed_tokens: the recent tokens need a row and a place per token")
     check(core_lib().ib_feed_tokens(tokens.data_ptr(), src.data_ptr(), selected.data_ptr(), selected.numel(),
-                                    tokens.numel(), stream_ptr(tokens)), "feed_tokens")
+                                    tokens.numel(), _ptr(recent), recent.shape[1] if recent is not None else 0,
+                                    _ptr(recent_pos), stream_ptr(tokens)), "feed_tokens")
 
 
 def decode_advance(tokens: torch.Tensor, selected: Optional[torch.Tensor], positions: torch.Tensor,

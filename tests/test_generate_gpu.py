@@ -190,12 +190,13 @@ def test_requests_come_and_go_under_recorded_decode_graphs(folders, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_steps_planned_ahead_survive_ends_and_arrivals(folders, dtype):
-    """While a decode step runs, the engine plans and prepares the next one.  A
-    request that ends on an end-of-sequence token, one that is cancelled and one
-    that arrives each void such a plan; the tokens of the others do not change."""
+    """With launching ahead switched off: while a step runs, the engine plans the
+    next one and keeps the plan until the tokens have come.  A request that ends
+    on an end-of-sequence token and one that is cancelled void such a plan, one
+    that arrives joins a step later; the tokens of the others do not change."""
     import infernum_b200 as ib
     model = ib.load_model(folders["B"], dtype=dtype)
-    cfg = ib.BatchConfig(max_batch_size=4, block_size=8, num_blocks=96, max_prefill_tokens=64)
+    cfg = ib.BatchConfig(max_batch_size=4, block_size=8, num_blocks=96, max_prefill_tokens=64, launch_ahead=False)
     solo = ib.Engine(model, cfg)
     prompts = [random_tokens(n, 320, 70 + n) for n in (5, 9, 14, 6)]
     sampled = ib.SamplingParams(temperature=0.9, top_p=0.95, seed=3, repetition_penalty=1.3)
@@ -215,7 +216,7 @@ def test_decode_steps_planned_ahead_survive_ends_and_arrivals(folders, dtype):
         engine.step()
     engine.cancel(h2)
     engine.run_until_done([h0, h1, h3])
-    assert engine.stats.ahead_used > 10 and engine.stats.ahead_voided >= 2
+    assert engine.stats.ahead_used > 10 and engine.stats.ahead_voided >= 2 and engine.stats.ahead_launched == 0
     assert h3.finish_reason == ib.FinishReason.LENGTH and len(h3.tokens) == 12 and len(h1.tokens) == 30
     # token for token; in bfloat16 the solo engine may round a near-tie otherwise, and what comes
     # after such a step is not compared
@@ -529,10 +530,11 @@ def test_steps_with_portions_are_launched_behind_the_step_in_flight(folders, dty
     seen = []
     launch = engine.decoder.launch
 
-    def spy(slot, caches, tokens, sample=None, portions=None, feed_from=None, feed_rows=None):
+    def spy(slot, caches, tokens, sample=None, portions=None, feed_from=None, feed_rows=None, **more):
         seen.append((len(caches), len(portions or ()), feed_from is not None,
                      sum(1 for r in (feed_rows or ()) if r >= 0)))
-        return launch(slot, caches, tokens, sample, portions=portions, feed_from=feed_from, feed_rows=feed_rows)
+        return launch(slot, caches, tokens, sample, portions=portions, feed_from=feed_from, feed_rows=feed_rows,
+                      **more)
 
     engine.decoder.launch = spy
     got = run(engine)
