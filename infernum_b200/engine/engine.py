@@ -20,7 +20,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..errors import InfernumError
 from ..sampling.params import GenerateOptions
-from ..sampling.sampler import Sampler, pack_choices, recent_window
+from ..sampling.sampler import Sampler, pack_choices
 from .decode import DecodeRunner, bucket_for
 from .scheduler import BatchConfig, FinishReason, Scheduler, Sequence_, StepPlan
 from .step import ModelRunner, StepEntry
@@ -161,8 +161,7 @@ class Engine:
                 choices = []
                 for p in wanting:
                     sp = p.seq.options.sampling
-                    choices.append(None if sp is None else
-                                   (sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
+                    choices.append(None if sp is None else (sp, len(p.seq.generated_ids), self._recent(p.seq, sp)))
                 if split is not None:
                     caches = [p.seq.cache for p in decodes]
                     width = self._recent_width(choices)
@@ -265,13 +264,11 @@ class Engine:
                 # (the token of the step in flight is not appended yet: this is the one after it;
                 # a repetition penalty looks at that token too, so it is given a place at the end
                 # of the row's recent tokens, which the device fills in)
-                rec = ()
-                if sp.repetition_penalty != 1.0:
-                    rec = list(recent_window(p.seq.tokens + [0], sp))
-                    place = len(rec) - 1
+                rec = self._recent(p.seq, sp, in_flight=True)
+                place = len(rec) - 1
                 choices.append((sp, len(p.seq.generated_ids) + 1, rec))
             else:
-                choices.append((sp, len(p.seq.generated_ids), recent_window(p.seq.tokens, sp)))
+                choices.append((sp, len(p.seq.generated_ids), self._recent(p.seq, sp)))
             if len(feed_recent) < len(decodes):
                 feed_recent.append(place)
         for p in decodes:
@@ -292,6 +289,17 @@ class Engine:
         self._note_flight(decodes, riding)
         self.h2d_bytes += 4 * int(ready.ints.numel())
         return ready, True, split
+
+    @staticmethod
+    def _recent(seq: Sequence_, sp, in_flight: bool = False) -> List[int]:
+        """The tokens a row's repetition penalty looks at: the last
+        ``repetition_penalty_window`` of its request (infernum-runtime/src/engine.rs:508-512);
+        none where there is no penalty.  ``in_flight``: the newest token is not known
+        yet and gets the last place, which the device fills in."""
+        w = sp.repetition_penalty_window
+        if sp.repetition_penalty == 1.0 or w <= 0:
+            return []
+        return seq.last_tokens(w - 1) + [0] if in_flight else seq.last_tokens(w)
 
     @staticmethod
     def _recent_width(choices) -> int:

@@ -118,6 +118,16 @@ class Sequence_:
     def num_tokens(self) -> int:
         return len(self.prompt_ids) + len(self.generated_ids) + self.pending
 
+    def last_tokens(self, n: int) -> List[int]:
+        """The last ``n`` known tokens (fewer if there are fewer), without building the whole list."""
+        if n <= 0:
+            return []
+        g = self.generated_ids
+        if len(g) >= n:
+            return g[len(g) - n:]
+        need = n - len(g)
+        return self.prompt_ids[max(0, len(self.prompt_ids) - need):] + g
+
     def token_at(self, i: int) -> int:
         n = len(self.prompt_ids)
         return self.prompt_ids[i] if i < n else self.generated_ids[i - n]

@@ -481,3 +481,12 @@ def test_leftover_budget_is_not_spent_on_a_sliver_of_a_prompt():
     drain(sched, cache)
     assert a.generated_ids == solo_tokens(list(range(3, 1203)), 4)
     cache.check_invariants()
+
+
+def test_last_tokens_of_a_request():
+    from infernum_b200.engine.scheduler import Sequence_
+    s = Sequence_(0, [1, 2, 3, 4, 5], GenerateOptions())
+    assert s.last_tokens(3) == [3, 4, 5] and s.last_tokens(9) == [1, 2, 3, 4, 5] and s.last_tokens(0) == []
+    s.generated_ids = [7, 8]
+    assert s.last_tokens(1) == [8] and s.last_tokens(2) == [7, 8] and s.last_tokens(4) == [4, 5, 7, 8]
+    assert s.last_tokens(99) == s.tokens
