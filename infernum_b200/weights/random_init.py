@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Dict, Mapping
+from typing import Any, Dict, Mapping, Optional
 
 import torch
 
@@ -128,17 +128,21 @@ def model_specs_for(config: Mapping[str, Any]):
 
 
 def write_random_model(folder: str, config: Mapping[str, Any], seed: int,
-                       dtype: torch.dtype = torch.bfloat16) -> str:
-    """Writes ``folder/config.json`` and ``folder/model.safetensors``."""
+                       dtype: torch.dtype = torch.bfloat16, device: Optional[str] = None) -> str:
+    """Writes ``folder/config.json`` and ``folder/model.safetensors``.  The
+    tensors are drawn on ``device`` (default: a GPU if there is one, which is a
+    hundred times faster for a large model) and are the same wherever they are drawn."""
     os.makedirs(folder, exist_ok=True)
     cfg, _, specs = model_specs_for(config)
     names = list(specs)
     index = {n: i for i, n in enumerate(names)}
+    if device is None:
+        device = "cuda" if torch.cuda.is_available() else "cpu"
 
     def produce(name: str) -> torch.Tensor:
         spec = specs[name]
-        t = _draw(spec, _tensor_key(seed, index[name]), "cpu")
-        return t if spec.kind == "int" else t.to(dtype)
+        t = _draw(spec, _tensor_key(seed, index[name]), device)
+        return (t if spec.kind == "int" else t.to(dtype)).cpu()
 
     file_specs = [(n, torch.int32 if specs[n].kind == "int" else dtype, specs[n].shape)
                   for n in names]
