@@ -15,7 +15,7 @@ A step of decoded tokens and a few prompt portions (the steps that recur while
 prompts are fed in portions - one portion, or the end of one prompt and the
 start of the next - and every step of a prompt that is alone) is recorded the
 same way, per bucket of the portions' rows together (``portion_bucket``): the
-recorded step has ``PORTION_ENTRIES`` entries for portions, of which a step may
+recorded step has 1, 3 or 12 entries for portions (``portion_entries``), of which a step may
 leave some empty, followed by an entry that belongs to no request and takes the
 rows left over (it attends to, and writes, the page reserved for padding), so
 that portions of any lengths up to the bucket replay one recording.  What
@@ -88,6 +88,7 @@ class _Slot:
     host_tables_np: object = None  # the same for host_tables
     rows_written: List[bool] = field(default_factory=list)  # a row that pads the bucket is written once
     portion: int = 0  # rows held for the prompt portions that ride along (0: decoded tokens only)
+    entries_k: int = 0  # entries held for them
     uploaded: Optional[torch.cuda.Event] = None  # after the last upload from the pinned mirrors
     prepared_for: Optional[tuple] = None  # request ids a prepared, not yet launched step is for
     result: Optional[torch.Tensor] = None  # device [size + 1]: the selected tokens, then the error word
@@ -125,8 +126,13 @@ class DecodeRunner:
     # portion) keys; beyond it the one unused for longest is dropped (a graph holds its own
     # activations: some 65 KB a row at the 8B layer sizes, 35 MB for a portion of 512).
     MAX_RECORDED = 256
-    # Entries a recorded step holds for prompt portions (a step with more runs kernel by kernel).
-    PORTION_ENTRIES = 3
+    # Entries a recorded step may hold for prompt portions: the smallest of these that takes the
+    # step's portions (a step with more runs kernel by kernel).  Part of a recording's key.
+    PORTION_ENTRIES = (1, 3, 12)
+
+    @classmethod
+    def portion_entries(cls, n: int) -> Optional[int]:
+        return next((k for k in cls.PORTION_ENTRIES if n <= k), None)
 
     def __init__(self, runner: ModelRunner, max_model_len: int, use_graph: bool = True):
         self.runner = runner
@@ -158,7 +164,7 @@ class DecodeRunner:
                 break
             del self._slots[victim]
             self.counts["dropped"] += 1
-        size, kv_cap, sampling, _feed, portion = key
+        size, kv_cap, sampling, _feed, portion, K = key
         dev = self.rt.device
         G = len(self.cache.groups)
         arange = torch.arange(size + 1, dtype=torch.int32, device=dev)
@@ -185,9 +191,8 @@ class DecodeRunner:
             # step: tokens | positions | row_entry (a row each) | cu_rows (entries + 1) |
             # q_start | kv_len | slots (an entry each) | logit rows (decoded rows and the last
             # row of every portion) | token sources of the decoded rows (size; see above).
-            K = self.PORTION_ENTRIES
             rows, entries = size + portion, size + K + 1
-            offs = self._portion_offsets(size, portion)
+            offs = self._portion_offsets(size, portion, K)
             ints = torch.zeros(offs["end"], dtype=torch.int32, device=dev)
             host_ints = torch.zeros(offs["end"], dtype=torch.int32).pin_memory()
             tables = torch.full((G, entries, self.MB), -1, dtype=torch.int32, device=dev)
@@ -203,11 +208,12 @@ class DecodeRunner:
                 # (for launch geometry: one portion at its longest, the entries behind it empty)
                 host_cu_rows=list(range(size + 1)) + [rows] * (K + 1), host_kv_len=[], max_rows_per_entry=portion,
                 max_kv_len=kv_cap, all_decode=False)
-        n_sel = size + (self.PORTION_ENTRIES if portion else 0)   # rows whose token is selected
+        n_sel = size + K   # rows whose token is selected
         slot = _Slot(size=size, ints=ints, host_ints=host_ints, tables=tables,
                      host_tables=torch.full(tuple(tables.shape), -1, dtype=torch.int32).pin_memory(),
                      selected=torch.zeros(n_sel, dtype=torch.int32, device=dev), ctx=ctx,
-                     rows=[None] * tables.shape[1], rows_written=[False] * tables.shape[1], portion=portion)
+                     rows=[None] * tables.shape[1], rows_written=[False] * tables.shape[1], portion=portion,
+                     entries_k=K)
         slot.host_np = slot.host_ints.numpy()
         slot.result = torch.zeros(n_sel + 1, dtype=torch.int32, device=dev)
         slot.host_results = [torch.zeros(n_sel + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -225,13 +231,13 @@ class DecodeRunner:
         self._slots[key] = slot
         return slot
 
-    @classmethod
-    def _portion_offsets(cls, size: int, portion: int) -> Dict[str, int]:
-        """Where the parts of a portion step's flat int32 buffer begin."""
-        rows, entries = size + portion, size + cls.PORTION_ENTRIES + 1
+    @staticmethod
+    def _portion_offsets(size: int, portion: int, K: int) -> Dict[str, int]:
+        """Where the parts of a portion step's flat int32 buffer begin (``K`` entries for portions)."""
+        rows, entries = size + portion, size + K + 1
         offs, at = {}, 0
         for name, n in (("tok", rows), ("pos", rows), ("rowe", rows), ("cu", entries + 1), ("q0", entries),
-                        ("kv", entries), ("sl", entries), ("logit", size + cls.PORTION_ENTRIES), ("src", size), ("rpos", size)):
+                        ("kv", entries), ("sl", entries), ("logit", size + K), ("src", size), ("rpos", size)):
             offs[name] = at
             at += n
         offs["end"] = at
@@ -321,11 +327,12 @@ class DecodeRunner:
         if portions:
             total = sum(n for _rc, n, _wants in portions)
             rows = portion_bucket(total) if portions[-1][2] else -(-total // 8) * 8
-        return (bucket_for(len(caches)), kv_cap, int(sampling), feed, rows)
+        return (bucket_for(len(caches)), kv_cap, int(sampling), feed, rows,
+                self.portion_entries(len(portions)) if portions else 0)
 
     def can_take(self, caches: Sequence[RequestCache],
                  portions: Optional[Sequence[Tuple[RequestCache, int, bool]]] = None) -> bool:
-        if portions is not None and (len(portions) > self.PORTION_ENTRIES or any(
+        if portions is not None and (self.portion_entries(len(portions)) is None or any(
                 self.cache.pages_for(prc.num_tokens + n) > self.MB for prc, n, _wants in portions)):
             return False
         return all(self.cache.pages_for(rc.num_tokens + 1) <= self.MB for rc in caches)
@@ -350,7 +357,7 @@ class DecodeRunner:
         (``recent_width``).  It may run while the
         step before is still on the GPU (its uploads are waited for first).
         ``portions``: (request, rows, whether its last row's logits are wanted) of
-        up to ``PORTION_ENTRIES`` prompt portions that ride along with the decoded
+        up to 12 prompt portions (``portion_entries``) that ride along with the decoded
         tokens (there may be none), each continuing its request where the cache
         ends; such a step is recorded per (bucket, bucket of the portions' rows
         together, cache-length class)."""
@@ -360,9 +367,9 @@ class DecodeRunner:
             slot.uploaded.synchronize()  # the pinned mirrors are free to be written again
         pad = slot.size - B
         if portions:
-            size, P, K = slot.size, slot.portion, self.PORTION_ENTRIES
+            size, P, K = slot.size, slot.portion, slot.entries_k
             rows, entries = size + P, size + K + 1
-            o = self._portion_offsets(size, P)
+            o = self._portion_offsets(size, P, K)
             hn = slot.host_np
             pos, rowe = hn[o["pos"]: o["pos"] + rows], hn[o["rowe"]: o["rowe"] + rows]
             cu, q0 = hn[o["cu"]: o["cu"] + entries + 1], hn[o["q0"]: o["q0"] + entries]
@@ -457,7 +464,7 @@ class DecodeRunner:
             feed_rows, tokens = range(B), [0] * B
         if portions:
             hn = slot.host_np
-            offs = self._portion_offsets(slot.size, slot.portion)
+            offs = self._portion_offsets(slot.size, slot.portion, slot.entries_k)
             at, rat = offs["src"], offs["rpos"]
             tok_rows, src_rows, rpos_rows = hn[:slot.size], hn[at: at + slot.size], hn[rat: rat + slot.size]
             row = slot.size

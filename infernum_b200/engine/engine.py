@@ -319,7 +319,7 @@ class Engine:
     def _recorded_shape(self, plan: StepPlan):
         """(decoded rows, prompt portions) if the step is one that runs from a
         recording: decoded tokens - or none - beside at most a few prompt portions
-        (``DecodeRunner.PORTION_ENTRIES``).  Such steps recur: while long prompts
+        (``DecodeRunner.portion_entries``).  Such steps recur: while long prompts
         are fed in portions beside the decoding requests (one portion, or the end
         of one prompt and the start of the next), and for every prompt that comes
         alone.  They are recorded per bucket of the portions' rows together (rows
@@ -333,7 +333,8 @@ class Engine:
         riding = [p for p in plan.portions if not (p.count == 1 and p.wants_logits)]
         if not riding:
             return (decodes, riding) if self.decoder.can_take([p.seq.cache for p in decodes]) else None
-        if len(riding) > self.decoder.PORTION_ENTRIES or sum(p.count for p in riding) < self.GRAPH_PORTION_MIN:
+        if self.decoder.portion_entries(len(riding)) is None \
+                or sum(p.count for p in riding) < self.GRAPH_PORTION_MIN:
             return None
         last = riding[-1]
         m = self.config.token_multiple
