@@ -78,8 +78,8 @@ class RequestCache:
 
 
 class CacheManager:
-    def __init__(self, needs: Sequence, page_size: int, num_pages: int, max_requests: int,
-                 dtype: torch.dtype = torch.bfloat16, device=None):
+    def __init__(self, needs: Sequence, page_size: int, num_pages, max_requests: int,
+                 dtype: torch.dtype = torch.bfloat16, device=None, memory_fraction: float = 0.9):
         """``needs``: one item per schedule position with attributes
         ``paged`` (PagedCacheSpec or None), ``state`` (StateSpec or None) and
         ``cache_of`` (an earlier position or None).  ``num_pages`` sizes the
@@ -87,12 +87,16 @@ class CacheManager:
         per group (groups are numbered in the order in which the schedule first
         needs them), or a function of the group's ``PagedCacheSpec`` - a group
         whose window lets it give pages back early, or whose keys are small,
-        needs fewer or cheaper pages than one that keeps everything."""
+        needs fewer or cheaper pages than one that keeps everything.  ``None``:
+        as many pages (the same number in every pool) as ``memory_fraction`` of
+        the device's free memory holds."""
         if page_size <= 0:
             raise CacheError("page_size must be positive")
         if max_requests <= 0:
             raise CacheError("max_requests must be positive")
         self.page_size = int(page_size)
+        if num_pages is None:
+            num_pages = self._pages_that_fit(needs, dtype, device, memory_fraction)
         self._pages_arg = num_pages
         self.group_pages: List[int] = []
         self.max_requests = int(max_requests)
@@ -128,8 +132,19 @@ class CacheManager:
                 lc.group, lc.page_size, lc.num_pages = g, self.page_size, pages + 1
                 if device is not None:
                     shape = (pages + 1, need.paged.kv_heads, self.page_size, need.paged.head_dim)
-                    lc.k_pool = torch.zeros(shape, dtype=dtype, device=device)
-                    lc.v_pool = torch.zeros(shape, dtype=dtype, device=device)
+                    try:
+                        lc.k_pool = torch.zeros(shape, dtype=dtype, device=device)
+                        lc.v_pool = torch.zeros(shape, dtype=dtype, device=device)
+                    except torch.cuda.OutOfMemoryError:
+                        el = torch.empty((), dtype=dtype).element_size()
+                        per_page = sum(2 * n.paged.kv_heads * self.page_size * n.paged.head_dim * el
+                                       for n in needs if n.paged is not None and n.cache_of is None)
+                        free = torch.cuda.mem_get_info(device)[0]
+                        raise CacheError(
+                            f"the cache pools do not fit the device: a page costs {per_page} bytes over all "
+                            f"layers, {pages} pages were asked for, {free / 1e9:.1f} GB were free when the "
+                            f"pool at schedule position {need.position} could not be made; ask for fewer pages "
+                            f"(or num_pages=None for as many as fit)") from None
             if need.state is not None and need.cache_of is None:
                 if device is not None:
                     lc.state = torch.zeros((self.max_requests + 1, *need.state.shape),
@@ -141,6 +156,23 @@ class CacheManager:
                 and len(self._pages_arg) != len(self.groups):
             raise CacheError(f"num_pages names {len(self._pages_arg)} pools, the model has "
                              f"{len(self.groups)} cache groups")
+
+    def _pages_that_fit(self, needs: Sequence, dtype: torch.dtype, device, fraction: float) -> int:
+        """Pages per pool so that all pools together take ``fraction`` of the free device memory."""
+        if device is None or torch.device(device).type != "cuda":
+            raise CacheError("num_pages=None sizes the pools from a CUDA device's free memory: give a device")
+        if not 0.0 < fraction <= 1.0:
+            raise CacheError("memory_fraction must be in (0, 1]")
+        el = torch.empty((), dtype=dtype).element_size()
+        per_page = sum(2 * n.paged.kv_heads * self.page_size * n.paged.head_dim * el
+                       for n in needs if n.paged is not None and n.cache_of is None)
+        if per_page == 0:
+            return 1
+        free = torch.cuda.mem_get_info(device)[0]
+        pages = int(fraction * free // per_page) - 1  # (a page behind every pool is kept for padding rows)
+        if pages < 1:
+            raise CacheError(f"no room for cache pages: a page costs {per_page} bytes, {free} are free")
+        return pages
 
     def _pages_of_group(self, g: int, spec: PagedCacheSpec) -> int:
         arg = self._pages_arg

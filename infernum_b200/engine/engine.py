@@ -81,7 +81,7 @@ class Engine:
         rt = model.rt
         self.cache = CacheManager(model.cache_needs(), page_size=cfg.block_size,
                                   num_pages=cfg.num_blocks, max_requests=cfg.max_batch_size,
-                                  dtype=rt.dtype, device=rt.device)
+                                  dtype=rt.dtype, device=rt.device, memory_fraction=cfg.cache_memory_fraction)
         self.runner = ModelRunner(model, self.cache, max_rows=cfg.max_tokens_per_step,
                                   max_entries=cfg.max_batch_size)
         max_len = cfg.max_model_len or model.spec.max_position

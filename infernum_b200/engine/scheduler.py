@@ -66,7 +66,10 @@ class BatchConfig:
     max_batch_size: int = 32
     max_prefill_tokens: int = 512
     block_size: int = 16
-    num_blocks: int = 1024  # pages of every cache group's pool, or a list with one number per group
+    # pages of every cache group's pool, or a list with one number per group; None: as many as
+    # `cache_memory_fraction` of the device's free memory holds
+    num_blocks: Optional[int] = 1024
+    cache_memory_fraction: float = 0.9
     max_tokens_per_step: int = 2048
     max_model_len: Optional[int] = None  # default: the model's max_position_embeddings
     cuda_graphs: bool = True  # replay a recorded graph while the same requests decode

@@ -184,3 +184,10 @@ def test_pools_sized_group_by_group():
         CacheManager(needs, page_size=4, num_pages=[40, 6, 3], max_requests=2)
     with pytest.raises(CacheError, match="cache groups"):
         CacheManager(needs, page_size=4, num_pages=[40], max_requests=2)
+
+
+def test_pools_sized_from_free_memory_need_a_device():
+    from infernum_b200.errors import CacheError
+    need = SimpleNamespace(position=0, paged=PagedCacheSpec(1, 8, 0), state=None, cache_of=None)
+    with pytest.raises(CacheError, match="free memory"):
+        CacheManager([need], page_size=4, num_pages=None, max_requests=2)

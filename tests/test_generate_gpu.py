@@ -611,3 +611,34 @@ def test_random_traffic_through_the_pipeline_equals_runs_alone(folders, seed):
     assert not engine.decoder._reads
     assert engine.cache.free_pages() == [44] and engine.cache.num_free_slots == 5
     engine.runner.check_errors()
+
+
+def test_cache_pools_sized_from_the_free_memory(folders, monkeypatch):
+    """``num_blocks=None``: as many pages as the given share of the free memory
+    holds; a request for pages that the device refuses says what a page costs
+    (the refusal is played by a stand-in: no memory is taken)."""
+    import infernum_b200 as ib
+    from infernum_b200.errors import CacheError
+    model = ib.load_model(folders["B"], dtype="bfloat16")
+    free = torch.cuda.mem_get_info()[0]
+    engine = ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=16, num_blocks=None,
+                                             cache_memory_fraction=0.01))
+    per_page = engine.cache.bytes_per_token() * 16
+    pages = engine.cache.num_pages
+    assert pages > 100 and 0.008 * free < (pages + 1) * per_page <= 0.0101 * free
+    prompt = random_tokens(9, 320, 5)
+    assert engine.generate(prompt, ib.GenerateOptions(max_new_tokens=8)) == \
+        ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=16, num_blocks=8)).generate(
+            prompt, ib.GenerateOptions(max_new_tokens=8))
+    del engine
+    torch.cuda.empty_cache()
+    zeros = torch.zeros
+
+    def refuse(shape, *args, **kwargs):
+        if len(shape) == 4 and shape[0] > 1000:
+            raise torch.cuda.OutOfMemoryError("stand-in")
+        return zeros(shape, *args, **kwargs)
+
+    monkeypatch.setattr(torch, "zeros", refuse)
+    with pytest.raises(CacheError, match="do not fit the device"):
+        ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=16, num_blocks=5000))
