@@ -1,7 +1,7 @@
 """``bench``: throughput of a model through the engine, in the manner of the
 reference's example (infernum-examples/examples/bench.rs:72-158, 1035-1036):
 
-    bench MODEL [N_GEN] [--dtype bf16|f32]
+    bench MODEL [N_GEN] [--dtype bf16|f32] [--graph | --graph-decode] [--cuda-graph-engine] [--gpus 1]
 
 ``MODEL`` is a model folder, or one of the shapes ``8b``, ``1b``, ``13b``,
 ``tinyA``, ``tinyB`` with random weights.  The default workload is the
@@ -66,6 +66,15 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("model", help="model folder, or a shape name: " + ", ".join(SHAPES))
     ap.add_argument("n_gen", nargs="?", type=int, default=128, help="tokens to generate")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "bfloat16", "float32"])
+    # the reference's mode switches (bench.rs:72-104).  It has several engines to choose from;
+    # here there is one, which records and replays its steps, so two of them only say so.
+    ap.add_argument("--graph", action="store_true",
+                    help="prefill throughput: N_GEN tokens in a single forward pass")
+    ap.add_argument("--graph-decode", action="store_true",
+                    help="decode throughput: N_GEN tokens one by one (the default workload)")
+    ap.add_argument("--cuda-graphs", action="store_true", help="accepted: steps are always recorded and replayed")
+    ap.add_argument("--cuda-graph-engine", action="store_true", help="accepted: this is the only engine")
+    ap.add_argument("--gpus", type=int, default=1, help="only 1: this engine runs on one GPU")
     ap.add_argument("--workload", default="single", choices=["single", "mixed", "pressure"])
     ap.add_argument("--requests", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
@@ -105,14 +114,15 @@ def run_single(model, args) -> dict:
 
     vocab = model.spec.vocab_size
     prompt = [t % vocab for t in (1, 15043, 29892, 920, 526, 366, 2599, 13)]  # bench.rs:138
-    n_gen = args.n_gen
-    prefill_tokens = min(512, model.spec.max_position - 1)
+    n_gen = 8 if args.graph else args.n_gen
+    prefill_tokens = min(args.n_gen if args.graph else 512, model.spec.max_position - 1)
     blocks = (max(prefill_tokens, len(prompt) + n_gen) + 1) // args.block_size + 4
     engine = ib.Engine(model, ib.BatchConfig(max_batch_size=1, block_size=args.block_size,
-                                             num_blocks=blocks, max_prefill_tokens=2048,
+                                             num_blocks=blocks, max_prefill_tokens=max(2048, prefill_tokens),
+                                             max_tokens_per_step=max(2048, prefill_tokens),
                                              max_model_len=max(prefill_tokens + 2, len(prompt) + n_gen + 1)))
     opts = ib.GenerateOptions(max_new_tokens=n_gen, ignore_eos=True)
-    engine.generate(prompt, ib.GenerateOptions(max_new_tokens=4, ignore_eos=True))  # warm-up
+    engine.generate(prompt, ib.GenerateOptions(max_new_tokens=8, ignore_eos=True))  # warm-up
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     tokens = engine.generate(prompt, opts)
@@ -121,7 +131,8 @@ def run_single(model, args) -> dict:
     rng = random.Random(args.seed)
     long_prompt = [rng.randrange(vocab) for _ in range(prefill_tokens)]
     one = ib.GenerateOptions(max_new_tokens=1, ignore_eos=True)
-    engine.generate(long_prompt, one)  # warm-up
+    for _ in range(2):  # warm-up: a step's shape is recorded the second time it is met
+        engine.generate(long_prompt, one)
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     engine.generate(long_prompt, one)
@@ -251,10 +262,16 @@ def run_pressure(model, args) -> dict:
 
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
+    if args.gpus != 1:
+        print("bench: this engine runs on one GPU (--gpus 1)", file=sys.stderr)
+        return 2
     model = load(args)
     result = {"single": run_single, "mixed": run_mixed, "pressure": run_pressure}[args.workload](model, args)
     if args.json:
         print(json.dumps({k: (round(v, 3) if isinstance(v, float) else v) for k, v in result.items()}))
+    elif args.workload == "single" and args.graph:
+        print(f"{result['prefill_tokens']} tokens in {result['prefill_tokens'] / result['prefill_tok_s']:.4f}s = "
+              f"{result['prefill_tok_s']:.1f} tok/s")
     elif args.workload == "single":
         print(f"{result['generated']} tokens in {result['seconds']:.2f}s = {result['decode_tok_s']:.1f} tok/s")
         print(f"prefill {result['prefill_tokens']} tokens = {result['prefill_tok_s']:.1f} tok/s")
