@@ -161,7 +161,8 @@ def load_module(name: str, sources: Sequence[str], defines: Sequence[str] = ()) 
             except OSError as exc:
                 raise KernelError(f"cannot load {path}: {exc}") from exc
             lib._ib_path = path
-            if os.environ.get("INFERNUM_PDL", "1") == "0" and hasattr(lib, "ib_set_pdl"):
+            serial = os.environ.get("INFERNUM_PDL", "1") == "0" or os.environ.get("INFERNUM_PROFILE", "0") not in ("", "0")
+            if serial and hasattr(lib, "ib_set_pdl"):
                 lib.ib_set_pdl(0)  # launch every kernel strictly after its predecessor
             _loaded[key] = lib
         return lib

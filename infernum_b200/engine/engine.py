@@ -19,6 +19,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..errors import InfernumError
+from ..ops import core
 from ..sampling.params import GenerateOptions
 from ..sampling.sampler import Sampler, pack_choices
 from .decode import DecodeRunner, bucket_for
@@ -89,7 +90,9 @@ class Engine:
         self.sampler = Sampler(rt.device)
         self.stats = EngineStats()
         self._handles: Dict[int, RequestHandle] = {}
-        self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if cfg.cuda_graphs and model.replayable else None
+        # (in profile mode every operation is launched and timed by itself: no recordings)
+        recorded = cfg.cuda_graphs and model.replayable and not core.PROFILE
+        self.decoder = DecodeRunner(self.runner, max_len, use_graph=True) if recorded else None
         # the next decode step, planned and prepared while the one before it ran
         # (plan, prepared buffers, whether it is on the GPU already)
         self._ahead: Optional[Tuple[StepPlan, object, bool, object]] = None

@@ -8,6 +8,7 @@ a CUDA device, or a missing/unbuildable extension, raises ``KernelError``.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -125,11 +126,94 @@ class step_stream:
 
 LAUNCHES = 0  # kernels of this package launched so far (benchmarks report the count)
 
+# ---------------------------------------------------------------------------
+# INFERNUM_PROFILE=1: the device time of every operation, summed per operation
+# and printed as a table when the process ends (the reference does this for its
+# CPU executor: infernum-cpu/src/executor.rs:24-62).  A CUDA event is recorded
+# before and behind every launch.  For the time between the two to be the
+# operation's, the kernels must not overlap and must be launched one by one:
+# in this mode programmatic dependent launch is off and the engine replays no
+# recordings.  What the table shows is therefore not what a step costs in
+# service, where kernels start under their predecessor's tail: it shows where
+# the time goes.  A kernel that starts on an idle stream pays its launch
+# (some 10 to 15 us between the two events even for the smallest kernel), and
+# the first call of a library product pays the library's set-up: read the
+# shares of the large operations here, and a kernel's own duration from
+# ``ncu`` or ``python -m infernum_b200.cli.kernel_bench``.
+# ---------------------------------------------------------------------------
+PROFILE = os.environ.get("INFERNUM_PROFILE", "0") not in ("", "0")
+_profile_marks: list = []  # (operation, event before, event after), in launch order
+_profile_totals: dict = {}  # operation -> [calls, microseconds]
+_profile_open = None  # the event before the operation being launched
+
+
+def _profile_event():
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record(torch.cuda.current_stream() if _step_stream is None else torch.cuda.ExternalStream(_step_stream))
+    return ev
+
+
+def profile_begin() -> None:
+    """The start of an operation (profile mode only): every wrapper passes here
+    on its way in (``require_cuda``); ``profile_mark`` closes it."""
+    global _profile_open
+    if PROFILE and _profile_open is None:
+        _profile_open = _profile_event()
+
+
+def profile_mark(what: str) -> None:
+    """The end of operation ``what`` on the current stream (profile mode only).
+    Its time runs from ``profile_begin``, or from the end of the operation
+    before it when one wrapper launches two kernels."""
+    global _profile_open
+    if not PROFILE:
+        return
+    after = _profile_event()
+    before = _profile_open if _profile_open is not None else (_profile_marks[-1][2] if _profile_marks else after)
+    _profile_open = None
+    _profile_marks.append((what, before, after))
+    if len(_profile_marks) >= 20000:
+        profile_collect()
+
+
+def profile_collect() -> dict:
+    """Folds the marks so far into the totals and returns them: operation -> [calls, microseconds]."""
+    if _profile_marks:
+        torch.cuda.synchronize()
+        for what, before, after in _profile_marks:
+            row = _profile_totals.setdefault(what, [0, 0.0])
+            row[0] += 1
+            row[1] += before.elapsed_time(after) * 1000.0
+        del _profile_marks[:]
+    return _profile_totals
+
+
+def profile_report(file=None) -> str:
+    """The table of ``profile_collect``; printed to ``file`` when given."""
+    totals = profile_collect()
+    whole = sum(v[1] for v in totals.values()) or 1.0
+    lines = [f"{'operation':28s} {'calls':>8s} {'total ms':>10s} {'mean us':>9s} {'share':>7s}"]
+    for what, (calls, us) in sorted(totals.items(), key=lambda kv: -kv[1][1]):
+        lines.append(f"{what:28s} {calls:8d} {us / 1000:10.2f} {us / max(calls, 1):9.2f} {100 * us / whole:6.1f}%")
+    text = "\n".join(lines)
+    if file is not None:
+        print(text, file=file)
+    return text
+
+
+if PROFILE:
+    import atexit
+    import sys as _sys
+
+    atexit.register(lambda: profile_report(_sys.stderr) if (_profile_marks or _profile_totals) else None)
+
 
 def check(code: int, what: str) -> None:
     global LAUNCHES
     if code == 0:
         LAUNCHES += 1
+        if PROFILE:
+            profile_mark(what)
         return
     if code < 0:
         raise KernelError(f"{what}: kernel refused its arguments ({_ERR_NAMES.get(code, code)})")
@@ -137,6 +221,8 @@ def check(code: int, what: str) -> None:
 
 
 def require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    if PROFILE:
+        profile_begin()
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise KernelError(

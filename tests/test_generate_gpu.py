@@ -642,3 +642,29 @@ def test_cache_pools_sized_from_the_free_memory(folders, monkeypatch):
     monkeypatch.setattr(torch, "zeros", refuse)
     with pytest.raises(CacheError, match="do not fit the device"):
         ib.Engine(model, ib.BatchConfig(max_batch_size=2, block_size=16, num_blocks=5000))
+
+
+def test_profile_mode_times_every_operation(folders, monkeypatch):
+    """With profiling on (the switch ``INFERNUM_PROFILE=1`` sets at start-up) every
+    operation's device time is summed per operation; the engine replays no
+    recordings then, and generates what it generates otherwise."""
+    import infernum_b200 as ib
+    from infernum_b200.ops import core
+    model = ib.load_model(folders["B"], dtype="bfloat16")
+    cfg = ib.BatchConfig(max_batch_size=2, block_size=8, num_blocks=32)
+    prompt = random_tokens(21, 320, 3)
+    want = ib.Engine(model, cfg).generate(prompt, ib.GenerateOptions(max_new_tokens=6))
+    monkeypatch.setattr(core, "PROFILE", True)
+    core._profile_marks.clear()
+    core._profile_totals.clear()
+    engine = ib.Engine(model, cfg)
+    assert engine.decoder is None
+    assert engine.generate(prompt, ib.GenerateOptions(max_new_tokens=6)) == want
+    totals = core.profile_collect()
+    layers = len(model.layers)
+    assert totals["add_rmsnorm"][0] == 6 * (2 * layers + 1) and totals["rope_append"][0] == 6 * layers
+    assert all(calls > 0 and us >= 0 for calls, us in totals.values()) and totals["add_rmsnorm"][1] > 0
+    assert any(k.startswith("attention") for k in totals) and any(k.startswith("gemm") for k in totals)
+    text = core.profile_report()
+    assert "share" in text and "add_rmsnorm" in text
+    core._profile_totals.clear()
