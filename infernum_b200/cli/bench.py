@@ -86,7 +86,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--solo-checks", type=int, default=None,
                     help="pressure: compare only so many requests with their run alone (preempted ones first)")
     ap.add_argument("--no-warmup", action="store_true",
-                    help="mixed: time the first pass too (it records the decode graphs)")
+                    help="mixed, pressure: time the first pass too (it records the steps' graphs)")
     ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
     return ap
 
@@ -212,6 +212,11 @@ def run_pressure(model, args) -> dict:
     cfg = dict(max_batch_size=n_req, max_prefill_tokens=512, block_size=args.block_size,
                max_tokens_per_step=512 + n_req, max_model_len=prompt_len + new_tokens + 1)
     tight = ib.Engine(model, ib.BatchConfig(num_blocks=blocks, **cfg))
+    if not args.no_warmup:
+        # one untimed pass: the steps' shapes are recorded (the timed pass replays them)
+        tight.run_until_done([tight.submit(p, opts) for p in prompts])
+        tight.stats = type(tight.stats)()
+        tight.scheduler.num_preemptions = 0
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     handles = [tight.submit(p, opts) for p in prompts]
