@@ -185,7 +185,7 @@ def test_sample_against_plain(V, R):
     beyond 262,144 tokens the kernel that reads its row once per pass."""
     c = core()
     rng = random.Random(V)
-    logits = torch.randn(R, V) * 3
+    logits = torch.randn(R, V, generator=torch.Generator().manual_seed(V)) * 3
     rows, recents = [], torch.zeros(R, 8, dtype=torch.int32)
     for i in range(R):
         nr = rng.randint(0, 8)
@@ -196,22 +196,24 @@ def test_sample_against_plain(V, R):
                      rng.choice([1.0, 1.1, 1.3]), rng.random(), nr))
     out = torch.empty(R, dtype=torch.int32, device=DEV)
     c.sample(logits.clone().to(DEV), pack_params(c, rows), recents.to(DEV), out)
-    checked = 0
+    exact = 0
     for i, (t, tp, pen, u, nr) in enumerate(rows):
+        # The plain distribution in 64-bit, and the place of the kernel's token in it.  The
+        # kernel works in 32-bit: its sums are off by rounding, and a token at the very edge
+        # of the nucleus (one of many of nearly the same, tiny probability in a wide
+        # vocabulary) may be in or out.  Either moves the cumulative distribution by some
+        # 1e-6, so the token must be the one whose interval holds u to within 1e-5.
         probs = pl.sample_probabilities(logits[i], t, tp, pen, recents[i, :nr].tolist())
-        want = pl.sample_index_order(probs, u)
-        # skip rows where u sits within rounding of a boundary of the CDF, or the
-        # nucleus edge is within rounding of top_p
+        got = int(out[i].item())
         cdf = torch.cumsum(probs, 0)
-        if (cdf - u).abs().min() < 1e-5:
-            continue
-        full = pl.sample_probabilities(logits[i], t, 1.0, pen, recents[i, :nr].tolist())
-        order = torch.argsort(full, descending=True)
-        if tp < 1.0 and (torch.cumsum(full[order], 0) - tp).abs().min() < 1e-5:
-            continue
-        assert out[i].item() == want, f"row {i}: {rows[i]}"
-        checked += 1
-    assert checked >= R // 2
+        lo = float(cdf[got - 1]) if got > 0 else 0.0
+        hi = float(cdf[got])
+        assert lo - 1e-5 <= u < hi + 1e-5, f"row {i}: {rows[i]} -> {got}, interval [{lo}, {hi})"
+        if probs[got] == 0:  # only a token at the edge: as probable as the least probable one kept
+            full = pl.sample_probabilities(logits[i], t, 1.0, pen, recents[i, :nr].tolist())
+            assert tp < 1.0 and full[got] >= (1 - 1e-4) * full[probs > 0].min(), f"row {i}: {rows[i]} -> {got}"
+        exact += int(got == pl.sample_index_order(probs, u))
+    assert exact >= R // 2  # (most rows are nowhere near an edge)
 
 
 def test_sample_distribution_over_many_draws():
