@@ -317,7 +317,8 @@ class Engine:
         return DecodeRunner.recent_width([sp.repetition_penalty_window for sp in rows
                                           if sp.repetition_penalty != 1.0])
 
-    GRAPH_PORTION_MIN = 16
+    # the fewest rows the portions of a recorded step have together (a portion is never cut below it)
+    GRAPH_PORTION_MIN = 2
 
     def _recorded_shape(self, plan: StepPlan):
         """(decoded rows, prompt portions) if the step is one that runs from a
