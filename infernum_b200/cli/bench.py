@@ -122,7 +122,8 @@ def run_single(model, args) -> dict:
                                              max_tokens_per_step=max(2048, prefill_tokens),
                                              max_model_len=max(prefill_tokens + 2, len(prompt) + n_gen + 1)))
     opts = ib.GenerateOptions(max_new_tokens=n_gen, ignore_eos=True)
-    engine.generate(prompt, ib.GenerateOptions(max_new_tokens=8, ignore_eos=True))  # warm-up
+    for _ in range(2):  # warm-up: a step's shape is recorded the second time it is met
+        engine.generate(prompt, ib.GenerateOptions(max_new_tokens=8, ignore_eos=True))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     tokens = engine.generate(prompt, opts)
