@@ -711,7 +711,7 @@ __device__ __forceinline__ const bf16* swz(const bf16* tile, int row, int dim) {
     return tile + (dim >> 6) * (TMA_BLOCK_BYTES / 2) + row * 64 + ((((dim & 63) >> 3) ^ (row & 7)) << 3);
 }
 
-__global__ void __launch_bounds__(TMA_THREADS)
+__global__ void __launch_bounds__(TMA_THREADS, 2)
 attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ __align__(16) unsigned char smem_dyn[];
