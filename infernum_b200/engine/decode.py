@@ -95,8 +95,6 @@ class _Slot:
     host_results: Optional[list] = None  # two pinned mirrors, used in turn
     result_events: Optional[list] = None  # and the events after their copies
     result_turn: int = 0
-    result_pending: bool = False  # a copy of `result` to the host has been queued
-    done: Optional[torch.cuda.Event] = None  # after the step's last kernel
     sampled: Optional[torch.Tensor] = None
     params: Optional[torch.Tensor] = None
     host_params: Optional[torch.Tensor] = None
@@ -147,7 +145,6 @@ class DecodeRunner:
         self.last: Optional[_Slot] = None
         # results of launched steps on their way to the host, oldest first
         self._reads: collections.deque = collections.deque(maxlen=4)
-        self._copy_stream = torch.cuda.Stream(device=self.rt.device) if self.rt.device.type == "cuda" else None
         # how the steps so far ran: kernel by kernel, recorded (and replayed at once), replayed
         self.counts = {"eager": 0, "recorded": 0, "replayed": 0, "dropped": 0}
 
@@ -218,7 +215,6 @@ class DecodeRunner:
         slot.result = torch.zeros(n_sel + 1, dtype=torch.int32, device=dev)
         slot.host_results = [torch.zeros(n_sel + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         slot.result_events = [torch.cuda.Event(), torch.cuda.Event()]
-        slot.done = torch.cuda.Event()
         if sampling:
             f = core.SAMPLE_PARAM_FLOATS
             slot.sampled = torch.zeros(n_sel, dtype=torch.int32, device=dev)
@@ -514,22 +510,11 @@ class DecodeRunner:
         if slot.uploaded is None:
             slot.uploaded = torch.cuda.Event()
         slot.uploaded.record()
+        self._run(slot, device_feed=False)
         turn = slot.result_turn
         slot.result_turn ^= 1
-        main = torch.cuda.current_stream(self.rt.device)
-        if slot.result_pending:
-            # (the step writes `slot.result` again: the copy of what it held, on the other
-            # stream, must be over - it has been for long; this makes it certain)
-            main.wait_event(slot.result_events[turn ^ 1])
-        self._run(slot, device_feed=False)
-        # The result goes to the host on a stream of its own, so that the copy is not in the way
-        # of the next step's uploads and launch, which queue on the step's stream behind it.
-        slot.done.record(main)
-        self._copy_stream.wait_event(slot.done)
-        with torch.cuda.stream(self._copy_stream):
-            slot.host_results[turn].copy_(slot.result, non_blocking=True)
-            slot.result_events[turn].record(self._copy_stream)
-        slot.result_pending = True
+        slot.host_results[turn].copy_(slot.result, non_blocking=True)
+        slot.result_events[turn].record()
         self._reads.append((slot.host_results[turn], slot.result_events[turn], slot.size,
                             slot.selected.shape[0]))
         for rc in caches:
