@@ -604,6 +604,7 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
         }
         tc_fence_before();
     }
+    __syncwarp();  // the elected lane is back with its warp before the aligned barriers
     if (S > 1) {
         // ---- merge of the slices: the leader adds the others' rows to its own ----------
         cluster_sync_all();

@@ -122,6 +122,20 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same without the attribute: the kernel starts when everything before it in
+// the stream is complete (its pdl_wait() is then a no-op), while its own
+// pdl_trigger() still lets the kernel after it begin early.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                          cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 

@@ -386,6 +386,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         }
         tc_fence_before();
     }
+    __syncwarp();  // the elected lanes are back with their warps before the aligned barriers
     if (p.splits > 1) {
         cluster_sync_all();  // every slice's partial tile is in place
         if (warp >= 2) {

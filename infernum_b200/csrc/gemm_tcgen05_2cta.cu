@@ -29,6 +29,8 @@
 //
 // Every wait on an mbarrier is bounded; on a time-out the CTA sets
 // IB_FLAG_WAIT_TIMEOUT, stops, frees its tensor memory and returns.
+// The kernel is launched in order (see launch_pair), so its griddepcontrol.wait
+// returns at once; its launch_dependents still lets the next kernel begin early.
 //
 // The reference computes these products with cuBLAS GemmEx
 // (infernum-cuda/src/inner/cuda/ops/matmul.rs:68-116) and SwiGLU in a kernel of
@@ -240,6 +242,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                      ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
     }
+    __syncwarp();
     tc_fence_before();
     cluster_sync_all();   // both CTAs' barriers are initialised before anyone signals them
     tc_fence_after();
@@ -358,6 +361,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         if (!ok && lane == 0) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_PAIR_EPILOGUE));
     }
+    __syncwarp();   // the elected lanes are back with their warps before the aligned instructions below
     tc_fence_before();
     cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still use it
     if (warp == 1) {
@@ -406,8 +410,16 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap&
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    cudaError_t le = launch_kernel(gemm_pair_kernel<SWIGLU>, dim3((unsigned)(pairs * 2)), dim3(NUM_THREADS),
-                                   (size_t)SMEM_BYTES, stream, mx, mw, mw2, p);
+    // In order, not as a programmatic dependent.  Begun under the tail of its
+    // predecessor (where its CTAs, which fill an SM each, sit on the SMs that fall
+    // free while the rest of the chain before them still runs), steps of whole
+    // 2,048-token prompts at d = 5120 with 40 heads stopped for good now and then:
+    // this kernel's MMA issuer, the one role that does not wait for the grid
+    // before, reported its time-out, and producers and epilogues never came out of
+    // griddepcontrol.wait.  Launched in order, with the same code, they never did
+    // (the prologue that no longer overlaps is about a microsecond a product).
+    cudaError_t le = launch_kernel_in_order(gemm_pair_kernel<SWIGLU>, dim3((unsigned)(pairs * 2)),
+                                            dim3(NUM_THREADS), (size_t)SMEM_BYTES, stream, mx, mw, mw2, p);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;
