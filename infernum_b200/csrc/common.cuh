@@ -57,6 +57,10 @@ typedef __nv_bfloat16 bf16;
 // setting up barriers, fetching weights, which no kernel writes - overlaps
 // with its predecessor.  pdl_trigger() lets the next kernel in the stream do
 // the same with this one.  Without the launch attribute both are no-ops.
+// Every thread of such a kernel calls pdl_wait() at some point, also warps that
+// touch nothing a predecessor wrote (an MMA issuer that only polls a barrier,
+// lanes that idle): with some threads left out, steps of the product on pairs of
+// SMs stalled for good now and then, and with all threads waiting they did not.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }

@@ -269,9 +269,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                 tma_load_2d(ws, &map_w, &full_bar[s], k0, n_tile * BM);
                 tma_load_2d(xs, &map_x, &full_bar[s], k0, t_tile * BN);
             }
+        } else {
+            pdl_wait();  // every thread of a dependent waits for the grid before (see common.cuh)
         }
     } else if (warp == 1) {
         // ---- MMA issuer -----------------------------------------------------------
+        pdl_wait();  // (it could issue nothing earlier: every stage holds token tiles too)
         if (elect_one()) {
             constexpr unsigned idesc = make_idesc(BN);
             bool ok = true;

@@ -271,9 +271,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
             }
             if (!ok) atomicOr(p.err, IB_TIMEOUT_AT(IB_SITE_PAIR_PRODUCER));
+        } else {
+            pdl_wait();  // every thread of a dependent waits for the grid before (see common.cuh)
         }
     } else if (warp == 1) {
         // ---- MMA issuer (leader CTA only) -----------------------------------------------
+        pdl_wait();
         if (rank == 0 && elect_one()) {
             bool ok = true;
             unsigned it = 0, j = 0;
@@ -417,7 +420,11 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap&
     // this kernel's MMA issuer, the one role that does not wait for the grid
     // before, reported its time-out, and producers and epilogues never came out of
     // griddepcontrol.wait.  Launched in order, with the same code, they never did
-    // (the prologue that no longer overlaps is about a microsecond a product).
+    // (the prologue that no longer overlaps is two or three microseconds a product).
+    // In one binary with the variants chosen at run time, the dependent launch also
+    // ran clean when every thread waited for the grid before (the MMA warp and the
+    // idle lanes too, as they now do) or when the kernel let no successor begin
+    // early, and stalled every time as it was.
     cudaError_t le = launch_kernel_in_order(gemm_pair_kernel<SWIGLU>, dim3((unsigned)(pairs * 2)),
                                             dim3(NUM_THREADS), (size_t)SMEM_BYTES, stream, mx, mw, mw2, p);
     if (le != cudaSuccess) return (int)le;
