@@ -23,7 +23,6 @@ draws the weights on the GPU from the configuration file and a seed (the values
 from __future__ import annotations
 
 import argparse
-import dataclasses
 import os
 import sys
 import time

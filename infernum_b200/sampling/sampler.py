@@ -15,7 +15,7 @@ in, nor on having been preempted and recomputed.
 
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -16,7 +16,7 @@ floating tensor to float32, which is exact.
 from __future__ import annotations
 
 import fnmatch
-from typing import Dict, Iterable, Mapping, Tuple
+from typing import Dict, Iterable, Mapping
 
 import torch
 
