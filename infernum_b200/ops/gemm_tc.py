@@ -204,8 +204,8 @@ def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: Optional[tor
     """Takes a product or leaves it to the library.  ``auto``: up to
     ``max_tokens`` tokens go to the kernel that streams the weights once, prompts
     whose length suits its tiles to the kernel on pairs of SMs (inside a model
-    step it is ahead of the library, whose kernels do not start under the tail of
-    their predecessor), the rest to the library; ``all``: every product."""
+    step it is ahead of the library, whose kernels do not let their successor
+    start under their tail), the rest to the library; ``all``: every product."""
     mode = POLICY["mode"]
     if mode in ("none", "cublas", "library") or not eligible(x, w, out):
         return False
